@@ -1,0 +1,167 @@
+/*
+ * mhc_b200.h -- C ABI of the B200 (sm_100a) hyper-connection kernels.
+ *
+ * Every entry point takes raw device pointers, 64-bit sizes and the CUDA stream
+ * to launch on; nothing here depends on PyTorch.  The library never allocates
+ * or frees device memory: outputs and scratch are caller-owned (scratch sizes
+ * come from mhc_scratch_bytes).  Inputs are never written.  All launches go to
+ * the stream passed in; no call synchronises the device or the host.
+ *
+ * Each declaration names the function of the reference project
+ * (WithNucleusAI/mHC-triton, paths relative to its root) that it replaces.
+ *
+ * Return value: 0 on success, otherwise one of the MHC_ERR_* codes; the text
+ * of the last failure on the calling thread is available from
+ * mhc_last_error_string().  No entry point aborts the process.
+ *
+ * Tensor layouts (all contiguous, row-major):
+ *   H, H_residual, H_new, dH*      [B, S, 4, D]   activation dtype (mhc_dtype)
+ *   branch_input / branch_output   [B, S, D]      activation dtype
+ *   H_pre, H_post                  [B, 4]         float32
+ *   H_res                          [B, 4, 4]      float32
+ *   x (pooled state)               [B, 4*D]       float32
+ *   phi                            [4*D, 24]      float32
+ *   bias                           [24]           float32   (pre 0..3, post 4..7, res 8..23)
+ */
+#ifndef MHC_B200_H
+#define MHC_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MHC_B200_VERSION 100 /* major*10000 + minor*100 + patch */
+
+typedef enum mhc_dtype { MHC_F32 = 0, MHC_BF16 = 1, MHC_F16 = 2 } mhc_dtype;
+
+typedef enum mhc_status {
+  MHC_OK = 0,
+  MHC_ERR_NULL_POINTER = 1,
+  MHC_ERR_BAD_SHAPE = 2,
+  MHC_ERR_BAD_DTYPE = 3,
+  MHC_ERR_BAD_ARGUMENT = 4,
+  MHC_ERR_SCRATCH_TOO_SMALL = 5,
+  MHC_ERR_MISALIGNED = 6,
+  MHC_ERR_CUDA = 7
+} mhc_status;
+
+/* d|m|/dm at m == 0 in the Sinkhorn backward.  0: zero (what autograd of the
+ * reference's PyTorch path gives, src/mhc/_torch_baseline.py:27).  1: +1 (what the
+ * reference's device kernel uses, src/mhc/_backward.py:106-121). */
+typedef enum mhc_abs_grad_at_zero { MHC_ABS0_ZERO = 0, MHC_ABS0_PLUS_ONE = 1 } mhc_abs_grad_at_zero;
+
+/* Which entry point a scratch-size query is for. */
+typedef enum mhc_op {
+  MHC_OP_ADD_RESIDUAL_BWD = 0,
+  MHC_OP_STREAM_MIX_BWD = 1,
+  MHC_OP_MEANPOOL_FWD = 2,
+  MHC_OP_DYNAMIC_WEIGHTS_FWD = 3,
+  MHC_OP_DYNAMIC_WEIGHTS_BWD = 4
+} mhc_op;
+
+typedef void* mhc_stream_t; /* a cudaStream_t */
+
+int mhc_version(void);
+const char* mhc_last_error_string(void);
+const char* mhc_status_name(int status);
+/* Kernels launched by this library since it was loaded (all threads). */
+int64_t mhc_launch_count(void);
+
+/* Bytes of device scratch the given entry point needs for these sizes
+ * (for the two dynamic-weights ops S is ignored and D is the per-stream width,
+ * i.e. the projection reads K = 4*D values per row).  Returns < 0 on bad arguments. */
+int64_t mhc_scratch_bytes(int op, int64_t B, int64_t S, int64_t D, int dtype);
+
+/* ---- Sinkhorn-Knopp on a batch of 4x4 matrices --------------------------------
+ * P = Sinkhorn_iters(|M| + eps).  M, P: [batch, 4, 4] of `dtype`.
+ * Replaces sinkhorn_forward, src/mhc/_kernels.py:597-614 (kernel :30-130). */
+int mhc_sinkhorn_fwd(const void* M, void* P, int64_t batch, int dtype, int iters, float eps,
+                     mhc_stream_t stream);
+
+/* dM from dP, recomputing the forward from M (O(iters^2) work, no saved state).
+ * Replaces sinkhorn_backward, src/mhc/_backward.py:503-530 (kernel :29-262). */
+int mhc_sinkhorn_bwd(const void* M, const void* dP, void* dM, int64_t batch, int dtype, int iters,
+                     float eps, int abs_grad_at_zero, mhc_stream_t stream);
+
+/* ---- Stream mix -----------------------------------------------------------------
+ * branch_input[b,s,d] = sum_n H_pre[b,n] H[b,s,n,d];
+ * H_residual[b,s,n,d] = sum_m H_res[b,n,m] H[b,s,m,d].
+ * Replaces stream_mix_forward, src/mhc/_kernels.py:617-652 (kernel :137-236). */
+int mhc_stream_mix_fwd(const void* H, const float* H_pre, const float* H_res, void* branch_input,
+                       void* H_residual, int64_t B, int64_t S, int64_t D, int dtype,
+                       mhc_stream_t stream);
+
+/* dH, dH_pre [B,4] (fp32), dH_res [B,4,4] (fp32) in one pass over the data.
+ * Replaces stream_mix_backward, src/mhc/_backward.py:578-626 (kernel :358-496) including
+ * the torch.sum over its partial buffers (:623-624). */
+int mhc_stream_mix_bwd(const void* d_branch_input, const void* dH_residual, const void* H,
+                       const float* H_pre, const float* H_res, void* dH, float* dH_pre,
+                       float* dH_res, void* scratch, int64_t scratch_bytes, int64_t B, int64_t S,
+                       int64_t D, int dtype, mhc_stream_t stream);
+
+/* Two-pass form used when the pooled-state gradient has to be folded into dH
+ * (the reference leaves that addition to autograd of H.mean(dim=1), src/mhc/module.py:123).
+ *   reduce: only dH_pre / dH_res (reads d_branch_input, dH_residual, H).
+ *   apply : dH[b,s,m,d] = H_pre[b,m] d_bi[b,s,d] + sum_n H_res[b,n,m] dH_residual[b,s,n,d]
+ *                         + inv_S * grad_x[b, m*D + d]      (grad_x fp32, may be NULL). */
+int mhc_stream_mix_bwd_reduce(const void* d_branch_input, const void* dH_residual, const void* H,
+                              float* dH_pre, float* dH_res, void* scratch, int64_t scratch_bytes,
+                              int64_t B, int64_t S, int64_t D, int dtype, mhc_stream_t stream);
+int mhc_stream_mix_bwd_apply(const void* d_branch_input, const void* dH_residual,
+                             const float* H_pre, const float* H_res, const float* grad_x,
+                             float inv_S, void* dH, int64_t B, int64_t S, int64_t D, int dtype,
+                             mhc_stream_t stream);
+
+/* ---- Add residual ---------------------------------------------------------------
+ * H_new[b,s,n,d] = H_residual[b,s,n,d] + H_post[b,n] branch_output[b,s,d].
+ * Replaces add_residual_forward, src/mhc/_kernels.py:655-687 (kernel :244-310). */
+int mhc_add_residual_fwd(const void* H_residual, const void* branch_output, const float* H_post,
+                         void* H_new, int64_t B, int64_t S, int64_t D, int dtype,
+                         mhc_stream_t stream);
+
+/* d_branch_output and dH_post [B,4] (fp32).  dH_residual equals dH_new and is not written:
+ * the caller aliases it.  Replaces add_residual_backward, src/mhc/_backward.py:533-575
+ * (kernel :269-351) including its torch.sum (:573). */
+int mhc_add_residual_bwd(const void* dH_new, const void* branch_output, const float* H_post,
+                         void* d_branch_output, float* dH_post, void* scratch,
+                         int64_t scratch_bytes, int64_t B, int64_t S, int64_t D, int dtype,
+                         mhc_stream_t stream);
+
+/* ---- Sequence mean-pool ---------------------------------------------------------
+ * x[b, n*D + d] = (1/S) sum_s H[b,s,n,d], fp32 output.
+ * Replaces H.mean(dim=1).reshape(B, 4*D), src/mhc/module.py:123. */
+int mhc_meanpool_fwd(const void* H, float* x, void* scratch, int64_t scratch_bytes, int64_t B,
+                     int64_t S, int64_t D, int dtype, mhc_stream_t stream);
+
+/* ---- Dynamic weights ------------------------------------------------------------
+ * raw = x phi; inv_rms = 1/sqrt(sum(x^2)/K + eps); s = inv_rms * alpha_g * raw + bias;
+ * H_pre = sigmoid(s[0:4]) / (sum + eps); H_post = 2 sigmoid(s[4:8]);
+ * H_res = Sinkhorn_iters(|s[8:24]| + eps).  alpha_* are device pointers to one float each
+ * (no host read of the scales).  saved [batch, 32] fp32 receives raw (24 values), sum(x^2),
+ * inv_rms and padding for the backward; it may be NULL.
+ * Replaces fused_dynamic_weights_forward, src/mhc/_kernels.py:690-752 (kernel :318-590). */
+int mhc_dynamic_weights_fwd(const float* x, const float* phi, const float* bias,
+                            const float* alpha_pre, const float* alpha_post,
+                            const float* alpha_res, float* H_pre, float* H_post, float* H_res,
+                            float* saved, void* scratch, int64_t scratch_bytes, int64_t batch,
+                            int64_t K, int iters, float eps, mhc_stream_t stream);
+
+/* Gradients of the above: grad_x [batch,K], grad_phi [K,24], grad_bias [24], grad_alpha [3]
+ * (pre, post, res), all fp32, written (not accumulated) unless `accumulate_params` is non-zero,
+ * in which case grad_phi / grad_bias / grad_alpha are added to.  `saved` is the buffer the
+ * forward filled.  Replaces _FusedDynamicWeights.backward, src/mhc/ops.py:109-228, including its
+ * call of sinkhorn_backward (:161-166). */
+int mhc_dynamic_weights_bwd(const float* x, const float* phi, const float* bias,
+                            const float* alpha_pre, const float* alpha_post,
+                            const float* alpha_res, const float* saved, const float* dH_pre,
+                            const float* dH_post, const float* dH_res, float* grad_x,
+                            float* grad_phi, float* grad_bias, float* grad_alpha, void* scratch,
+                            int64_t scratch_bytes, int64_t batch, int64_t K, int iters, float eps,
+                            int abs_grad_at_zero, int accumulate_params, mhc_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MHC_B200_H */

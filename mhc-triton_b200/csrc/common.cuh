@@ -1,0 +1,232 @@
+// Shared device helpers for the sm_100a hyper-connection kernels: 128-bit element packs,
+// the (batch element, token chunk, column group) work decomposition used by every streaming
+// kernel, and the fixed-order block reduction behind the deterministic weight gradients.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace mhc {
+
+constexpr int kStreams = 4;
+constexpr int kOut = 24;        // 4 pre + 4 post + 16 res
+constexpr int kSavedStride = 32;  // floats per row of the forward's saved buffer
+
+// ---------------------------------------------------------------------------------------
+// Element packs: V elements of T moved as one access (16 bytes when V == vec_width<T>),
+// always computed on as fp32.
+// ---------------------------------------------------------------------------------------
+template <typename T> struct vec_width;
+template <> struct vec_width<float> { static constexpr int value = 4; };
+template <> struct vec_width<__nv_bfloat16> { static constexpr int value = 8; };
+template <> struct vec_width<__half> { static constexpr int value = 8; };
+
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+
+// Read-only 16-byte load that does not allocate in L1 (every byte is used exactly once per kernel).
+__device__ __forceinline__ uint4 ld_stream16(const void* p) {
+  uint4 r;
+  asm("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+      : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+      : "l"(p));
+  return r;
+}
+__device__ __forceinline__ void st_stream16(void* p, uint4 v) {
+  asm volatile("st.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
+template <typename T, int V> struct PackIO;
+
+template <typename T> struct PackIO<T, 1> {
+  static __device__ __forceinline__ void load(const T* __restrict__ p, float (&o)[1]) { o[0] = to_f32(__ldg(p)); }
+  static __device__ __forceinline__ void store(T* __restrict__ p, const float (&v)[1]) { *p = from_f32<T>(v[0]); }
+};
+
+template <> struct PackIO<float, 4> {
+  static __device__ __forceinline__ void load(const float* __restrict__ p, float (&o)[4]) {
+    uint4 r = ld_stream16(p);
+    o[0] = __uint_as_float(r.x); o[1] = __uint_as_float(r.y);
+    o[2] = __uint_as_float(r.z); o[3] = __uint_as_float(r.w);
+  }
+  static __device__ __forceinline__ void store(float* __restrict__ p, const float (&v)[4]) {
+    st_stream16(p, make_uint4(__float_as_uint(v[0]), __float_as_uint(v[1]), __float_as_uint(v[2]),
+                              __float_as_uint(v[3])));
+  }
+};
+
+template <> struct PackIO<__nv_bfloat16, 8> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* __restrict__ p, float (&o)[8]) {
+    uint4 r = ld_stream16(p);
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {  // bf16 -> fp32 is a 16-bit shift
+      o[2 * i] = __uint_as_float(w[i] << 16);
+      o[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* __restrict__ p, const float (&v)[8]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+      w[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    st_stream16(p, make_uint4(w[0], w[1], w[2], w[3]));
+  }
+};
+
+template <> struct PackIO<__half, 8> {
+  static __device__ __forceinline__ void load(const __half* __restrict__ p, float (&o)[8]) {
+    uint4 r = ld_stream16(p);
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+      o[2 * i] = f.x;
+      o[2 * i + 1] = f.y;
+    }
+  }
+  static __device__ __forceinline__ void store(__half* __restrict__ p, const float (&v)[8]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+      w[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    st_stream16(p, make_uint4(w[0], w[1], w[2], w[3]));
+  }
+};
+
+// ---------------------------------------------------------------------------------------
+// Work decomposition.  One CTA = one (batch element b, chunk of `tpc` consecutive tokens,
+// group of blockDim.x consecutive packs along D).  The layout of the per-CTA partial sums
+// depends only on (S, D, dtype, alignment), never on the batch size or the grid, so a batch
+// shard reduces in exactly the same order as the full batch does.
+// ---------------------------------------------------------------------------------------
+struct Geo {
+  int64_t S;       // tokens per batch element
+  int64_t D;       // elements per stream row
+  int32_t DV;      // packs per stream row (D / V)
+  int32_t CG;      // column groups per row = ceil(DV / columns per CTA)
+  int32_t tpc;     // tokens per chunk
+  int32_t nchunk;  // ceil(S / tpc)
+  int32_t cols;    // columns (packs) per CTA
+  int32_t sub;     // token sub-groups inside a CTA (blockDim.x = cols * sub)
+};
+
+struct Item {
+  int64_t b;
+  int32_t chunk, cg;
+  int64_t s0, s1;  // token range
+  int32_t col;     // pack index along D for this thread (may be >= DV: idle lane)
+  int32_t sub;
+  int32_t slot;    // index of this CTA's partial inside its batch element: chunk * CG + cg
+};
+
+__device__ __forceinline__ Item decode_item(const Geo& g) {
+  Item it;
+  const int64_t w = blockIdx.x;
+  it.cg = (int32_t)(w % g.CG);
+  const int64_t r = w / g.CG;
+  it.chunk = (int32_t)(r % g.nchunk);
+  it.b = r / g.nchunk;
+  it.s0 = (int64_t)it.chunk * g.tpc;
+  it.s1 = min(it.s0 + (int64_t)g.tpc, g.S);
+  it.col = it.cg * g.cols + (int32_t)(threadIdx.x % g.cols);
+  it.sub = (int32_t)(threadIdx.x / g.cols);
+  it.slot = it.chunk * g.CG + it.cg;
+  return it;
+}
+
+__device__ __forceinline__ int64_t geo_slots_dev(const Geo& g) { return (int64_t)g.nchunk * g.CG; }
+
+// ---------------------------------------------------------------------------------------
+// Fixed-order block reduction of W per-thread accumulators: xor-shuffle tree inside each warp,
+// then one thread per value sums the warps in index order.  blockDim.x must be a multiple of
+// 32 and every thread of the CTA must call this.  `out` receives W floats.
+// ---------------------------------------------------------------------------------------
+template <int W>
+__device__ __forceinline__ void block_reduce_store(float (&acc)[W], float* __restrict__ out, float* smem) {
+#pragma unroll
+  for (int i = 0; i < W; ++i) {
+    float v = acc[i];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    acc[i] = v;
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+  if (lane == 0) {
+#pragma unroll
+    for (int i = 0; i < W; ++i) smem[warp * W + i] = acc[i];
+  }
+  __syncthreads();
+  if (threadIdx.x < W) {
+    float s = 0.f;
+    for (int w = 0; w < nw; ++w) s += smem[w * W + threadIdx.x];
+    out[threadIdx.x] = s;
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// One Sinkhorn-Knopp iteration on a register-resident 4x4 matrix (row-major m[16]):
+// divide rows by (row sum + eps), then columns by (column sum + eps).  Optionally hands back the
+// sums and the row-normalised matrix, which the backward needs.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void sinkhorn_step(float (&m)[16], float eps, float (&r)[4], float (&mr)[16],
+                                              float (&c)[4]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    r[i] = ((m[4 * i] + m[4 * i + 1]) + m[4 * i + 2]) + m[4 * i + 3] + eps;
+    const float inv = __frcp_rn(r[i]);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) mr[4 * i + j] = m[4 * i + j] * inv;
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    c[j] = ((mr[j] + mr[4 + j]) + mr[8 + j]) + mr[12 + j] + eps;
+    const float inv = __frcp_rn(c[j]);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) m[4 * i + j] = mr[4 * i + j] * inv;
+  }
+}
+
+__device__ __forceinline__ void sinkhorn_step(float (&m)[16], float eps) {
+  float r[4], c[4], mr[16];
+  sinkhorn_step(m, eps, r, mr, c);
+}
+
+// Pull a gradient d (on the output of one iteration) back to the iteration's input.
+// For y = x / (sum(x) + eps) along an axis: dx = (dy - <dy, y>) / (sum(x) + eps).
+__device__ __forceinline__ void sinkhorn_step_bwd(float (&d)[16], const float (&m_out)[16], const float (&r)[4],
+                                                  const float (&mr)[16], const float (&c)[4]) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float dot = ((d[j] * m_out[j] + d[4 + j] * m_out[4 + j]) + d[8 + j] * m_out[8 + j]) +
+                      d[12 + j] * m_out[12 + j];
+    const float inv = __frcp_rn(c[j]);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) d[4 * i + j] = (d[4 * i + j] - dot) * inv;
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float dot = ((d[4 * i] * mr[4 * i] + d[4 * i + 1] * mr[4 * i + 1]) + d[4 * i + 2] * mr[4 * i + 2]) +
+                      d[4 * i + 3] * mr[4 * i + 3];
+    const float inv = __frcp_rn(r[i]);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) d[4 * i + j] = (d[4 * i + j] - dot) * inv;
+  }
+}
+
+__device__ __forceinline__ float sigmoidf_(float v) { return 1.f / (1.f + expf(-v)); }
+
+}  // namespace mhc

@@ -1,0 +1,352 @@
+// Dynamic connection weights: split-K projection x*phi with sum(x^2) in the same pass, then a
+// one-warp finish per row (RMS norm, scale + bias, sigmoids, register-resident Sinkhorn), and
+// the matching backward (Sinkhorn reverse sweep, activation / norm algebra, grad_x, grad_phi,
+// grad_bias, grad_alpha).  phi is read in its parameter layout [K, 24]: one row is 96
+// contiguous bytes, so consecutive k read consecutive memory and no transposed copy exists.
+#include "common.cuh"
+#include "launch.h"
+
+namespace mhc {
+
+constexpr int kProjW = 25;       // 24 dot products + sum of squares
+constexpr int kBwdStride = 56;   // per-row buffer of the backward: ds[24] d_raw[24] coef ga[3] pad
+constexpr int kMaxStoredIters = 64;
+
+static inline int k_slices(int64_t K) {
+  int64_t ks = (K + 511) / 512;
+  if (ks > 128) ks = 128;
+  if (ks < 1) ks = 1;
+  return (int)ks;
+}
+
+int64_t weights_fwd_scratch_bytes(int64_t batch, int64_t K) {
+  return batch * k_slices(K) * kProjW * (int64_t)sizeof(float);
+}
+int64_t weights_bwd_scratch_bytes(int64_t batch, int64_t K) {
+  (void)K;
+  return batch * kBwdStride * (int64_t)sizeof(float);
+}
+
+__device__ __forceinline__ void load_phi_row(const float* __restrict__ phi, int64_t k, bool aligned, float (&p)[24]) {
+  const float* row = phi + k * 24;
+  if (aligned) {
+#pragma unroll
+    for (int i = 0; i < 6; ++i) {
+      const float4 v = __ldg(reinterpret_cast<const float4*>(row) + i);
+      p[4 * i] = v.x; p[4 * i + 1] = v.y; p[4 * i + 2] = v.z; p[4 * i + 3] = v.w;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 24; ++i) p[i] = __ldg(row + i);
+  }
+}
+
+// part[row, slice, 0..23] = sum over the slice's k of x[row,k] phi[k,:];  part[row, slice, 24] = sum x^2.
+__global__ void __launch_bounds__(256)
+k_dw_project(const float* __restrict__ x, const float* __restrict__ phi, float* __restrict__ part, int64_t K,
+             int ks, bool phi_aligned) {
+  __shared__ float red[32 * kProjW];
+  const int64_t row = blockIdx.x / ks;
+  const int slice = (int)(blockIdx.x % ks);
+  const int64_t per = (K + ks - 1) / ks;
+  const int64_t k0 = slice * per, k1 = min(k0 + per, K);
+  float acc[kProjW];
+#pragma unroll
+  for (int i = 0; i < kProjW; ++i) acc[i] = 0.f;
+  const float* xr = x + row * K;
+  for (int64_t k = k0 + threadIdx.x; k < k1; k += blockDim.x) {
+    const float xv = __ldg(xr + k);
+    float p[24];
+    load_phi_row(phi, k, phi_aligned, p);
+#pragma unroll
+    for (int j = 0; j < 24; ++j) acc[j] = fmaf(xv, p[j], acc[j]);
+    acc[24] = fmaf(xv, xv, acc[24]);
+  }
+  block_reduce_store<kProjW>(acc, part + (row * ks + slice) * kProjW, red);
+}
+
+__device__ __forceinline__ float group_alpha(int j, float a_pre, float a_post, float a_res) {
+  return j < 4 ? a_pre : (j < 8 ? a_post : a_res);
+}
+
+// One warp per row: lanes 0..24 add the slices (fp64, index order); lanes 0..7 do the sigmoids;
+// lane 8 runs the Sinkhorn projection in registers.
+__global__ void __launch_bounds__(32)
+k_dw_finish(const float* __restrict__ part, const float* __restrict__ bias, const float* __restrict__ alpha_pre,
+            const float* __restrict__ alpha_post, const float* __restrict__ alpha_res, float* __restrict__ H_pre,
+            float* __restrict__ H_post, float* __restrict__ H_res, float* __restrict__ saved, int64_t K, int ks,
+            int iters, float eps) {
+  __shared__ float s_sc[24];
+  const int64_t row = blockIdx.x;
+  const int lane = threadIdx.x;
+  float tot = 0.f;
+  if (lane < kProjW) {
+    double a = 0.0;
+    const float* p = part + row * ks * kProjW + lane;
+    for (int s = 0; s < ks; ++s) a += (double)__ldg(p + s * kProjW);
+    tot = (float)a;
+  }
+  const float q = __shfl_sync(0xffffffffu, tot, 24);
+  const float inv_rms = 1.f / sqrtf(q / (float)K + eps);
+  const float a_pre = __ldg(alpha_pre), a_post = __ldg(alpha_post), a_res = __ldg(alpha_res);
+  float sc = 0.f;
+  if (lane < 24) {
+    sc = (inv_rms * group_alpha(lane, a_pre, a_post, a_res)) * tot + __ldg(bias + lane);
+    s_sc[lane] = sc;
+    if (saved) saved[row * kSavedStride + lane] = tot;
+  }
+  if (saved && lane == 24) {
+    saved[row * kSavedStride + 24] = q;
+    saved[row * kSavedStride + 25] = inv_rms;
+  }
+  __syncwarp();
+  const float sg = sigmoidf_(sc);
+  // sum of the four pre-mix sigmoids, in index order, visible to lanes 0..3
+  const float s0 = __shfl_sync(0xffffffffu, sg, 0), s1 = __shfl_sync(0xffffffffu, sg, 1),
+              s2 = __shfl_sync(0xffffffffu, sg, 2), s3 = __shfl_sync(0xffffffffu, sg, 3);
+  if (lane < 4) H_pre[row * 4 + lane] = sg / ((((s0 + s1) + s2) + s3) + eps);
+  else if (lane < 8) H_post[row * 4 + (lane - 4)] = 2.f * sg;
+  else if (lane == 8) {
+    float m[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) m[i] = fabsf(s_sc[8 + i]) + eps;
+    for (int t = 0; t < iters; ++t) sinkhorn_step(m, eps);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) H_res[row * 16 + i] = m[i];
+  }
+}
+
+// Per row: gradients of the 24 pre-activation values (ds), of the raw projections (d_raw), the
+// coefficient of x in grad_x that comes from the RMS norm, and this row's share of grad_alpha.
+//   buf[row, 0..23] ds   buf[row, 24..47] d_raw   buf[row, 48] coef   buf[row, 49..51] ga(pre,post,res)
+// Lanes 0..7 handle the sigmoid outputs; lane 8 runs the Sinkhorn reverse sweep (states of all
+// iterations kept in shared memory when iters <= kMaxStoredIters, else recomputed per step).
+__global__ void __launch_bounds__(32)
+k_dw_bwd_rows(const float* __restrict__ saved, const float* __restrict__ bias, const float* __restrict__ alpha_pre,
+              const float* __restrict__ alpha_post, const float* __restrict__ alpha_res,
+              const float* __restrict__ dH_pre, const float* __restrict__ dH_post, const float* __restrict__ dH_res,
+              float* __restrict__ buf, int64_t K, int iters, float eps, float sign_at_zero) {
+  __shared__ float s_sc[24], s_ds[24];
+  __shared__ float s_state[kMaxStoredIters][40];  // r[4] c[4] mr[16] m_out[16]
+  const int64_t row = blockIdx.x;
+  const int lane = threadIdx.x;
+  const float inv_rms = __ldg(saved + row * kSavedStride + 25);
+  const float a_pre = __ldg(alpha_pre), a_post = __ldg(alpha_post), a_res = __ldg(alpha_res);
+  const float alpha = group_alpha(lane, a_pre, a_post, a_res);
+  float raw = 0.f, sc = 0.f;
+  if (lane < 24) {
+    raw = __ldg(saved + row * kSavedStride + lane);
+    sc = (inv_rms * alpha) * raw + __ldg(bias + lane);
+    s_sc[lane] = sc;
+  }
+  __syncwarp();
+  const float sg = sigmoidf_(sc);
+  float g = 0.f;
+  if (lane < 4) g = __ldg(dH_pre + row * 4 + lane);
+  else if (lane < 8) g = __ldg(dH_post + row * 4 + lane - 4);
+  // pre-mix: H_pre = sg / (sum + eps);  d sg = (g - <g, H_pre>) / (sum + eps)
+  const float s0 = __shfl_sync(0xffffffffu, sg, 0), s1 = __shfl_sync(0xffffffffu, sg, 1),
+              s2 = __shfl_sync(0xffffffffu, sg, 2), s3 = __shfl_sync(0xffffffffu, sg, 3);
+  const float ssum = (((s0 + s1) + s2) + s3) + eps;
+  const float gh = lane < 4 ? g * (sg / ssum) : 0.f;
+  const float dot = ((__shfl_sync(0xffffffffu, gh, 0) + __shfl_sync(0xffffffffu, gh, 1)) +
+                     __shfl_sync(0xffffffffu, gh, 2)) + __shfl_sync(0xffffffffu, gh, 3);
+  float ds = 0.f;
+  if (lane < 4) ds = ((g - dot) / ssum) * sg * (1.f - sg);
+  else if (lane < 8) ds = g * 2.f * sg * (1.f - sg);
+  if (lane < 8) s_ds[lane] = ds;
+  if (lane == 8) {
+    float m0[16], d[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      m0[i] = s_sc[8 + i];
+      d[i] = __ldg(dH_res + row * 16 + i);
+    }
+    if (iters <= kMaxStoredIters) {
+      float m[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) m[i] = fabsf(m0[i]) + eps;
+      for (int t = 0; t < iters; ++t) {
+        float r[4], c[4], mr[16];
+        sinkhorn_step(m, eps, r, mr, c);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { s_state[t][i] = r[i]; s_state[t][4 + i] = c[i]; }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) { s_state[t][8 + i] = mr[i]; s_state[t][24 + i] = m[i]; }
+      }
+      for (int t = iters - 1; t >= 0; --t) {
+        float r[4], c[4], mr[16], mo[16];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { r[i] = s_state[t][i]; c[i] = s_state[t][4 + i]; }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) { mr[i] = s_state[t][8 + i]; mo[i] = s_state[t][24 + i]; }
+        sinkhorn_step_bwd(d, mo, r, mr, c);
+      }
+    } else {
+      for (int t = iters - 1; t >= 0; --t) {
+        float m[16], r[4], c[4], mr[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) m[i] = fabsf(m0[i]) + eps;
+        for (int f = 0; f < t; ++f) sinkhorn_step(m, eps);
+        sinkhorn_step(m, eps, r, mr, c);
+        sinkhorn_step_bwd(d, m, r, mr, c);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float sgn = m0[i] > 0.f ? 1.f : (m0[i] < 0.f ? -1.f : sign_at_zero);
+      s_ds[8 + i] = d[i] * sgn;
+    }
+  }
+  __syncwarp();
+  float t_inv = 0.f, t_alpha = 0.f;
+  if (lane < 24) {
+    ds = s_ds[lane];
+    buf[row * kBwdStride + lane] = ds;
+    buf[row * kBwdStride + 24 + lane] = (ds * inv_rms) * alpha;
+    t_inv = (ds * alpha) * raw;       // this lane's term of d(inv_rms)
+    t_alpha = (ds * inv_rms) * raw;   // this lane's term of d(alpha_group)
+  }
+  // fixed-order sums over lanes 0..3, 4..7, 8..23 (lane 0 gathers)
+  float inv_g[3] = {0.f, 0.f, 0.f}, al_g[3] = {0.f, 0.f, 0.f};
+#pragma unroll
+  for (int j = 0; j < 24; ++j) {
+    const float a = __shfl_sync(0xffffffffu, t_inv, j), b = __shfl_sync(0xffffffffu, t_alpha, j);
+    const int gi = j < 4 ? 0 : (j < 8 ? 1 : 2);
+    inv_g[gi] += a;
+    al_g[gi] += b;
+  }
+  if (lane == 0) {
+    const float d_inv_rms = (inv_g[0] + inv_g[1]) + inv_g[2];
+    // inv_rms = 1/rms: d rms = -d_inv_rms * inv_rms^2;  rms = sqrt(sum x^2 / K + eps): d x = d rms * x / (K rms)
+    const float d_rms = d_inv_rms * (-(inv_rms * inv_rms));
+    buf[row * kBwdStride + 48] = d_rms * inv_rms / (float)K;
+    buf[row * kBwdStride + 49] = al_g[0];
+    buf[row * kBwdStride + 50] = al_g[1];
+    buf[row * kBwdStride + 51] = al_g[2];
+  }
+}
+
+// grad_x[row,k] = sum_j d_raw[row,j] phi[k,j] + coef[row] x[row,k];  grad_phi[k,j] = sum_row x[row,k] d_raw[row,j]
+// (rows added in index order, fp64 accumulators).  The last CTA sums grad_bias and grad_alpha over rows.
+constexpr int kRowTile = 32;
+__global__ void __launch_bounds__(256)
+k_dw_bwd_main(const float* __restrict__ x, const float* __restrict__ phi, const float* __restrict__ buf,
+              float* __restrict__ grad_x, float* __restrict__ grad_phi, float* __restrict__ grad_bias,
+              float* __restrict__ grad_alpha, int64_t batch, int64_t K, bool phi_aligned, bool gphi_aligned,
+              int accumulate) {
+  __shared__ float s_draw[kRowTile][25];
+  if (blockIdx.x == gridDim.x - 1) {  // parameter sums over rows
+    const int j = threadIdx.x;
+    if (j < 27) {
+      const int col = j < 24 ? j : 49 + (j - 24);
+      double a = 0.0;
+      for (int64_t r = 0; r < batch; ++r) a += (double)__ldg(buf + r * kBwdStride + col);
+      float* dst = j < 24 ? grad_bias + j : grad_alpha + (j - 24);
+      *dst = accumulate ? *dst + (float)a : (float)a;
+    }
+    return;
+  }
+  const int64_t k = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const bool live = k < K;
+  float p[24];
+  double acc[24];
+#pragma unroll
+  for (int j = 0; j < 24; ++j) { p[j] = 0.f; acc[j] = 0.0; }
+  if (live) load_phi_row(phi, k, phi_aligned, p);
+  for (int64_t r0 = 0; r0 < batch; r0 += kRowTile) {
+    const int nr = (int)min((int64_t)kRowTile, batch - r0);
+    __syncthreads();
+    for (int i = threadIdx.x; i < nr * 25; i += blockDim.x) {
+      const int rr = i / 25, jj = i % 25;
+      s_draw[rr][jj] = __ldg(buf + (r0 + rr) * kBwdStride + 24 + jj);  // d_raw[24] then coef
+    }
+    __syncthreads();
+    if (live) {
+      for (int rr = 0; rr < nr; ++rr) {
+        const float xv = __ldg(x + (r0 + rr) * K + k);
+        double gx = (double)s_draw[rr][24] * (double)xv;
+#pragma unroll
+        for (int j = 0; j < 24; ++j) {
+          gx += (double)s_draw[rr][j] * (double)p[j];
+          acc[j] += (double)xv * (double)s_draw[rr][j];
+        }
+        grad_x[(r0 + rr) * K + k] = (float)gx;
+      }
+    }
+  }
+  if (live) {
+    float* o = grad_phi + k * 24;
+    if (gphi_aligned) {
+#pragma unroll
+      for (int i = 0; i < 6; ++i) {
+        float4 v = make_float4((float)acc[4 * i], (float)acc[4 * i + 1], (float)acc[4 * i + 2], (float)acc[4 * i + 3]);
+        float4* dst = reinterpret_cast<float4*>(o) + i;
+        if (accumulate) { const float4 old = *dst; v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w; }
+        *dst = v;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 24; ++j) o[j] = accumulate ? o[j] + (float)acc[j] : (float)acc[j];
+    }
+  }
+}
+
+}  // namespace mhc
+
+using namespace mhc;
+
+extern "C" int mhc_dynamic_weights_fwd(const float* x, const float* phi, const float* bias, const float* alpha_pre,
+                                       const float* alpha_post, const float* alpha_res, float* H_pre, float* H_post,
+                                       float* H_res, float* saved, void* scratch, int64_t scratch_bytes,
+                                       int64_t batch, int64_t K, int iters, float eps, mhc_stream_t stream) {
+  if (batch < 0 || K <= 0) return fail(MHC_ERR_BAD_SHAPE, "dynamic_weights_fwd: bad shape");
+  if (iters < 0) return fail(MHC_ERR_BAD_ARGUMENT, "dynamic_weights_fwd: iters < 0");
+  if (batch == 0) return MHC_OK;
+  if (!x || !phi || !bias || !alpha_pre || !alpha_post || !alpha_res || !H_pre || !H_post || !H_res || !scratch)
+    return fail(MHC_ERR_NULL_POINTER, "dynamic_weights_fwd: null pointer");
+  const int ks = k_slices(K);
+  if (batch * ks > kMaxGridItems) return fail(MHC_ERR_BAD_SHAPE, "dynamic_weights_fwd: batch too large");
+  if (scratch_bytes < weights_fwd_scratch_bytes(batch, K))
+    return fail(MHC_ERR_SCRATCH_TOO_SMALL, "dynamic_weights_fwd: scratch %lld < %lld bytes", (long long)scratch_bytes,
+                (long long)weights_fwd_scratch_bytes(batch, K));
+  cudaStream_t st = (cudaStream_t)stream;
+  k_dw_project<<<(unsigned)(batch * ks), 256, 0, st>>>(x, phi, (float*)scratch, K, ks, is_aligned16(phi));
+  if (int e = check_launch("dynamic_weights_fwd(project)")) return e;
+  k_dw_finish<<<(unsigned)batch, 32, 0, st>>>((const float*)scratch, bias, alpha_pre, alpha_post, alpha_res, H_pre,
+                                              H_post, H_res, saved, K, ks, iters, eps);
+  return check_launch("dynamic_weights_fwd(finish)");
+}
+
+extern "C" int mhc_dynamic_weights_bwd(const float* x, const float* phi, const float* bias, const float* alpha_pre,
+                                       const float* alpha_post, const float* alpha_res, const float* saved,
+                                       const float* dH_pre, const float* dH_post, const float* dH_res, float* grad_x,
+                                       float* grad_phi, float* grad_bias, float* grad_alpha, void* scratch,
+                                       int64_t scratch_bytes, int64_t batch, int64_t K, int iters, float eps,
+                                       int abs_grad_at_zero, int accumulate_params, mhc_stream_t stream) {
+  if (batch < 0 || K <= 0) return fail(MHC_ERR_BAD_SHAPE, "dynamic_weights_bwd: bad shape");
+  if (iters < 0) return fail(MHC_ERR_BAD_ARGUMENT, "dynamic_weights_bwd: iters < 0");
+  if (abs_grad_at_zero != MHC_ABS0_ZERO && abs_grad_at_zero != MHC_ABS0_PLUS_ONE)
+    return fail(MHC_ERR_BAD_ARGUMENT, "dynamic_weights_bwd: abs_grad_at_zero must be 0 or 1");
+  if (!x && batch) return fail(MHC_ERR_NULL_POINTER, "dynamic_weights_bwd: null pointer");
+  if (!phi || !bias || !alpha_pre || !alpha_post || !alpha_res || !grad_phi || !grad_bias || !grad_alpha)
+    return fail(MHC_ERR_NULL_POINTER, "dynamic_weights_bwd: null pointer");
+  if (batch && (!saved || !dH_pre || !dH_post || !dH_res || !grad_x || !scratch))
+    return fail(MHC_ERR_NULL_POINTER, "dynamic_weights_bwd: null pointer");
+  if (batch > kMaxGridItems) return fail(MHC_ERR_BAD_SHAPE, "dynamic_weights_bwd: batch too large");
+  if (scratch_bytes < weights_bwd_scratch_bytes(batch, K))
+    return fail(MHC_ERR_SCRATCH_TOO_SMALL, "dynamic_weights_bwd: scratch %lld < %lld bytes", (long long)scratch_bytes,
+                (long long)weights_bwd_scratch_bytes(batch, K));
+  cudaStream_t st = (cudaStream_t)stream;
+  if (batch) {
+    k_dw_bwd_rows<<<(unsigned)batch, 32, 0, st>>>(saved, bias, alpha_pre, alpha_post, alpha_res, dH_pre, dH_post,
+                                                  dH_res, (float*)scratch, K, iters, eps,
+                                                  abs_grad_at_zero == MHC_ABS0_PLUS_ONE ? 1.f : 0.f);
+    if (int e = check_launch("dynamic_weights_bwd(rows)")) return e;
+  }
+  const int64_t kblocks = (K + 255) / 256;
+  k_dw_bwd_main<<<(unsigned)(kblocks + 1), 256, 0, st>>>(x, phi, (const float*)scratch, grad_x, grad_phi, grad_bias,
+                                                         grad_alpha, batch, K, is_aligned16(phi),
+                                                         is_aligned16(grad_phi), accumulate_params);
+  return check_launch("dynamic_weights_bwd(main)");
+}

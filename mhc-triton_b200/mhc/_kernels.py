@@ -1,0 +1,122 @@
+"""Forward launch wrappers: validate, allocate outputs with torch, call the C ABI.
+
+Names and signatures follow the launch wrappers of the reference
+(src/mhc/_kernels.py:597-752 there); `block_dim` is accepted and ignored because the
+tiling is fixed inside the CUDA kernels.
+"""
+
+from typing import Tuple
+
+import torch
+
+from . import _lib as L
+
+
+def _check(cond, msg):
+    if not cond:
+        raise AssertionError(msg)
+
+
+def sinkhorn_forward(M: torch.Tensor, num_iters: int = 20, eps: float = 1e-8) -> torch.Tensor:
+    """P = Sinkhorn(|M| + eps) for M of shape (..., 4, 4); same dtype as M."""
+    _check(M.shape[-2:] == (4, 4), "Expected (..., 4, 4)")
+    L.require_cuda(M)
+    M = M.contiguous()
+    P = torch.empty_like(M)
+    with torch.cuda.device(M.device):
+        L.check(L.load().mhc_sinkhorn_fwd(L.ptr(M), L.ptr(P), M.numel() // 16, L.dtype_code(M), int(num_iters),
+                                          float(eps), L.stream_of(M)))
+    return P
+
+
+def stream_mix_forward(H: torch.Tensor, H_pre: torch.Tensor, H_res: torch.Tensor,
+                       block_dim: int = 128) -> Tuple[torch.Tensor, torch.Tensor]:
+    """(branch_input [B,S,D], H_residual [B,S,4,D]) in H's dtype."""
+    _check(H.dim() == 4, "H must be [batch, seq, 4, dim]")
+    B, S, n, D = H.shape
+    _check(n == 4, "num_streams must be 4")
+    _check(tuple(H_pre.shape) == (B, 4), f"H_pre shape mismatch: {tuple(H_pre.shape)} vs ({B}, 4)")
+    _check(tuple(H_res.shape) == (B, 4, 4), f"H_res shape mismatch: {tuple(H_res.shape)} vs ({B}, 4, 4)")
+    L.require_cuda(H, H_pre, H_res)
+    H = H.contiguous()
+    H_pre, H_res = L.f32c(H_pre), L.f32c(H_res)
+    bi = torch.empty(B, S, D, device=H.device, dtype=H.dtype)
+    Hr = torch.empty_like(H)
+    with torch.cuda.device(H.device):
+        L.check(L.load().mhc_stream_mix_fwd(L.ptr(H), L.ptr(H_pre), L.ptr(H_res), L.ptr(bi), L.ptr(Hr), B, S, D,
+                                            L.dtype_code(H), L.stream_of(H)))
+    return bi, Hr
+
+
+def add_residual_forward(H_residual: torch.Tensor, branch_output: torch.Tensor, H_post: torch.Tensor,
+                         block_dim: int = 128) -> torch.Tensor:
+    """H_new = H_residual + H_post[:, None, :, None] * branch_output[:, :, None, :]."""
+    _check(H_residual.dim() == 4, "H_residual must be [batch, seq, 4, dim]")
+    B, S, n, D = H_residual.shape
+    _check(n == 4, "num_streams must be 4")
+    _check(tuple(branch_output.shape) == (B, S, D), "branch_output shape mismatch")
+    _check(tuple(H_post.shape) == (B, 4), "H_post shape mismatch")
+    L.require_cuda(H_residual, branch_output, H_post)
+    H_residual = H_residual.contiguous()
+    branch_output = branch_output.to(H_residual.dtype).contiguous()
+    H_post = L.f32c(H_post)
+    H_new = torch.empty_like(H_residual)
+    with torch.cuda.device(H_residual.device):
+        L.check(L.load().mhc_add_residual_fwd(L.ptr(H_residual), L.ptr(branch_output), L.ptr(H_post), L.ptr(H_new),
+                                              B, S, D, L.dtype_code(H_residual), L.stream_of(H_residual)))
+    return H_new
+
+
+def meanpool_forward(H: torch.Tensor) -> torch.Tensor:
+    """x[b, n*D+d] = mean_s H[b,s,n,d] as fp32 [B, 4*D] (fp32 accumulation, fixed order)."""
+    _check(H.dim() == 4 and H.shape[2] == 4, "H must be [batch, seq, 4, dim]")
+    B, S, _, D = H.shape
+    _check(S > 0, "empty sequence")
+    L.require_cuda(H)
+    H = H.contiguous()
+    x = torch.empty(B, 4 * D, device=H.device, dtype=torch.float32)
+    buf, nbytes = L.scratch(L.OP_MEANPOOL_FWD, B, S, D, H)
+    with torch.cuda.device(H.device):
+        L.check(L.load().mhc_meanpool_fwd(L.ptr(H), L.ptr(x), L.ptr(buf), nbytes, B, S, D, L.dtype_code(H),
+                                          L.stream_of(H)))
+    return x
+
+
+def _alpha_dev(a, like: torch.Tensor) -> torch.Tensor:
+    """A scale as a one-element fp32 device tensor (Python floats are uploaded without a sync)."""
+    if torch.is_tensor(a):
+        _check(a.numel() == 1, "alpha must have one element")
+        L.require_cuda(a)
+        return L.f32c(a.reshape(1))
+    return torch.full((1,), float(a), device=like.device, dtype=torch.float32)
+
+
+def fused_dynamic_weights_forward(x: torch.Tensor, phi: torch.Tensor, bias: torch.Tensor, alpha_pre, alpha_post,
+                                  alpha_res, sinkhorn_iters: int = 20, eps: float = 1e-6, return_saved: bool = False):
+    """(H_pre [B,4], H_post [B,4], H_res [B,4,4]), always fp32.
+
+    alpha_* may be Python floats (as in the reference signature) or one-element device
+    tensors; tensors are read on the device, so no host synchronisation happens.
+    With return_saved=True a fourth tensor [B,32] with the raw projections, sum(x^2) and
+    inv_rms is returned for the backward.
+    """
+    _check(x.dim() == 2, "x must be [batch, in_dim]")
+    B, K = x.shape
+    _check(tuple(phi.shape) == (K, 24), f"phi shape mismatch: {tuple(phi.shape)} vs ({K}, 24)")
+    _check(tuple(bias.shape) == (24,), f"bias shape mismatch: {tuple(bias.shape)} vs (24,)")
+    L.require_cuda(x, phi, bias)
+    x, phi, bias = L.f32c(x), L.f32c(phi), L.f32c(bias)
+    a = [_alpha_dev(v, x) for v in (alpha_pre, alpha_post, alpha_res)]
+    H_pre = torch.empty(B, 4, device=x.device, dtype=torch.float32)
+    H_post = torch.empty(B, 4, device=x.device, dtype=torch.float32)
+    H_res = torch.empty(B, 4, 4, device=x.device, dtype=torch.float32)
+    saved = torch.empty(B, 32, device=x.device, dtype=torch.float32)
+    buf, nbytes = L.scratch(L.OP_DYNAMIC_WEIGHTS_FWD, B, 0, (K + 3) // 4, x)
+    with torch.cuda.device(x.device):
+        L.check(L.load().mhc_dynamic_weights_fwd(L.ptr(x), L.ptr(phi), L.ptr(bias), L.ptr(a[0]), L.ptr(a[1]),
+                                                 L.ptr(a[2]), L.ptr(H_pre), L.ptr(H_post), L.ptr(H_res), L.ptr(saved),
+                                                 L.ptr(buf), nbytes, B, K, int(sinkhorn_iters), float(eps),
+                                                 L.stream_of(x)))
+    if return_saved:
+        return H_pre, H_post, H_res, saved
+    return H_pre, H_post, H_res

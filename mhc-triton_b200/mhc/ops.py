@@ -1,0 +1,187 @@
+"""Autograd ops of the hyper-connection path, backed by the sm_100a CUDA library.
+
+Public functions and their semantics follow the reference's src/mhc/ops.py:231-323:
+sinkhorn_knopp, fused_stream_mix, fused_add_residual, fused_dynamic_weights.
+`hyper_connection_mix` is the fused node the module uses: mean-pool + dynamic weights +
+stream mix in one autograd Function, so that the gradient of the pooled state is folded into
+the single write of dH instead of a separate read-modify-write pass.
+"""
+
+from typing import Tuple
+
+import torch
+
+from ._backward import (add_residual_backward, fused_dynamic_weights_backward, sinkhorn_backward,
+                        stream_mix_backward, stream_mix_backward_apply, stream_mix_backward_reduce)
+from ._kernels import (add_residual_forward, fused_dynamic_weights_forward, meanpool_forward, sinkhorn_forward,
+                       stream_mix_forward)
+
+
+class _SinkhornKnopp(torch.autograd.Function):
+    """Saves only M; the backward recomputes the iterations (reference: src/mhc/ops.py:15-29)."""
+
+    @staticmethod
+    def forward(ctx, M, num_iters, eps):
+        ctx.save_for_backward(M)
+        ctx.num_iters, ctx.eps = num_iters, eps
+        return sinkhorn_forward(M, num_iters, eps)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        (M,) = ctx.saved_tensors
+        return sinkhorn_backward(M, grad_output, ctx.num_iters, ctx.eps), None, None
+
+
+class _FusedStreamMix(torch.autograd.Function):
+    """Reference: src/mhc/ops.py:32-49."""
+
+    @staticmethod
+    def forward(ctx, H, H_pre, H_res):
+        branch_input, H_residual = stream_mix_forward(H, H_pre, H_res)
+        ctx.save_for_backward(H, H_pre, H_res)
+        return branch_input, H_residual
+
+    @staticmethod
+    def backward(ctx, grad_branch_input, grad_H_residual):
+        H, H_pre, H_res = ctx.saved_tensors
+        dH, dH_pre, dH_res = stream_mix_backward(grad_branch_input, grad_H_residual, H, H_pre, H_res)
+        return dH, dH_pre.to(H_pre.dtype), dH_res.to(H_res.dtype)
+
+
+class _FusedAddResidual(torch.autograd.Function):
+    """Reference: src/mhc/ops.py:52-69.  The gradient of H_residual is the upstream gradient
+    itself and is returned without a copy."""
+
+    @staticmethod
+    def forward(ctx, H_residual, branch_output, H_post):
+        H_new = add_residual_forward(H_residual, branch_output, H_post)
+        ctx.save_for_backward(branch_output, H_post)
+        return H_new
+
+    @staticmethod
+    def backward(ctx, grad_H_new):
+        branch_output, H_post = ctx.saved_tensors
+        dH_residual, d_bo, dH_post = add_residual_backward(grad_H_new, branch_output, H_post)
+        return dH_residual, d_bo.to(branch_output.dtype), dH_post.to(H_post.dtype)
+
+
+class _FusedDynamicWeights(torch.autograd.Function):
+    """Reference: src/mhc/ops.py:72-228.  The scales are read on the device (no .item())."""
+
+    @staticmethod
+    def forward(ctx, x, phi, bias, alpha_pre, alpha_post, alpha_res, sinkhorn_iters, eps):
+        H_pre, H_post, H_res, saved = fused_dynamic_weights_forward(
+            x, phi, bias, alpha_pre, alpha_post, alpha_res, sinkhorn_iters, eps, return_saved=True)
+        ctx.save_for_backward(x, phi, bias, alpha_pre, alpha_post, alpha_res, saved)
+        ctx.sinkhorn_iters, ctx.eps = sinkhorn_iters, eps
+        return H_pre, H_post, H_res
+
+    @staticmethod
+    def backward(ctx, grad_H_pre, grad_H_post, grad_H_res):
+        x, phi, bias, alpha_pre, alpha_post, alpha_res, saved = ctx.saved_tensors
+        gx, gphi, gbias, galpha = fused_dynamic_weights_backward(
+            x, phi, bias, alpha_pre, alpha_post, alpha_res, saved, grad_H_pre, grad_H_post, grad_H_res,
+            ctx.sinkhorn_iters, ctx.eps)
+        return (gx.to(x.dtype), gphi.to(phi.dtype), gbias.to(bias.dtype),
+                galpha[0:1].reshape_as(alpha_pre).to(alpha_pre.dtype),
+                galpha[1:2].reshape_as(alpha_post).to(alpha_post.dtype),
+                galpha[2:3].reshape_as(alpha_res).to(alpha_res.dtype), None, None)
+
+
+class _SequenceMeanPool(torch.autograd.Function):
+    """x = H.mean(dim=1).reshape(B, 4*D) in fp32 (reference: src/mhc/module.py:123)."""
+
+    @staticmethod
+    def forward(ctx, H):
+        ctx.shape, ctx.dtype = H.shape, H.dtype
+        return meanpool_forward(H)
+
+    @staticmethod
+    def backward(ctx, gx):
+        B, S, n, D = ctx.shape
+        return (gx.reshape(B, 1, n, D) / S).to(ctx.dtype).expand(B, S, n, D)
+
+
+class _HyperConnectionMix(torch.autograd.Function):
+    """Mean-pool + dynamic weights + stream mix as one autograd node.
+
+    Inputs : H, H_pre_base, H_post_base, H_res_base, phi, alpha_pre, alpha_post, alpha_res
+    Outputs: branch_input, H_residual, H_post
+    Backward: one reduction pass (dH_pre, dH_res), the small weights backward, then one
+    apply pass that writes dH once, including grad_x / S.  When `grad_sink` (a flat fp32
+    buffer of 4*D*24 + 27 elements) is given, grad_phi / grad_bias / grad_alpha are written
+    straight into it, ready for one all-reduce, and `ready_hook` is told so.
+    """
+
+    @staticmethod
+    def forward(ctx, H, H_pre_base, H_post_base, H_res_base, phi, alpha_pre, alpha_post, alpha_res,
+                sinkhorn_iters, eps, grad_sink, ready_hook):
+        x = meanpool_forward(H)
+        bias = torch.cat([H_pre_base.reshape(-1), H_post_base.reshape(-1), H_res_base.reshape(-1)]).float()
+        H_pre, H_post, H_res, saved = fused_dynamic_weights_forward(
+            x, phi, bias, alpha_pre, alpha_post, alpha_res, sinkhorn_iters, eps, return_saved=True)
+        branch_input, H_residual = stream_mix_forward(H, H_pre, H_res)
+        ctx.save_for_backward(H, x, phi, bias, alpha_pre, alpha_post, alpha_res, saved, H_pre, H_res)
+        ctx.sinkhorn_iters, ctx.eps, ctx.grad_sink, ctx.ready_hook = sinkhorn_iters, eps, grad_sink, ready_hook
+        ctx.param_meta = [(p.shape, p.dtype) for p in (H_pre_base, H_post_base, H_res_base)]
+        ctx.mark_non_differentiable(H_pre, H_res)
+        return branch_input, H_residual, H_post, H_pre, H_res
+
+    @staticmethod
+    def backward(ctx, d_branch_input, dH_residual, dH_post, _unused_pre, _unused_res):
+        H, x, phi, bias, alpha_pre, alpha_post, alpha_res, saved, H_pre, H_res = ctx.saved_tensors
+        dH_pre, dH_res = stream_mix_backward_reduce(d_branch_input, dH_residual, H)
+        gx, gphi, gbias, galpha = fused_dynamic_weights_backward(
+            x, phi, bias, alpha_pre, alpha_post, alpha_res, saved, dH_pre, dH_post, dH_res,
+            ctx.sinkhorn_iters, ctx.eps, param_grads=ctx.grad_sink)
+        if ctx.ready_hook is not None:
+            ctx.ready_hook(ctx.grad_sink)
+        dH = stream_mix_backward_apply(d_branch_input, dH_residual, H_pre, H_res, gx, H)
+        if ctx.grad_sink is not None:  # the parameters' .grad tensors are views of the sink already
+            return (dH,) + (None,) * 11
+        (s0, t0), (s1, t1), (s2, t2) = ctx.param_meta
+        return (dH, gbias[0:4].reshape(s0).to(t0), gbias[4:8].reshape(s1).to(t1), gbias[8:24].reshape(s2).to(t2),
+                gphi.to(phi.dtype), galpha[0:1].reshape_as(alpha_pre).to(alpha_pre.dtype),
+                galpha[1:2].reshape_as(alpha_post).to(alpha_post.dtype),
+                galpha[2:3].reshape_as(alpha_res).to(alpha_res.dtype), None, None, None, None)
+
+
+def sinkhorn_knopp(M: torch.Tensor, num_iters: int = 20, eps: float = 1e-8) -> torch.Tensor:
+    """Project (batch, 4, 4) matrices to (approximately) doubly stochastic ones by `num_iters`
+    alternating row / column normalisations of |M| + eps."""
+    return _SinkhornKnopp.apply(M, num_iters, eps)
+
+
+def fused_stream_mix(H: torch.Tensor, H_pre: torch.Tensor, H_res: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """H (batch, seq, 4, dim), H_pre (batch, 4), H_res (batch, 4, 4) ->
+    branch_input (batch, seq, dim), H_residual (batch, seq, 4, dim)."""
+    return _FusedStreamMix.apply(H, H_pre, H_res)
+
+
+def fused_add_residual(H_residual: torch.Tensor, branch_output: torch.Tensor, H_post: torch.Tensor) -> torch.Tensor:
+    """H_new[n] = H_residual[n] + H_post[n] * branch_output, per batch element."""
+    return _FusedAddResidual.apply(H_residual, branch_output, H_post)
+
+
+def fused_dynamic_weights(x, phi, bias, alpha_pre, alpha_post, alpha_res, sinkhorn_iters: int = 20,
+                          eps: float = 1e-6) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """x [batch, in_dim], phi [in_dim, 24], bias [24], three one-element scale tensors ->
+    H_pre [batch, 4] (rows sum to 1), H_post [batch, 4] in (0, 2), H_res [batch, 4, 4]
+    (Sinkhorn-projected).  Outputs are fp32."""
+    return _FusedDynamicWeights.apply(x, phi, bias, alpha_pre, alpha_post, alpha_res, sinkhorn_iters, eps)
+
+
+def sequence_mean_pool(H: torch.Tensor) -> torch.Tensor:
+    """H (batch, seq, 4, dim) -> fp32 (batch, 4*dim) mean over the sequence axis."""
+    return _SequenceMeanPool.apply(H)
+
+
+def hyper_connection_mix(H, H_pre_base, H_post_base, H_res_base, phi, alpha_pre, alpha_post, alpha_res,
+                         sinkhorn_iters: int = 20, eps: float = 1e-6, grad_sink=None, ready_hook=None):
+    """Fused pooled-weights + stream-mix node; returns
+    (branch_input, H_residual, H_post, H_pre, H_res); the last two carry no gradient.
+    With `grad_sink` the parameter gradients are written into that flat buffer and no
+    gradient is returned for the parameters; `ready_hook(grad_sink)` is called as soon as
+    the kernels that fill it have been launched."""
+    return _HyperConnectionMix.apply(H, H_pre_base, H_post_base, H_res_base, phi, alpha_pre, alpha_post, alpha_res,
+                                     sinkhorn_iters, eps, grad_sink, ready_hook)

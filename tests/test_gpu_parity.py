@@ -1,0 +1,340 @@
+"""CUDA path vs the CPU oracle and the golden fixtures, on identical seeded inputs.
+
+Tolerances (stated by the task contract): fp32 rtol 1e-5 / atol 1e-6; bf16/fp16 inputs
+rtol 2e-2 against the fp32 oracle run on up-cast inputs; Sinkhorn row/column sums within
+1e-5 of the oracle's.  Reductions whose fp32 oracle is itself noisier than that band are
+compared with the fp64 oracle, allowing the fp32 oracle's own distance to fp64 as slack.
+"""
+
+import pytest
+import torch
+
+from oracle import mhc_oracle as O
+from tests import cases
+from tests.util import assert_close, assert_close_norm, maxdiff, to_module
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+RT, AT = 1e-5, 1e-6
+
+
+def dev(t):
+    return t.detach().clone().to(DEV)
+
+
+# ------------------------------------------------------------------ Sinkhorn
+def test_sinkhorn_golden(golden):
+    from mhc import sinkhorn_knopp
+    g = golden("sinkhorn.npz")
+    M = dev(g["M"]).requires_grad_(True)
+    P = sinkhorn_knopp(M, 20, 1e-8)
+    assert_close(P, g["P"], RT, AT, "P")
+    P.backward(dev(g["dP"]))
+    assert_close_norm(M.grad, g["dM_f64"], RT, AT, "dM", extra=2 * maxdiff(g["dM"], g["dM_f64"]))
+    P8 = sinkhorn_knopp(dev(g["M8"]))
+    assert_close(P8, g["P8"], RT, AT, "P8")
+    # row / column sums equal the oracle's within 1e-5
+    assert maxdiff(P8.sum(-1), g["P8"].sum(-1)) < 1e-5 and maxdiff(P8.sum(-2), g["P8"].sum(-2)) < 1e-5
+
+
+@pytest.mark.parametrize("T", [1, 5, 20])
+def test_sinkhorn_zero_sign_cases(golden, T):
+    import mhc
+    g = golden("sinkhorn.npz")
+    M = dev(g["Mz"]).requires_grad_(True)
+    P = mhc.sinkhorn_knopp(M, T, 1e-6)
+    assert_close(P, g[f"Pz_T{T}"], RT, AT)
+    P.backward(dev(g["dPz"]))
+    ref = O.sinkhorn_grad(g["Mz"].double(), g["dPz"].double(), T, 1e-6)
+    assert_close_norm(M.grad, ref, 1e-4, 1e-6, "dM")
+    assert (M.grad[M == 0] == 0).all()
+    mhc.set_abs_grad_at_zero("plus_one")
+    try:
+        M2 = dev(g["Mz"]).requires_grad_(True)
+        mhc.sinkhorn_knopp(M2, T, 1e-6).backward(dev(g["dPz"]))
+        ref1 = O.sinkhorn_grad(g["Mz"].double(), g["dPz"].double(), T, 1e-6, sign_of_zero=1.0)
+        assert_close_norm(M2.grad, ref1, 1e-4, 1e-6, "dM(+1)")
+    finally:
+        mhc.set_abs_grad_at_zero("zero")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("batch", [1, 127, 4099])
+def test_sinkhorn_batches_and_dtypes(dtype, batch):
+    from mhc import sinkhorn_knopp
+    torch.manual_seed(batch)
+    M = torch.randn(batch, 4, 4).to(dtype)
+    dP = torch.randn(batch, 4, 4).to(dtype)
+    Md = dev(M).requires_grad_(True)
+    P = sinkhorn_knopp(Md, 20, 1e-6)
+    assert P.dtype == dtype
+    P.backward(dev(dP))
+    Pref = O.sinkhorn(M.double(), 20, 1e-6)
+    dref = O.sinkhorn_grad(M.double(), dP.double(), 20, 1e-6)
+    if dtype == torch.float32:
+        assert_close(P, Pref, RT, AT)
+        assert maxdiff(P.sum(-1), Pref.sum(-1)) < 1e-5 and maxdiff(P.sum(-2), Pref.sum(-2)) < 1e-5
+        assert_close_norm(Md.grad.reshape(batch, -1), dref.reshape(batch, -1), 1e-4, 1e-5)
+    else:
+        assert_close(P, Pref, 2e-2, 1e-3)
+        assert_close_norm(Md.grad, dref, 2e-2, 1e-3)
+
+
+def test_sinkhorn_misaligned_view():
+    from mhc import sinkhorn_knopp
+    torch.manual_seed(3)
+    flat = torch.randn(1 + 5 * 16)
+    M = flat[1:].view(5, 4, 4)               # 4-byte aligned only
+    Md = dev(flat)[1:].view(5, 4, 4)
+    assert Md.data_ptr() % 16 != 0
+    assert_close(sinkhorn_knopp(Md, 20, 1e-6), O.sinkhorn(M, 20, 1e-6), RT, AT)
+
+
+# ------------------------------------------------------------ dynamic weights
+def test_dynamic_weights_golden(golden):
+    from mhc import fused_dynamic_weights
+    g = golden("dynamic_weights.npz")
+    names = ("x", "phi", "bias", "alpha_pre", "alpha_post", "alpha_res")
+    leaves = [dev(g[n]).requires_grad_(True) for n in names]
+    H_pre, H_post, H_res = fused_dynamic_weights(*leaves, 20, 1e-6)
+    assert H_pre.dtype == H_post.dtype == H_res.dtype == torch.float32
+    for got, key in ((H_pre, "H_pre"), (H_post, "H_post"), (H_res, "H_res")):
+        assert_close(got, g[key], RT, AT, key)
+    ((H_pre * dev(g["g_pre"])).sum() + (H_post * dev(g["g_post"])).sum() + (H_res * dev(g["g_res"])).sum()).backward()
+    for n, l in zip(names, leaves):
+        ref64, ref32 = g["d" + n + "_f64"], g["d" + n]
+        assert l.grad.shape == ref32.shape and l.grad.dtype == torch.float32
+        assert_close_norm(l.grad, ref64, RT, AT, "d" + n, extra=2 * maxdiff(ref32, ref64))
+
+
+@pytest.mark.parametrize("B,K", [(1, 4), (2, 100), (16, 4 * 512), (5, 4 * 1000 + 4)])
+def test_dynamic_weights_shapes(B, K):
+    from mhc import fused_dynamic_weights
+    torch.manual_seed(B * 1000 + K)
+    x = torch.randn(B, K)
+    phi = torch.randn(K, 24) * 0.05
+    bias = torch.randn(24)
+    al = [torch.tensor([0.3]), torch.tensor([-0.2]), torch.tensor([0.5])]
+    gp, gq, gr = torch.randn(B, 4), torch.randn(B, 4), torch.randn(B, 4, 4)
+    ref = [t.double().requires_grad_(True) for t in (x, phi, bias, *al)]
+    a, b, c = O.dynamic_weights(*ref, 20, 1e-6)
+    ((a * gp).sum() + (b * gq).sum() + (c * gr).sum()).backward()
+    lv = [dev(t).requires_grad_(True) for t in (x, phi, bias, *al)]
+    a2, b2, c2 = fused_dynamic_weights(*lv, 20, 1e-6)
+    assert_close(a2, a, RT, AT, "H_pre"); assert_close(b2, b, RT, AT, "H_post"); assert_close(c2, c, 2e-5, AT, "H_res")
+    ((a2 * dev(gp)).sum() + (b2 * dev(gq)).sum() + (c2 * dev(gr)).sum()).backward()
+    for r, l, n in zip(ref, lv, "x phi bias a_pre a_post a_res".split()):
+        assert_close_norm(l.grad, r.grad, 1e-4, 1e-6, "d" + n)
+
+
+# ------------------------------------------------------------- streaming ops
+def test_stream_ops_golden(golden):
+    from mhc import fused_add_residual, fused_stream_mix
+    g = golden("stream_mix.npz")
+    lv = [dev(g[n]).requires_grad_(True) for n in ("H", "H_pre", "H_res")]
+    bi, Hr = fused_stream_mix(*lv)
+    assert_close(bi, g["bi"], RT, AT, "bi"); assert_close(Hr, g["Hr"], RT, AT, "Hr")
+    ((bi * dev(g["g_bi"])).sum() + (Hr * dev(g["g_hr"])).sum()).backward()
+    assert_close(lv[0].grad, g["dH"], RT, 2 * AT, "dH")
+    assert_close_norm(lv[1].grad, g["dH_pre"], RT, AT, "dH_pre"); assert_close_norm(lv[2].grad, g["dH_res"], RT, AT, "dH_res")
+    a = golden("add_residual.npz")
+    lv = [dev(a[n]).requires_grad_(True) for n in ("Hr", "bo", "H_post")]
+    H_new = fused_add_residual(*lv)
+    assert_close(H_new, a["H_new"], RT, AT, "H_new")
+    H_new.backward(dev(a["g"]))
+    assert_close(lv[0].grad, a["dHr"], 0, 0, "dHr")
+    assert_close(lv[1].grad, a["dbo"], RT, 2 * AT, "dbo"); assert_close_norm(lv[2].grad, a["dH_post"], RT, AT, "dH_post")
+
+
+SHAPES = [(1, 1, 8), (2, 5, 24), (1, 33, 7), (3, 130, 100), (2, 64, 1024), (1, 257, 2056), (2, 40, 8 * 300)]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,S,D", SHAPES)
+def test_stream_ops_shapes(dtype, B, S, D):
+    """Ragged sizes: odd D (scalar path), S not a multiple of the chunk, single token."""
+    from mhc import fused_add_residual, fused_stream_mix
+    torch.manual_seed(B * 7919 + S * 31 + D)
+    H = torch.randn(B, S, 4, D).to(dtype)
+    H_pre = torch.softmax(torch.randn(B, 4), -1)
+    H_res = O.sinkhorn(torch.randn(B, 4, 4))
+    H_post = 2 * torch.sigmoid(torch.randn(B, 4))
+    bo = torch.randn(B, S, D).to(dtype)
+    g_bi, g_hr, g_new = torch.randn(B, S, D).to(dtype), torch.randn(B, S, 4, D).to(dtype), torch.randn(B, S, 4, D).to(dtype)
+    f = lambda t: t.double().requires_grad_(True)
+    rH, rpre, rres, rpost, rbo = f(H), f(H_pre), f(H_res), f(H_post), f(bo)
+    bi, Hr = O.stream_mix(rH, rpre, rres)
+    ((bi * g_bi.double()).sum() + (Hr * g_hr.double()).sum()).backward()
+    Hr_in = Hr.detach().to(dtype)
+    rHr = f(Hr_in)
+    Hn = O.add_residual(rHr, rbo, rpost)
+    Hn.backward(g_new.double())
+
+    dH_, dpre, dres, dpost = (dev(t).requires_grad_(True) for t in (H, H_pre, H_res, H_post))
+    dbo = dev(bo).requires_grad_(True)
+    bi2, Hr2 = fused_stream_mix(dH_, dpre, dres)
+    assert bi2.dtype == dtype and Hr2.dtype == dtype
+    ((bi2.float() * dev(g_bi).float()).sum() + (Hr2.float() * dev(g_hr).float()).sum()).backward()
+    dHr_in = dev(Hr_in).requires_grad_(True)
+    Hn2 = fused_add_residual(dHr_in, dbo, dpost)
+    Hn2.backward(dev(g_new))
+    rt, at = (RT, 4 * AT) if dtype == torch.float32 else (2e-2, 2e-2)
+    assert_close(bi2, bi, rt, at, "bi"); assert_close(Hr2, Hr, rt, at, "Hr"); assert_close(Hn2, Hn, rt, at, "H_new")
+    assert_close(dH_.grad, rH.grad, rt, at, "dH"); assert_close(dbo.grad, rbo.grad, rt, at, "dbo")
+    assert torch.equal(dHr_in.grad, dev(g_new)), "dH_residual must be the upstream gradient itself"
+    wt = 1e-5 if dtype == torch.float32 else 1e-5   # weight grads are fp32 sums of exact products either way
+    assert_close_norm(dpre.grad, rpre.grad, wt, AT, "dH_pre"); assert_close_norm(dres.grad, rres.grad, wt, AT, "dH_res")
+    assert_close_norm(dpost.grad, rpost.grad, wt, AT, "dH_post")
+
+
+def test_noncontiguous_and_misaligned_inputs():
+    from mhc import fused_stream_mix
+    torch.manual_seed(9)
+    B, S, D = 2, 9, 16
+    big = torch.randn(B, S, 4, D + 3)
+    H = big[..., 3:]                          # non-contiguous view, made contiguous by the wrapper
+    flat = torch.randn(B * S * 4 * D + 1)
+    H2 = flat[1:].view(B, S, 4, D)            # contiguous but only 4-byte aligned: scalar path
+    H_pre = torch.softmax(torch.randn(B, 4), -1)
+    H_res = O.sinkhorn(torch.randn(B, 4, 4))
+    for Hc, Hd in ((H, dev(big)[..., 3:]), (H2, dev(flat)[1:].view(B, S, 4, D))):
+        bi, Hr = fused_stream_mix(Hd, dev(H_pre), dev(H_res))
+        rbi, rHr = O.stream_mix(Hc, H_pre, H_res)
+        assert_close(bi, rbi, RT, 2 * AT); assert_close(Hr, rHr, RT, 2 * AT)
+
+
+def test_empty_batch():
+    from mhc import fused_add_residual, fused_stream_mix, sinkhorn_knopp
+    assert sinkhorn_knopp(torch.empty(0, 4, 4, device=DEV)).shape == (0, 4, 4)
+    bi, Hr = fused_stream_mix(torch.empty(0, 5, 4, 8, device=DEV), torch.empty(0, 4, device=DEV), torch.empty(0, 4, 4, device=DEV))
+    assert bi.shape == (0, 5, 8) and Hr.shape == (0, 5, 4, 8)
+    assert fused_add_residual(Hr, bi, torch.empty(0, 4, device=DEV)).shape == (0, 5, 4, 8)
+
+
+# ------------------------------------------------------------------ whole layer
+def _run_module(hc, H, g, branch):
+    import mhc  # noqa: F401
+    for p in hc.parameters():
+        p.grad = None
+    Hd = dev(H).requires_grad_(True)
+    bi, add = hc(Hd)
+    H_new = add(branch(bi))
+    H_new.backward(dev(g))
+    out = {"branch_input": bi, "H_new": H_new, "dH": Hd.grad}
+    for n, p in hc.named_parameters():
+        out["d" + n.replace(".weight", "")] = p.grad
+    return out
+
+
+@pytest.mark.parametrize("mode", ["fused", "unfused", "static"])
+def test_layer_small_golden(golden, mode):
+    from mhc import HyperConnection
+    g = golden("layer_small.npz")
+    kw = dict(fused=dict(dynamic=True), unfused=dict(dynamic=True, use_fused_weights=False), static=dict(dynamic=False))[mode]
+    hc = HyperConnection(dim=64, layer_idx=1, **kw)
+    p = O.LayerParams(**{k[len(mode) + 7:]: v for k, v in g.items() if k.startswith(mode + ".param.")})
+    to_module(hc, p).to(DEV)
+    Wb = dev(g["Wb"])
+    out = _run_module(hc, g["H"], g["g"], lambda t: torch.tanh(t @ Wb))
+    for k, v in out.items():
+        ref32, ref64 = g[f"{mode}.{k}"], g[f"{mode}.{k}_f64"]
+        assert_close_norm(v, ref64, RT, AT, f"{mode}.{k}", extra=2 * maxdiff(ref32, ref64))
+        if k in ("branch_input", "H_new"):
+            assert_close(v, ref32, RT, 2 * AT, k)
+
+
+@pytest.mark.parametrize("tag", ["default", "perturbed"])
+def test_layer_c1(golden, tag):
+    """Config 1: HyperConnection(512) on fp32 H(2,128,4,512), identity branch, fwd+bwd."""
+    from mhc import HyperConnection
+    g = golden("layer_c1.npz")
+    H, up = cases.c1_inputs()
+    p = cases.c1_params(tag)
+    hc = to_module(HyperConnection(dim=512, num_streams=4, layer_idx=0, dynamic=True, sinkhorn_iters=20,
+                                   init_scale=0.1), p).to(DEV)
+    out = _run_module(hc, H, up, lambda t: t)
+    ref32 = O.layer_fwd_bwd(p, H, up, None, "fused")
+    ref64 = O.layer_fwd_bwd(p, H, up, None, "fused", dtype=torch.float64)
+    for k, v in out.items():
+        if k in ("branch_input", "H_new", "dH"):
+            assert_close(v, ref64[k], RT, 2 * AT, k)                 # full tensors vs the fp64 oracle
+            assert_close(v.flatten()[::97], g[f"{tag}.{k}_sample"], RT, 4 * AT, k + " (fixture)")
+        else:
+            gold32, gold64 = g[f"{tag}.{k}"], g[f"{tag}.{k}_f64"]
+            noise = max(maxdiff(gold32, gold64), maxdiff(ref32[k], ref64[k]))
+            assert_close_norm(v, gold64, RT, AT, k, extra=2 * noise)
+    if tag == "default":
+        # |.| kink: off-diagonal residual-base gradients are exactly zero under the default convention
+        off = ~torch.eye(4, dtype=torch.bool)
+        assert (out["dH_res_base"].cpu()[off] == 0).all()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_layer_half_precision(dtype):
+    """Half-precision H with fp32 parameters (the mixed configuration of configs 3-5, reduced
+    size) against the fp32 oracle on the up-cast input: rtol 2e-2 on outputs and weight grads."""
+    from mhc import HyperConnection
+    torch.manual_seed(0)
+    B, S, D = 2, 512, 512
+    H = torch.randn(B, S, 4, D).to(dtype)
+    up = torch.randn(B, S, 4, D).to(dtype)
+    p = cases.perturb_params_(O.default_params(D, 0, 0.1), 21)
+    hc = to_module(HyperConnection(dim=D), p).to(DEV)
+    lin = torch.nn.Linear(D, D)
+    branch_ref = lambda t: t @ lin.weight.detach().double().T + lin.bias.detach().double()
+    lin_d = torch.nn.Linear(D, D).to(DEV)
+    lin_d.load_state_dict(lin.state_dict()); lin_d = lin_d.to(dtype)
+    out = _run_module(hc, H, up, lin_d)
+    ref = O.layer_fwd_bwd(p, H.float(), up.float(), branch_ref, "fused", dtype=torch.float64)
+    for k, v in out.items():
+        if k in ("branch_input", "H_new", "dH"):
+            assert v.dtype == dtype
+            assert_close_norm(v, ref[k], 2e-2, 0, k)
+        else:
+            assert v.dtype == torch.float32
+            assert_close_norm(v, ref[k], 2e-2, 1e-6, k)
+
+
+def test_determinism_and_shard_invariance():
+    """Two runs are bit-identical, and a batch shard reproduces the full batch's per-element
+    results bit for bit (the reduction layout does not depend on the batch size)."""
+    from mhc import HyperConnection
+    torch.manual_seed(1)
+    B, S, D = 4, 300, 256
+    H = torch.randn(B, S, 4, D).bfloat16()
+    up = torch.randn(B, S, 4, D).bfloat16()
+    p = cases.perturb_params_(O.default_params(D, 0, 0.1), 2)
+    hc = to_module(HyperConnection(dim=D), p).to(DEV)
+    a = _run_module(hc, H, up, lambda t: t)
+    a = {k: v.clone() for k, v in a.items()}
+    b = _run_module(hc, H, up, lambda t: t)
+    for k in a:
+        assert torch.equal(a[k], b[k]), k
+    c = _run_module(hc, H[1:3], up[1:3], lambda t: t)
+    for k in ("branch_input", "H_new", "dH"):
+        assert torch.equal(a[k][1:3], c[k]), k
+
+
+def test_unfused_ops_match_fused_node():
+    """The public ops chained by hand (as the reference module does) give the same result as the
+    fused node the module uses."""
+    import mhc
+    torch.manual_seed(4)
+    B, S, D = 2, 70, 96
+    H = torch.randn(B, S, 4, D)
+    up = torch.randn(B, S, 4, D)
+    p = cases.perturb_params_(O.default_params(D, 0, 0.1), 8)
+    hc = to_module(mhc.HyperConnection(dim=D), p).to(DEV)
+    fused = _run_module(hc, H, up, lambda t: t)
+    fused = {k: v.clone() for k, v in fused.items()}
+    for q in hc.parameters():
+        q.grad = None
+    Hd = dev(H).requires_grad_(True)
+    H_post, H_pre, H_res = hc._compute_weights(Hd)
+    bi, Hr = mhc.fused_stream_mix(Hd, H_pre, H_res)
+    H_new = mhc.fused_add_residual(Hr, bi, H_post)
+    H_new.backward(dev(up))
+    assert_close(bi, fused["branch_input"], 0, 0); assert_close(H_new, fused["H_new"], 0, 0)
+    assert_close(Hd.grad, fused["dH"], RT, 2 * AT, "dH")
+    for n, q in hc.named_parameters():
+        assert_close_norm(q.grad, fused["d" + n], RT, AT, n)

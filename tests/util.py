@@ -1,0 +1,35 @@
+"""Comparison helpers for the parity tests."""
+
+import torch
+
+
+def maxdiff(a, b):
+    return float((a.detach().double().cpu() - b.detach().double().cpu()).abs().max()) if a.numel() else 0.0
+
+
+def assert_close(a, b, rtol, atol, what=""):
+    """Element-wise |a-b| <= atol + rtol*|b|."""
+    a, b = a.detach().double().cpu(), b.detach().double().cpu()
+    assert a.shape == b.shape, (what, a.shape, b.shape)
+    bad = (a - b).abs() > atol + rtol * b.abs()
+    assert not bad.any(), f"{what}: {int(bad.sum())}/{a.numel()} outside tol, max abs diff {float((a - b).abs().max()):.3e}"
+
+
+def assert_close_norm(a, b, rtol, atol, what="", extra=0.0):
+    """Norm-wise max|a-b| <= atol + rtol*max|b| (+ extra)."""
+    a, b = a.detach().double().cpu(), b.detach().double().cpu()
+    assert a.shape == b.shape, (what, a.shape, b.shape)
+    if a.numel() == 0:
+        return
+    d = float((a - b).abs().max())
+    lim = atol + rtol * float(b.abs().max()) + extra
+    assert d <= lim, f"{what}: max abs diff {d:.3e} > {lim:.3e}"
+
+
+def to_module(hc, params):
+    """Copy oracle LayerParams into a HyperConnection (names match the state dict)."""
+    sd = {}
+    for k, v in params.tensors().items():
+        sd[k + ".weight" if k.startswith("W_") else k] = v.detach().clone()
+    hc.load_state_dict(sd)
+    return hc
