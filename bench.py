@@ -1,0 +1,337 @@
+#!/usr/bin/env python
+"""Benchmark of the hyper-connection hot path: one HyperConnection layer, forward + backward.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c4|c3|c1]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+One step = HyperConnection(H) -> identity branch -> add_residual -> backward with an upstream
+gradient on H_new, through the public module API.  The default workload is the bf16
+H(8, 4096, 4, 4096) configuration (phi [16384, 24] ~ N(0, 0.02^2), 20 Sinkhorn iterations).
+With N ranks every rank processes its own batch of that size (whole sequences are the sharding
+unit; weak scaling) and the replicated-parameter gradients are SUM all-reduced over NCCL.
+
+Rank 0 prints one JSON line: tokens/s over all ranks (device-timed, max over ranks), the roofline
+of the dominant kernel (CUDA events around its launches inside the timed region), the same
+metric end to end from pinned host buffers, and the CPU oracle timed on the host cores.
+
+`--impl reference` times the CPU implementation of the same layer (the oracle under oracle/,
+a restatement of the reference's pure-PyTorch path) on the host cores, on a bounded sample.
+"""
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (ROOT, os.path.join(ROOT, "mhc-triton_b200")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import torch  # noqa: E402
+
+WORKLOADS = {
+    # name: (B per rank, S, D, dtype)
+    "c4": (8, 4096, 4096, torch.bfloat16),
+    "c3": (8, 4096, 2048, torch.bfloat16),
+    "c1": (2, 128, 512, torch.float32),
+}
+METRIC = "hc_fwd_bwd_tokens_per_s"
+# Algorithmic HBM bytes per token, in units of D * element size: each logical tensor is read once
+# per consuming op and written once (mean-pool 4, stream mix 9, add residual 9, add-residual
+# backward 6, stream-mix backward: reduction pass 9 + apply pass 9).
+OP_UNITS = {
+    "mhc_meanpool_fwd": 4, "mhc_stream_mix_fwd": 9, "mhc_add_residual_fwd": 9, "mhc_add_residual_bwd": 6,
+    "mhc_stream_mix_bwd_reduce": 9, "mhc_stream_mix_bwd_apply": 9,
+}
+TOTAL_UNITS = 46
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
+# summarised under profiles/, keyed by (workload, op); None = not captured.
+NCU_TRAFFIC = {}
+
+
+def hbm_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks / throttle reasons of one GPU with nvidia-smi while a region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *a):
+        if self.proc is not None:
+            time.sleep(0.12)
+            self.proc.terminate()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def make_layer(D, device):
+    import mhc
+    hc = mhc.HyperConnection(dim=D, num_streams=4, dynamic=True, sinkhorn_iters=20, init_scale=0.1, layer_idx=0)
+    gen = torch.Generator().manual_seed(0)
+    phi_t = torch.randn(24, 4 * D, generator=gen) * 0.02
+    with torch.no_grad():
+        hc.phi.copy_(phi_t.T.contiguous())
+    return hc.to(device)
+
+
+def cpu_oracle_sample(D, S, dtype, steps, warmup, threads=None):
+    """Oracle forward+backward on the host cores for ONE batch element of S tokens (batch elements
+    are independent, so tokens/s of the sample is tokens/s of the workload).  Returns (tokens/s, cores)."""
+    from oracle import mhc_oracle as O
+    cores = threads or os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    gen = torch.Generator().manual_seed(0)
+    H = torch.randn(1, S, 4, D, generator=gen)
+    g = torch.randn(1, S, 4, D, generator=gen)
+    if dtype != torch.float32:   # the CPU path computes in fp32 on the up-cast half-precision values
+        H, g = H.to(dtype).float(), g.to(dtype).float()
+    p = O.default_params(D, 0, 0.1)
+    p.phi.copy_((torch.randn(24, 4 * D, generator=gen) * 0.02).T)
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        O.layer_fwd_bwd(p, H, g, None, "fused")
+        if i >= warmup:
+            times.append(time.perf_counter() - t0)
+    return S / statistics.mean(times), cores, statistics.mean(times)
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    B, S, D, dtype = WORKLOADS[args.workload]
+    tps, cores, sec = cpu_oracle_sample(D, S, dtype, args.steps, args.warmup)
+    sample = f"1 of {B} batch elements per step: {S} tokens, D={D}, fp32 math, fwd+bwd"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tps, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": describe(args.workload), "timed": sample},
+        "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def describe(name):
+    B, S, D, dtype = WORKLOADS[name]
+    return (f"{name}: dynamic HyperConnection fwd+bwd, {str(dtype).split('.')[-1]} H({B},{S},4,{D}) per GPU, "
+            f"fp32 phi[{4 * D},24], 20 Sinkhorn iters, identity branch")
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS))
+    ap.add_argument("--batch", type=int, default=None, help="override the per-GPU batch (profiling small cases)")
+    ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--cpu-steps", type=int, default=2)
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-overlap", action="store_true", help="all-reduce on the compute stream")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch.distributed as dist
+    from mhc import _lib
+    from mhc.parallel import GradSync
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    B, S, D, dtype = WORKLOADS[args.workload]
+    if args.batch:
+        B = args.batch
+    esz = torch.empty(0, dtype=dtype).element_size()
+    gen = torch.Generator(device=dev).manual_seed(1234 + rank)
+    H = torch.randn(B, S, 4, D, device=dev, dtype=torch.float32, generator=gen).to(dtype) if B * S * D <= 2 ** 24 else \
+        torch.cat([torch.randn(1, S, 4, D, device=dev, dtype=torch.float32, generator=gen).to(dtype) for _ in range(B)])
+    g = torch.cat([torch.randn(1, S, 4, D, device=dev, dtype=torch.float32, generator=gen).to(dtype) for _ in range(B)])
+    H.requires_grad_(True)
+    hc = make_layer(D, dev)
+    sync = GradSync([hc], overlap=not args.no_overlap)
+    lib = _lib.load()
+
+    def step():
+        H.grad = None
+        bi, add = hc(H)
+        H_new = add(bi)            # identity branch
+        H_new.backward(g)
+        sync.finish()
+        return H_new
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    # ---- timed region: K steps, device-timed; every C-ABI call is bracketed by CUDA events ----
+    _lib.timer = _lib.KernelTimer()
+    n0 = lib.mhc_launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        ev0.record()
+        for _ in range(args.steps):
+            step()
+        ev1.record()
+        barrier()
+    ms = ev0.elapsed_time(ev1)
+    launches = lib.mhc_launch_count() - n0
+    ksum = _lib.timer.summary()
+    _lib.timer = None
+    t = torch.tensor([ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    ms_per_step = ms / args.steps
+    tokens = B * S * world
+    value = tokens / (ms_per_step * 1e-3)
+
+    # ---- roofline of the dominant kernel (largest share of device time) ----
+    peak, peak_kind = hbm_peak()
+    per_op = {}
+    for name, (calls, total_ms) in ksum.items():
+        units = OP_UNITS.get(name)
+        avg_ms = total_ms / calls
+        ent = {"launches_per_step": calls / args.steps, "avg_ms": avg_ms, "share": total_ms / (ms_per_step * args.steps)}
+        if units:
+            ent["algorithmic_bytes"] = units * D * esz * B * S
+            ent["gbs"] = ent["algorithmic_bytes"] / (avg_ms * 1e-3) / 1e9
+            ent["frac"] = ent["gbs"] / peak
+        per_op[name] = ent
+    dom = max((n for n in per_op if n in OP_UNITS), key=lambda n: per_op[n]["avg_ms"] * per_op[n]["launches_per_step"])
+    roofline = {
+        "bound": "hbm", "kernel": dom, "achieved": per_op[dom]["gbs"], "peak": peak, "peak_kind": f"of {peak_kind}",
+        "unit": "GB/s", "frac": per_op[dom]["frac"], "traffic": NCU_TRAFFIC.get((args.workload, dom)),
+        "algorithmic_bytes_per_launch": per_op[dom]["algorithmic_bytes"],
+        "whole_step": {"algorithmic_bytes": TOTAL_UNITS * D * esz * B * S,
+                       "achieved": TOTAL_UNITS * D * esz * B * S / (ms_per_step * 1e-3) / 1e9,
+                       "frac": TOTAL_UNITS * D * esz * B * S / (ms_per_step * 1e-3) / 1e9 / peak},
+    }
+
+    # ---- end to end: same step from pinned host buffers, results read back to the host ----
+    e2e = None
+    if not args.no_e2e:
+        H_host = H.detach().cpu().pin_memory()
+        g_host = g.cpu().pin_memory()
+        out_new = torch.empty_like(H_host).pin_memory()
+        out_dH = torch.empty_like(H_host).pin_memory()
+        out_grads = torch.empty(sync.flat.numel(), dtype=torch.float32).pin_memory()
+        h2d = H_host.numel() * esz * 2
+        d2h = H_host.numel() * esz * 2 + out_grads.numel() * 4
+
+        def e2e_step():
+            with torch.no_grad():
+                H.copy_(H_host, non_blocking=True)
+                g.copy_(g_host, non_blocking=True)
+            H_new = step()
+            out_new.copy_(H_new.detach(), non_blocking=True)
+            out_dH.copy_(H.grad, non_blocking=True)
+            out_grads.copy_(sync.flat, non_blocking=True)
+
+        e2e_step()
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(args.e2e_steps):
+            e2e_step()
+        b.record()
+        barrier()
+        t = torch.tensor([a.elapsed_time(b)], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item()) / args.e2e_steps
+        e2e = {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+               "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world,
+               "what": "pinned host H and upstream grad -> device, module fwd+bwd, H_new + dH + parameter grads -> pinned host"}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        tps, cores, sec = cpu_oracle_sample(D, S, dtype, args.cpu_steps, 1)
+        cpu = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port",
+               "sample": f"1 of {B} batch elements ({S} tokens, D={D}), fp32 math, fwd+bwd, {args.cpu_steps} timed runs "
+                         f"of {sec:.2f} s"}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16" if dtype == torch.bfloat16 else "f32", "data": "synthetic",
+            "config": {"workload": describe(args.workload) + (f" [batch overridden to {B}]" if args.batch else ""),
+                       "global_tokens": tokens, "sharding": f"batch x{world}",
+                       "l2": "inputs larger than L2 (H alone is %.0f MiB per GPU)" % (B * S * 4 * D * esz / 2 ** 20),
+                       "collective": "NCCL SUM all-reduce of phi/bias/alpha grads" if world > 1 else "none"},
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches) * world,
+            "clocks": clocks.summary(), "kernels": per_op,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

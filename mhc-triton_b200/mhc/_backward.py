@@ -39,9 +39,8 @@ def sinkhorn_backward(M_orig: torch.Tensor, dP: torch.Tensor, num_iters: int = 2
     dP = dP.to(M_orig.dtype).contiguous()
     dM = torch.empty_like(M_orig)
     with torch.cuda.device(M_orig.device):
-        L.check(L.load().mhc_sinkhorn_bwd(L.ptr(M_orig), L.ptr(dP), L.ptr(dM), M_orig.numel() // 16,
-                                          L.dtype_code(M_orig), int(num_iters), float(eps), _ABS0[_abs_grad_at_zero],
-                                          L.stream_of(M_orig)))
+        L.call("mhc_sinkhorn_bwd", L.stream_of(M_orig), L.ptr(M_orig), L.ptr(dP), L.ptr(dM), M_orig.numel() // 16,
+                                          L.dtype_code(M_orig), int(num_iters), float(eps), _ABS0[_abs_grad_at_zero])
     return dM
 
 
@@ -59,9 +58,8 @@ def add_residual_backward(dH_new: torch.Tensor, branch_output: torch.Tensor, H_p
     dH_post = torch.empty(B, 4, device=dH_new.device, dtype=torch.float32)
     buf, nbytes = L.scratch(L.OP_ADD_RESIDUAL_BWD, B, S, D, dH_new)
     with torch.cuda.device(dH_new.device):
-        L.check(L.load().mhc_add_residual_bwd(L.ptr(dH_new), L.ptr(branch_output), L.ptr(H_post), L.ptr(d_bo),
-                                              L.ptr(dH_post), L.ptr(buf), nbytes, B, S, D, L.dtype_code(dH_new),
-                                              L.stream_of(dH_new)))
+        L.call("mhc_add_residual_bwd", L.stream_of(dH_new), L.ptr(dH_new), L.ptr(branch_output), L.ptr(H_post), L.ptr(d_bo),
+                                              L.ptr(dH_post), L.ptr(buf), nbytes, B, S, D, L.dtype_code(dH_new))
     return dH_new, d_bo, dH_post
 
 
@@ -85,9 +83,9 @@ def stream_mix_backward(d_branch_input: torch.Tensor, dH_residual: torch.Tensor,
     dH_res = torch.empty(B, 4, 4, device=H.device, dtype=torch.float32)
     buf, nbytes = L.scratch(L.OP_STREAM_MIX_BWD, B, S, D, H)
     with torch.cuda.device(H.device):
-        L.check(L.load().mhc_stream_mix_bwd(L.ptr(d_bi), L.ptr(dHr), L.ptr(H), L.ptr(H_pre), L.ptr(H_res), L.ptr(dH),
+        L.call("mhc_stream_mix_bwd", L.stream_of(H), L.ptr(d_bi), L.ptr(dHr), L.ptr(H), L.ptr(H_pre), L.ptr(H_res), L.ptr(dH),
                                             L.ptr(dH_pre), L.ptr(dH_res), L.ptr(buf), nbytes, B, S, D,
-                                            L.dtype_code(H), L.stream_of(H)))
+                                            L.dtype_code(H))
     return dH, dH_pre, dH_res
 
 
@@ -99,8 +97,8 @@ def stream_mix_backward_reduce(d_branch_input, dH_residual, H) -> Tuple[torch.Te
     dH_res = torch.empty(B, 4, 4, device=H.device, dtype=torch.float32)
     buf, nbytes = L.scratch(L.OP_STREAM_MIX_BWD, B, S, D, H)
     with torch.cuda.device(H.device):
-        L.check(L.load().mhc_stream_mix_bwd_reduce(L.ptr(d_bi), L.ptr(dHr), L.ptr(H), L.ptr(dH_pre), L.ptr(dH_res),
-                                                   L.ptr(buf), nbytes, B, S, D, L.dtype_code(H), L.stream_of(H)))
+        L.call("mhc_stream_mix_bwd_reduce", L.stream_of(H), L.ptr(d_bi), L.ptr(dHr), L.ptr(H), L.ptr(dH_pre), L.ptr(dH_res),
+                                                   L.ptr(buf), nbytes, B, S, D, L.dtype_code(H))
     return dH_pre, dH_res
 
 
@@ -117,9 +115,8 @@ def stream_mix_backward_apply(d_branch_input, dH_residual, H_pre, H_res, grad_x:
         grad_x = L.f32c(grad_x)
     dH = torch.empty_like(like, memory_format=torch.contiguous_format)
     with torch.cuda.device(like.device):
-        L.check(L.load().mhc_stream_mix_bwd_apply(L.ptr(d_bi), L.ptr(dHr), L.ptr(H_pre), L.ptr(H_res), L.ptr(grad_x),
-                                                  1.0 / S, L.ptr(dH), B, S, D, L.dtype_code(like),
-                                                  L.stream_of(like)))
+        L.call("mhc_stream_mix_bwd_apply", L.stream_of(like), L.ptr(d_bi), L.ptr(dHr), L.ptr(H_pre), L.ptr(H_res), L.ptr(grad_x),
+                                                  1.0 / S, L.ptr(dH), B, S, D, L.dtype_code(like))
     return dH
 
 
@@ -147,8 +144,7 @@ def fused_dynamic_weights_backward(x, phi, bias, alpha_pre, alpha_post, alpha_re
     grad_x = torch.empty(B, K, device=x.device, dtype=torch.float32)
     buf, nbytes = L.scratch(L.OP_DYNAMIC_WEIGHTS_BWD, B, 0, (K + 3) // 4, x)
     with torch.cuda.device(x.device):
-        L.check(L.load().mhc_dynamic_weights_bwd(
-            L.ptr(x), L.ptr(phi), L.ptr(bias), L.ptr(a[0]), L.ptr(a[1]), L.ptr(a[2]), L.ptr(saved), L.ptr(dH_pre),
+        L.call("mhc_dynamic_weights_bwd", L.stream_of(x), L.ptr(x), L.ptr(phi), L.ptr(bias), L.ptr(a[0]), L.ptr(a[1]), L.ptr(a[2]), L.ptr(saved), L.ptr(dH_pre),
             L.ptr(dH_post), L.ptr(dH_res), L.ptr(grad_x), L.ptr(g_phi), L.ptr(g_bias), L.ptr(g_alpha), L.ptr(buf),
-            nbytes, B, K, int(sinkhorn_iters), float(eps), _ABS0[_abs_grad_at_zero], 0, L.stream_of(x)))
+            nbytes, B, K, int(sinkhorn_iters), float(eps), _ABS0[_abs_grad_at_zero], 0)
     return grad_x, g_phi, g_bias, g_alpha

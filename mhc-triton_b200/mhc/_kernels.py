@@ -24,8 +24,8 @@ def sinkhorn_forward(M: torch.Tensor, num_iters: int = 20, eps: float = 1e-8) ->
     M = M.contiguous()
     P = torch.empty_like(M)
     with torch.cuda.device(M.device):
-        L.check(L.load().mhc_sinkhorn_fwd(L.ptr(M), L.ptr(P), M.numel() // 16, L.dtype_code(M), int(num_iters),
-                                          float(eps), L.stream_of(M)))
+        L.call("mhc_sinkhorn_fwd", L.stream_of(M), L.ptr(M), L.ptr(P), M.numel() // 16, L.dtype_code(M), int(num_iters),
+                                          float(eps))
     return P
 
 
@@ -43,8 +43,8 @@ def stream_mix_forward(H: torch.Tensor, H_pre: torch.Tensor, H_res: torch.Tensor
     bi = torch.empty(B, S, D, device=H.device, dtype=H.dtype)
     Hr = torch.empty_like(H)
     with torch.cuda.device(H.device):
-        L.check(L.load().mhc_stream_mix_fwd(L.ptr(H), L.ptr(H_pre), L.ptr(H_res), L.ptr(bi), L.ptr(Hr), B, S, D,
-                                            L.dtype_code(H), L.stream_of(H)))
+        L.call("mhc_stream_mix_fwd", L.stream_of(H), L.ptr(H), L.ptr(H_pre), L.ptr(H_res), L.ptr(bi), L.ptr(Hr), B, S, D,
+                                            L.dtype_code(H))
     return bi, Hr
 
 
@@ -62,8 +62,8 @@ def add_residual_forward(H_residual: torch.Tensor, branch_output: torch.Tensor, 
     H_post = L.f32c(H_post)
     H_new = torch.empty_like(H_residual)
     with torch.cuda.device(H_residual.device):
-        L.check(L.load().mhc_add_residual_fwd(L.ptr(H_residual), L.ptr(branch_output), L.ptr(H_post), L.ptr(H_new),
-                                              B, S, D, L.dtype_code(H_residual), L.stream_of(H_residual)))
+        L.call("mhc_add_residual_fwd", L.stream_of(H_residual), L.ptr(H_residual), L.ptr(branch_output), L.ptr(H_post), L.ptr(H_new),
+                                              B, S, D, L.dtype_code(H_residual))
     return H_new
 
 
@@ -77,8 +77,7 @@ def meanpool_forward(H: torch.Tensor) -> torch.Tensor:
     x = torch.empty(B, 4 * D, device=H.device, dtype=torch.float32)
     buf, nbytes = L.scratch(L.OP_MEANPOOL_FWD, B, S, D, H)
     with torch.cuda.device(H.device):
-        L.check(L.load().mhc_meanpool_fwd(L.ptr(H), L.ptr(x), L.ptr(buf), nbytes, B, S, D, L.dtype_code(H),
-                                          L.stream_of(H)))
+        L.call("mhc_meanpool_fwd", L.stream_of(H), L.ptr(H), L.ptr(x), L.ptr(buf), nbytes, B, S, D, L.dtype_code(H))
     return x
 
 
@@ -113,10 +112,9 @@ def fused_dynamic_weights_forward(x: torch.Tensor, phi: torch.Tensor, bias: torc
     saved = torch.empty(B, 32, device=x.device, dtype=torch.float32)
     buf, nbytes = L.scratch(L.OP_DYNAMIC_WEIGHTS_FWD, B, 0, (K + 3) // 4, x)
     with torch.cuda.device(x.device):
-        L.check(L.load().mhc_dynamic_weights_fwd(L.ptr(x), L.ptr(phi), L.ptr(bias), L.ptr(a[0]), L.ptr(a[1]),
+        L.call("mhc_dynamic_weights_fwd", L.stream_of(x), L.ptr(x), L.ptr(phi), L.ptr(bias), L.ptr(a[0]), L.ptr(a[1]),
                                                  L.ptr(a[2]), L.ptr(H_pre), L.ptr(H_post), L.ptr(H_res), L.ptr(saved),
-                                                 L.ptr(buf), nbytes, B, K, int(sinkhorn_iters), float(eps),
-                                                 L.stream_of(x)))
+                                                 L.ptr(buf), nbytes, B, K, int(sinkhorn_iters), float(eps))
     if return_saved:
         return H_pre, H_post, H_res, saved
     return H_pre, H_post, H_res

@@ -75,6 +75,38 @@ def load():
     return lib
 
 
+class KernelTimer:
+    """Collects CUDA-event pairs around every C-ABI call made while it is installed
+    (`_lib.timer = KernelTimer()`), on the stream the kernels are launched on."""
+
+    def __init__(self):
+        self.records = {}
+
+    def add(self, name, start, end):
+        self.records.setdefault(name, []).append((start, end))
+
+    def summary(self):
+        """name -> (calls, total milliseconds); call after a device synchronize."""
+        return {k: (len(v), sum(a.elapsed_time(b) for a, b in v)) for k, v in self.records.items()}
+
+
+timer = None
+
+
+def call(name, stream, *args):
+    """Invoke an entry point (its last argument is the stream) and raise on a non-zero status."""
+    fn = getattr(load(), name)
+    if timer is None:
+        return check(fn(*args, stream))
+    ext = torch.cuda.ExternalStream(stream) if stream else torch.cuda.current_stream()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record(ext)
+    status = fn(*args, stream)
+    b.record(ext)
+    timer.add(name, a, b)
+    return check(status)
+
+
 def check(status):
     if status != 0:
         lib = load()

@@ -50,11 +50,12 @@ class GradSync:
         if not self.layers:
             raise ValueError("GradSync needs at least one layer")
         self.group = process_group
-        dev = self.layers[0].phi.device
         sizes = []
         for l in self.layers:
             if not getattr(l, "use_fused_weights", False):
                 raise ValueError("GradSync supports fused dynamic HyperConnection layers only")
+        dev = self.layers[0].phi.device
+        for l in self.layers:
             for p in l.parameters():
                 if p.dtype != torch.float32 or p.device != dev:
                     raise ValueError("GradSync needs fp32 parameters on one device")

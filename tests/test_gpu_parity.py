@@ -269,10 +269,44 @@ def test_layer_c1(golden, tag):
         assert (out["dH_res_base"].cpu()[off] == 0).all()
 
 
+class _StoreAs(torch.autograd.Function):
+    """Round a tensor (and, on the way back, its gradient) to a storage dtype: emulates the points
+    where the device path keeps activations in half precision."""
+
+    @staticmethod
+    def forward(ctx, t, dtype):
+        ctx.dtype = dtype
+        return t.to(dtype).to(t.dtype)
+
+    @staticmethod
+    def backward(ctx, g):
+        return g.to(ctx.dtype).to(g.dtype), None
+
+
+def _oracle_with_storage_rounding(p, H, up, branch, dtype):
+    """fp64 oracle whose activations are rounded to `dtype` wherever the device path stores them
+    (branch_input, H_residual, branch_output, H_new and their gradients); weights and weight
+    gradients stay unrounded, as on the device."""
+    p64 = p.to(torch.float64)
+    leaves = {k: v.requires_grad_(True) for k, v in p64.tensors().items()}
+    Hl = H.double().requires_grad_(True)
+    H_pre, H_post, H_res = O.layer_weights(O.LayerParams(**leaves), Hl, "fused", 20, 1e-6)
+    bi, Hr = O.stream_mix(Hl, H_pre, H_res)
+    bi, Hr = _StoreAs.apply(bi, dtype), _StoreAs.apply(Hr, dtype)
+    bo = _StoreAs.apply(branch(bi), dtype)
+    H_new = _StoreAs.apply(O.add_residual(Hr, bo, H_post), dtype)
+    H_new.backward(up.double())
+    out = {"branch_input": bi.detach(), "H_new": H_new.detach(), "dH": Hl.grad}
+    out.update({"d" + k: v.grad for k, v in leaves.items()})
+    return out
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_layer_half_precision(dtype):
     """Half-precision H with fp32 parameters (the mixed configuration of configs 3-5, reduced
-    size) against the fp32 oracle on the up-cast input: rtol 2e-2 on outputs and weight grads."""
+    size).  Outputs and weight gradients are within rtol 2e-2 of the fp32-exact oracle on the
+    up-cast input; the three scalar scale gradients are sums with heavy cancellation, so they are
+    held to rtol 2e-2 against the oracle that rounds activations where the device stores them."""
     from mhc import HyperConnection
     torch.manual_seed(0)
     B, S, D = 2, 512, 512
@@ -280,19 +314,24 @@ def test_layer_half_precision(dtype):
     up = torch.randn(B, S, 4, D).to(dtype)
     p = cases.perturb_params_(O.default_params(D, 0, 0.1), 21)
     hc = to_module(HyperConnection(dim=D), p).to(DEV)
-    lin = torch.nn.Linear(D, D)
-    branch_ref = lambda t: t @ lin.weight.detach().double().T + lin.bias.detach().double()
-    lin_d = torch.nn.Linear(D, D).to(DEV)
-    lin_d.load_state_dict(lin.state_dict()); lin_d = lin_d.to(dtype)
+    lin = torch.nn.Linear(D, D).to(dtype)           # the branch's own weights are half precision too
+    W, bvec = lin.weight.detach().double(), lin.bias.detach().double()
+    branch_ref = lambda t: t @ W.T + bvec
+    lin_d = torch.nn.Linear(D, D).to(dtype)
+    lin_d.load_state_dict(lin.state_dict()); lin_d = lin_d.to(DEV)
     out = _run_module(hc, H, up, lin_d)
     ref = O.layer_fwd_bwd(p, H.float(), up.float(), branch_ref, "fused", dtype=torch.float64)
+    ref_r = _oracle_with_storage_rounding(p, H, up, branch_ref, dtype)
     for k, v in out.items():
         if k in ("branch_input", "H_new", "dH"):
             assert v.dtype == dtype
             assert_close_norm(v, ref[k], 2e-2, 0, k)
+            assert_close_norm(v, ref_r[k], 1e-2, 0, k + " (storage-rounded oracle)")
         else:
             assert v.dtype == torch.float32
-            assert_close_norm(v, ref[k], 2e-2, 1e-6, k)
+            assert_close_norm(v, ref_r[k], 2e-2, 1e-6, k + " (storage-rounded oracle)")
+            if not k.startswith("dalpha"):
+                assert_close_norm(v, ref[k], 2e-2, 1e-6, k)
 
 
 def test_determinism_and_shard_invariance():

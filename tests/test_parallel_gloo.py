@@ -1,0 +1,109 @@
+"""Batch sharding + gradient all-reduce with two CPU ranks over gloo.
+
+The device kernels are not involved: each rank obtains its shard's parameter gradients from
+the CPU oracle, places them in the flat record that GradSync owns (the layout the CUDA backward
+writes), and the SUM all-reduce must reproduce the unsharded gradients; activations and their
+gradients must equal the corresponding slices of the unsharded run.
+"""
+
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import mhc_oracle as O
+from tests import cases
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _fill_record(layer, grads):
+    K24 = 4 * layer.dim * 24
+    rec = layer.grad_sink
+    rec[:K24] = grads["dphi"].reshape(-1)
+    rec[K24:K24 + 4] = grads["dH_pre_base"]
+    rec[K24 + 4:K24 + 8] = grads["dH_post_base"]
+    rec[K24 + 8:K24 + 24] = grads["dH_res_base"].reshape(-1)
+    rec[K24 + 24] = grads["dalpha_pre"][0]
+    rec[K24 + 25] = grads["dalpha_post"][0]
+    rec[K24 + 26] = grads["dalpha_res"][0]
+
+
+def _worker(rank, world, port, B, use_hook, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import mhc
+        from mhc.parallel import GradSync, shard_batch
+        torch.manual_seed(0)
+        S, D = 24, 32
+        H = torch.randn(B, S, 4, D)
+        g = torch.randn(B, S, 4, D)
+        p = cases.perturb_params_(O.default_params(D, 0, 0.1), 3)
+        full = O.layer_fwd_bwd(p, H, g, None, "fused", dtype=torch.float64)
+        Hs, gs = shard_batch(H, rank, world), shard_batch(g, rank, world)
+        mine = O.layer_fwd_bwd(p, Hs, gs, None, "fused", dtype=torch.float64)
+        lo = sum(shard_batch(H, r, world).shape[0] for r in range(rank))
+        for k in ("branch_input", "H_new", "dH"):       # no communication needed for these
+            ref = full[k][lo:lo + Hs.shape[0]]            # fp64; BLAS blocking may differ with the batch size
+            assert (mine[k] - ref).abs().max() <= 1e-12 * (1 + ref.abs().max()), k
+        layer = mhc.HyperConnection(dim=D)
+        sync = GradSync([layer], overlap=True)            # CPU tensors: falls back to the in-line collective
+        assert layer.phi.grad.data_ptr() == sync.flat.data_ptr()
+        _fill_record(layer, {k: v.float() for k, v in mine.items()})
+        if use_hook:
+            layer.grads_ready_hook(layer.grad_sink)
+            sync.finish()
+        else:
+            sync.all_reduce_now()
+        for name, q_ in layer.named_parameters():
+            ref = full["d" + name].float()
+            assert q_.grad.shape == ref.shape
+            assert (q_.grad - ref).abs().max() <= 1e-6 + 1e-5 * ref.abs().max(), name
+        q.put((rank, "ok"))
+    except Exception as e:  # report instead of hanging the peer
+        q.put((rank, f"{type(e).__name__}: {e}"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("B,use_hook", [(4, False), (5, True)])
+def test_two_rank_gradient_allreduce(B, use_hook):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, B, use_hook, q)) for r in range(2)]
+    for pr in procs:
+        pr.start()
+    results = [q.get(timeout=120) for _ in procs]
+    for pr in procs:
+        pr.join(timeout=60)
+    assert sorted(results) == [(0, "ok"), (1, "ok")], results
+
+
+def test_shard_batch_covers_batch_once():
+    from mhc.parallel import shard_batch, sink_numel
+    t = torch.arange(11)
+    for world in (1, 2, 3, 4, 8):
+        parts = [shard_batch(t, r, world) for r in range(world)]
+        assert torch.equal(torch.cat(parts), t)
+        assert max(len(p) for p in parts) - min(len(p) for p in parts) <= 1
+    assert sink_numel(4096) == 16384 * 24 + 27
+
+
+def test_gradsync_rejects_unsupported_layers():
+    import mhc
+    from mhc.parallel import GradSync
+    with pytest.raises(ValueError):
+        GradSync([])
+    with pytest.raises(ValueError):
+        GradSync([mhc.HyperConnection(dim=8, dynamic=False)])
+    with pytest.raises(ValueError):
+        GradSync([mhc.HyperConnection(dim=8).half()])
