@@ -45,12 +45,12 @@ METRIC = "hc_fwd_bwd_tokens_per_s"
 # per consuming op and written once (mean-pool 4, stream mix 9, add residual 9, add-residual
 # backward 6, stream-mix backward: reduction pass 9 + apply pass 9).
 OP_UNITS = {
-    "mhc_meanpool_fwd": 4, "mhc_stream_mix_fwd": 9, "mhc_add_residual_fwd": 9, "mhc_add_residual_bwd": 6,
-    "mhc_stream_mix_bwd_reduce": 9, "mhc_stream_mix_bwd_apply": 9,
+    "k_meanpool_partial": 4, "k_stream_mix_fwd": 9, "k_add_residual_fwd": 9, "k_add_residual_bwd": 6,
+    "k_stream_mix_bwd_reduce": 9, "k_stream_mix_bwd_apply": 9,
 }
 TOTAL_UNITS = 46
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
-# summarised under profiles/, keyed by (workload, op); None = not captured.
+# summarised under profiles/, keyed by (workload, kernel); None = not captured.
 NCU_TRAFFIC = {}
 
 
@@ -229,8 +229,8 @@ def main():
     for _ in range(args.warmup):
         step()
     barrier()
-    # ---- timed region: K steps, device-timed; every C-ABI call is bracketed by CUDA events ----
-    _lib.timer = _lib.KernelTimer()
+    # ---- timed region: K steps, device-timed; the library brackets every kernel launch with CUDA events ----
+    _lib.profile_start()
     n0 = lib.mhc_launch_count()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local) as clocks:
@@ -241,8 +241,7 @@ def main():
         barrier()
     ms = ev0.elapsed_time(ev1)
     launches = lib.mhc_launch_count() - n0
-    ksum = _lib.timer.summary()
-    _lib.timer = None
+    ksum = _lib.profile_stop()
     t = torch.tensor([ms], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)

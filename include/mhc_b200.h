@@ -58,7 +58,9 @@ typedef enum mhc_op {
   MHC_OP_STREAM_MIX_BWD = 1,
   MHC_OP_MEANPOOL_FWD = 2,
   MHC_OP_DYNAMIC_WEIGHTS_FWD = 3,
-  MHC_OP_DYNAMIC_WEIGHTS_BWD = 4
+  MHC_OP_DYNAMIC_WEIGHTS_BWD = 4,
+  MHC_OP_HC_MIX_FWD = 5,
+  MHC_OP_HC_MIX_BWD = 6
 } mhc_op;
 
 typedef void* mhc_stream_t; /* a cudaStream_t */
@@ -68,6 +70,13 @@ const char* mhc_last_error_string(void);
 const char* mhc_status_name(int status);
 /* Kernels launched by this library since it was loaded (all threads). */
 int64_t mhc_launch_count(void);
+
+/* Per-kernel timing.  While enabled, every kernel launch of this library is bracketed by two CUDA
+ * events on the stream it is launched on.  enable(1) drops earlier records and starts; enable(0)
+ * stops.  After the device is synchronised, record i gives the kernel's name and its duration. */
+int mhc_profile_enable(int on);
+int64_t mhc_profile_count(void);
+int mhc_profile_get(int64_t index, const char** name, float* milliseconds);
 
 /* Bytes of device scratch the given entry point needs for these sizes
  * (for the two dynamic-weights ops S is ignored and D is the per-stream width,
@@ -160,6 +169,33 @@ int mhc_dynamic_weights_bwd(const float* x, const float* phi, const float* bias,
                             float* grad_phi, float* grad_bias, float* grad_alpha, void* scratch,
                             int64_t scratch_bytes, int64_t batch, int64_t K, int iters, float eps,
                             int abs_grad_at_zero, int accumulate_params, mhc_stream_t stream);
+
+/* ---- Fused layer entry points ------------------------------------------------------
+ * Forward of the module's fused dynamic path in one call: x = mean_s H (fp32 [B,4D], output),
+ * the dynamic weights from x (bias given as the three base parameters, pre [4], post [4],
+ * res [16]), then the stream mix.  Replaces the chain HyperConnection._compute_weights (fused
+ * branch, src/mhc/module.py:119-139) + fused_stream_mix (src/mhc/module.py:177). */
+int mhc_hc_mix_fwd(const void* H, const float* phi, const float* H_pre_base, const float* H_post_base,
+                   const float* H_res_base, const float* alpha_pre, const float* alpha_post,
+                   const float* alpha_res, float* x, float* H_pre, float* H_post, float* H_res,
+                   float* saved, void* branch_input, void* H_residual, void* scratch,
+                   int64_t scratch_bytes, int64_t B, int64_t S, int64_t D, int dtype, int iters,
+                   float eps, mhc_stream_t stream);
+
+/* Backward of the same chain in one call.  In: gradients of branch_input, H_residual and H_post
+ * plus what the forward left (H, x, saved, H_pre, H_res).  Out: dH (including grad_x / S, i.e.
+ * the gradient through the mean-pool), grad_phi [4D,24], grad_bias [24] (pre, post, res bases),
+ * grad_alpha [3]; grad_x [B,4D], dH_pre [B,4] and dH_res [B,16] are also written (fp32).
+ * Replaces _FusedStreamMix.backward + _FusedDynamicWeights.backward (src/mhc/ops.py:42-49,
+ * 109-228) and autograd's backward of H.mean(dim=1) and torch.cat (src/mhc/module.py:123-131). */
+int mhc_hc_mix_bwd(const void* d_branch_input, const void* dH_residual, const float* dH_post,
+                   const void* H, const float* x, const float* phi, const float* H_pre_base,
+                   const float* H_post_base, const float* H_res_base, const float* alpha_pre,
+                   const float* alpha_post, const float* alpha_res, const float* saved,
+                   const float* H_pre, const float* H_res, void* dH, float* grad_phi, float* grad_bias,
+                   float* grad_alpha, float* grad_x, float* dH_pre, float* dH_res, void* scratch,
+                   int64_t scratch_bytes, int64_t B, int64_t S, int64_t D, int dtype, int iters,
+                   float eps, int abs_grad_at_zero, int accumulate_params, mhc_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -2,6 +2,8 @@
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
+#include <mutex>
+#include <vector>
 
 #include "launch.h"
 
@@ -27,7 +29,66 @@ int check_launch(const char* what) {
   return fail(MHC_ERR_CUDA, "%s: CUDA error %d (%s)", what, (int)e, cudaGetErrorString(e));
 }
 
+// ---- optional per-kernel timing: CUDA events around each launch, on the launching stream ----
+struct ProfRec { const char* name; cudaEvent_t a, b; };
+static std::atomic<int> g_prof_on{0};
+static std::mutex g_prof_mu;
+static std::vector<ProfRec> g_prof;
+
+ProfScope::ProfScope(const char* name, cudaStream_t s) : slot(-1), st(s) {
+  if (!g_prof_on.load(std::memory_order_relaxed)) return;
+  ProfRec r{name, nullptr, nullptr};
+  if (cudaEventCreate(&r.a) != cudaSuccess || cudaEventCreate(&r.b) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return;
+  }
+  cudaEventRecord(r.a, st);
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  g_prof.push_back(r);
+  slot = (int)g_prof.size() - 1;
+}
+
+ProfScope::~ProfScope() {
+  if (slot < 0) return;
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  if (slot < (int)g_prof.size()) cudaEventRecord(g_prof[slot].b, st);
+}
+
+static void prof_clear() {
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  for (auto& r : g_prof) {
+    cudaEventDestroy(r.a);
+    cudaEventDestroy(r.b);
+  }
+  g_prof.clear();
+}
+
 }  // namespace mhc
+
+extern "C" int mhc_profile_enable(int on) {
+  if (on) mhc::prof_clear();
+  mhc::g_prof_on.store(on ? 1 : 0);
+  return MHC_OK;
+}
+
+extern "C" int64_t mhc_profile_count(void) {
+  std::lock_guard<std::mutex> lk(mhc::g_prof_mu);
+  return (int64_t)mhc::g_prof.size();
+}
+
+extern "C" int mhc_profile_get(int64_t index, const char** name, float* milliseconds) {
+  std::lock_guard<std::mutex> lk(mhc::g_prof_mu);
+  if (index < 0 || index >= (int64_t)mhc::g_prof.size() || !name || !milliseconds)
+    return mhc::fail(MHC_ERR_BAD_ARGUMENT, "profile_get: bad index or null pointer");
+  const mhc::ProfRec& r = mhc::g_prof[(size_t)index];
+  *name = r.name;
+  const cudaError_t e = cudaEventElapsedTime(milliseconds, r.a, r.b);
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    return mhc::fail(MHC_ERR_CUDA, "profile_get: %s (synchronize the device first)", cudaGetErrorString(e));
+  }
+  return MHC_OK;
+}
 
 extern "C" int mhc_version(void) { return MHC_B200_VERSION; }
 

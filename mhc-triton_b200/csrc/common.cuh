@@ -107,6 +107,65 @@ template <> struct PackIO<__half, 8> {
   }
 };
 
+// Raw (unconverted) packs: what a load leaves in registers until the arithmetic needs it.  Keeping
+// the next token's packs raw lets a thread hold a second token in flight for 4 registers per pack.
+template <typename T, int V> struct RawPack { uint4 w; };
+template <typename T> struct RawPack<T, 1> { T w; };
+
+template <typename T, int V> __device__ __forceinline__ RawPack<T, V> ld_raw(const T* __restrict__ p) {
+  RawPack<T, V> r;
+  r.w = ld_stream16(p);
+  return r;
+}
+template <> __device__ __forceinline__ RawPack<float, 1> ld_raw<float, 1>(const float* __restrict__ p) {
+  RawPack<float, 1> r; r.w = __ldg(p); return r;
+}
+template <> __device__ __forceinline__ RawPack<__nv_bfloat16, 1> ld_raw<__nv_bfloat16, 1>(const __nv_bfloat16* __restrict__ p) {
+  RawPack<__nv_bfloat16, 1> r; r.w = __ldg(p); return r;
+}
+template <> __device__ __forceinline__ RawPack<__half, 1> ld_raw<__half, 1>(const __half* __restrict__ p) {
+  RawPack<__half, 1> r; r.w = __ldg(p); return r;
+}
+
+// Element e (compile-time constant after unrolling) of a raw pack, as fp32.
+template <int V> __device__ __forceinline__ float raw_get(const RawPack<float, V>& r, int e) {
+  if constexpr (V == 1) return r.w;
+  else return __uint_as_float(e == 0 ? r.w.x : e == 1 ? r.w.y : e == 2 ? r.w.z : r.w.w);
+}
+template <int V> __device__ __forceinline__ float raw_get(const RawPack<__nv_bfloat16, V>& r, int e) {
+  if constexpr (V == 1) return __bfloat162float(r.w);
+  else {
+    const uint32_t w = (e >> 1) == 0 ? r.w.x : (e >> 1) == 1 ? r.w.y : (e >> 1) == 2 ? r.w.z : r.w.w;
+    return __uint_as_float((e & 1) ? (w & 0xffff0000u) : (w << 16));
+  }
+}
+template <int V> __device__ __forceinline__ float raw_get(const RawPack<__half, V>& r, int e) {
+  if constexpr (V == 1) return __half2float(r.w);
+  else {
+    const uint32_t w = (e >> 1) == 0 ? r.w.x : (e >> 1) == 1 ? r.w.y : (e >> 1) == 2 ? r.w.z : r.w.w;
+    const __half2 h = *reinterpret_cast<const __half2*>(&w);
+    return (e & 1) ? __high2float(h) : __low2float(h);
+  }
+}
+
+// Software pipeline over the tokens s0, s0+step, ... < s1: the loads of the next token are issued
+// before the arithmetic of the current one, so every thread always has one token's packs in flight.
+template <class Bundle, class Load, class Compute>
+__device__ __forceinline__ void for_tokens_pipelined(int64_t s0, int64_t s1, int64_t step, Load load, Compute compute) {
+  if (s0 >= s1) return;
+  Bundle a, b;
+  load(a, s0);
+  for (int64_t s = s0; s < s1; s += 2 * step) {
+    const bool second = s + step < s1;
+    if (second) load(b, s + step);
+    compute(a, s);
+    if (second) {
+      if (s + 2 * step < s1) load(a, s + 2 * step);
+      compute(b, s + step);
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------
 // Work decomposition.  One CTA = one (batch element b, chunk of `tpc` consecutive tokens,
 // group of blockDim.x consecutive packs along D).  The layout of the per-CTA partial sums
@@ -177,6 +236,20 @@ __device__ __forceinline__ void block_reduce_store(float (&acc)[W], float* __res
   }
 }
 
+// 1/x with one MUFU instruction (relative error about 1 ulp); every divisor here is >= eps > 0.
+__device__ __forceinline__ float rcp_fast(float x) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+
+// Sum over the 32 lanes of a warp in fp64, xor-shuffle tree (the same order on every lane).
+__device__ __forceinline__ double warp_sum_f64(double v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
 // ---------------------------------------------------------------------------------------
 // One Sinkhorn-Knopp iteration on a register-resident 4x4 matrix (row-major m[16]):
 // divide rows by (row sum + eps), then columns by (column sum + eps).  Optionally hands back the
@@ -187,14 +260,14 @@ __device__ __forceinline__ void sinkhorn_step(float (&m)[16], float eps, float (
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     r[i] = ((m[4 * i] + m[4 * i + 1]) + m[4 * i + 2]) + m[4 * i + 3] + eps;
-    const float inv = __frcp_rn(r[i]);
+    const float inv = rcp_fast(r[i]);
 #pragma unroll
     for (int j = 0; j < 4; ++j) mr[4 * i + j] = m[4 * i + j] * inv;
   }
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     c[j] = ((mr[j] + mr[4 + j]) + mr[8 + j]) + mr[12 + j] + eps;
-    const float inv = __frcp_rn(c[j]);
+    const float inv = rcp_fast(c[j]);
 #pragma unroll
     for (int i = 0; i < 4; ++i) m[4 * i + j] = mr[4 * i + j] * inv;
   }
@@ -213,7 +286,7 @@ __device__ __forceinline__ void sinkhorn_step_bwd(float (&d)[16], const float (&
   for (int j = 0; j < 4; ++j) {
     const float dot = ((d[j] * m_out[j] + d[4 + j] * m_out[4 + j]) + d[8 + j] * m_out[8 + j]) +
                       d[12 + j] * m_out[12 + j];
-    const float inv = __frcp_rn(c[j]);
+    const float inv = rcp_fast(c[j]);
 #pragma unroll
     for (int i = 0; i < 4; ++i) d[4 * i + j] = (d[4 * i + j] - dot) * inv;
   }
@@ -221,7 +294,7 @@ __device__ __forceinline__ void sinkhorn_step_bwd(float (&d)[16], const float (&
   for (int i = 0; i < 4; ++i) {
     const float dot = ((d[4 * i] * mr[4 * i] + d[4 * i + 1] * mr[4 * i + 1]) + d[4 * i + 2] * mr[4 * i + 2]) +
                       d[4 * i + 3] * mr[4 * i + 3];
-    const float inv = __frcp_rn(r[i]);
+    const float inv = rcp_fast(r[i]);
 #pragma unroll
     for (int j = 0; j < 4; ++j) d[4 * i + j] = (d[4 * i + j] - dot) * inv;
   }

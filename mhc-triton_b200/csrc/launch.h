@@ -29,6 +29,41 @@ inline int64_t geo_slots(const Geo& g) { return (int64_t)g.nchunk * g.CG; }  // 
 // Pack width usable for a row length D of `dtype` given the pointers involved.
 int pick_vec(int dtype, int64_t D, std::initializer_list<const void*> ptrs);
 
+// The 24 bias entries as three device arrays (pre-mix base [4], post base [4], residual base [16]).
+struct BiasPtrs { const float *pre, *post, *res; };
+
+// Brackets one kernel launch with CUDA events on its stream while profiling is enabled
+// (mhc_profile_enable); free when it is not.
+struct ProfScope {
+  ProfScope(const char* name, cudaStream_t st);
+  ~ProfScope();
+  int slot;
+  cudaStream_t st;
+};
+
+// Internal launch sequences shared by the single-op and the fused entry points.
+int stream_mix_fwd_impl(const void* H, const float* H_pre, const float* H_res, void* bi, void* Hr, int64_t B, int64_t S,
+                        int64_t D, int dtype, cudaStream_t st);
+int meanpool_partial_impl(const void* H, float* part, int64_t B, int64_t S, int64_t D, int dtype, cudaStream_t st,
+                          int* nchunk);
+int mix_bwd_partials_impl(int mode, const void* dbi, const void* dHr, const void* H, const float* H_pre,
+                          const float* H_res, void* dH, float* part, int64_t B, int64_t S, int64_t D, int dtype,
+                          cudaStream_t st, int64_t* slots);
+int check_bsd_pub(const char* what, int64_t B, int64_t S, int64_t D, int dtype);
+int mix_bwd_apply_impl(const void* dbi, const void* dHr, const float* H_pre, const float* H_res, const float* gx,
+                       float inv_S, void* dH, int64_t B, int64_t S, int64_t D, int dtype, cudaStream_t st);
+int64_t meanpool_scratch_floats(int64_t B, int64_t S, int64_t D);
+int64_t mix_bwd_scratch_floats(int64_t B, int64_t S, int64_t D);
+int weights_fwd_impl(const float* xsrc, int nsrc, float scale, float* x_out, const float* phi, BiasPtrs bias,
+                     const float* alpha_pre, const float* alpha_post, const float* alpha_res, float* H_pre,
+                     float* H_post, float* H_res, float* saved, float* part, int64_t batch, int64_t K, int iters,
+                     float eps, cudaStream_t st);
+int weights_bwd_impl(const float* x, const float* phi, BiasPtrs bias, const float* alpha_pre, const float* alpha_post,
+                     const float* alpha_res, const float* saved, const float* part20, int64_t slots, float* dH_pre,
+                     const float* dH_post, float* dH_res, float* grad_x, float* grad_phi, float* grad_bias,
+                     float* grad_alpha, float* buf, int64_t batch, int64_t K, int iters, float eps,
+                     int abs_grad_at_zero, int accumulate_params, cudaStream_t st);
+
 int64_t weights_fwd_scratch_bytes(int64_t batch, int64_t K);
 int64_t weights_bwd_scratch_bytes(int64_t batch, int64_t K);
 

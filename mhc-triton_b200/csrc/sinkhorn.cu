@@ -86,7 +86,10 @@ static int launch_fwd(const void* M, void* P, int64_t batch, int iters, float ep
   const bool aligned = is_aligned16(M) && is_aligned16(P);
   const int block = 128;
   const int64_t grid = (batch + block - 1) / block;
-  k_sinkhorn_fwd<T><<<(unsigned)grid, block, 0, st>>>((const T*)M, (T*)P, batch, iters, eps, aligned);
+  {
+    ProfScope ps("k_sinkhorn_fwd", st);
+    k_sinkhorn_fwd<T><<<(unsigned)grid, block, 0, st>>>((const T*)M, (T*)P, batch, iters, eps, aligned);
+  }
   return check_launch("sinkhorn_fwd");
 }
 
@@ -96,8 +99,11 @@ static int launch_bwd(const void* M, const void* dP, void* dM, int64_t batch, in
   const bool aligned = is_aligned16(M) && is_aligned16(dP) && is_aligned16(dM);
   const int block = 128;
   const int64_t grid = (batch + block - 1) / block;
-  k_sinkhorn_bwd<T><<<(unsigned)grid, block, 0, st>>>((const T*)M, (const T*)dP, (T*)dM, batch, iters, eps, sz,
-                                                       aligned);
+  {
+    ProfScope ps("k_sinkhorn_bwd", st);
+    k_sinkhorn_bwd<T><<<(unsigned)grid, block, 0, st>>>((const T*)M, (const T*)dP, (T*)dM, batch, iters, eps, sz,
+                                                         aligned);
+  }
   return check_launch("sinkhorn_bwd");
 }
 

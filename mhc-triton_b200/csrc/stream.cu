@@ -10,6 +10,14 @@
 
 namespace mhc {
 
+template <typename T, int V, int N> struct Bundle { RawPack<T, V> p[N]; };
+
+template <typename T, int V>
+__device__ __forceinline__ void unpack(const RawPack<T, V>& r, float (&o)[V]) {
+#pragma unroll
+  for (int e = 0; e < V; ++e) o[e] = raw_get<V>(r, e);
+}
+
 // ------------------------------------------------------------------------------- stream mix
 template <typename T, int V>
 __global__ void __launch_bounds__(256)
@@ -22,28 +30,31 @@ k_stream_mix_fwd(const T* __restrict__ H, const float* __restrict__ Hpre, const 
   for (int n = 0; n < 4; ++n) w[n] = __ldg(Hpre + it.b * 4 + n);
 #pragma unroll
   for (int k = 0; k < 16; ++k) R[k] = __ldg(Hres + it.b * 16 + k);
-  const int64_t D = g.D;
-  const int64_t tok0 = it.b * g.S + it.s0;
-  const T* h = H + tok0 * 4 * D + (int64_t)it.col * V;
-  T* o = Hr + tok0 * 4 * D + (int64_t)it.col * V;
-  T* q = bi + tok0 * D + (int64_t)it.col * V;
-#pragma unroll 2
-  for (int64_t s = it.s0; s < it.s1; ++s, h += 4 * D, o += 4 * D, q += D) {
-    float x[4][V];
+  const int64_t D = g.D, c0 = (int64_t)it.col * V, tok = it.b * g.S;
+  using B4 = Bundle<T, V, 4>;
+  for_tokens_pipelined<B4>(
+      it.s0, it.s1, 1,
+      [&](B4& u, int64_t s) {
+        const T* h = H + (tok + s) * 4 * D + c0;
 #pragma unroll
-    for (int n = 0; n < 4; ++n) PackIO<T, V>::load(h + n * D, x[n]);
-    float y[V];
+        for (int n = 0; n < 4; ++n) u.p[n] = ld_raw<T, V>(h + n * D);
+      },
+      [&](const B4& u, int64_t s) {
+        float x[4][V], y[V];
 #pragma unroll
-    for (int e = 0; e < V; ++e) y[e] = ((w[0] * x[0][e] + w[1] * x[1][e]) + w[2] * x[2][e]) + w[3] * x[3][e];
-    PackIO<T, V>::store(q, y);
+        for (int n = 0; n < 4; ++n) unpack<T, V>(u.p[n], x[n]);
 #pragma unroll
-    for (int n = 0; n < 4; ++n) {
+        for (int e = 0; e < V; ++e) y[e] = ((w[0] * x[0][e] + w[1] * x[1][e]) + w[2] * x[2][e]) + w[3] * x[3][e];
+        PackIO<T, V>::store(bi + (tok + s) * D + c0, y);
+        T* o = Hr + (tok + s) * 4 * D + c0;
 #pragma unroll
-      for (int e = 0; e < V; ++e)
-        y[e] = ((R[4 * n] * x[0][e] + R[4 * n + 1] * x[1][e]) + R[4 * n + 2] * x[2][e]) + R[4 * n + 3] * x[3][e];
-      PackIO<T, V>::store(o + n * D, y);
-    }
-  }
+        for (int n = 0; n < 4; ++n) {
+#pragma unroll
+          for (int e = 0; e < V; ++e)
+            y[e] = ((R[4 * n] * x[0][e] + R[4 * n + 1] * x[1][e]) + R[4 * n + 2] * x[2][e]) + R[4 * n + 3] * x[3][e];
+          PackIO<T, V>::store(o + n * D, y);
+        }
+      });
 }
 
 // ------------------------------------------------------------------------------ add residual
@@ -56,24 +67,28 @@ k_add_residual_fwd(const T* __restrict__ Hr, const T* __restrict__ bo, const flo
   float p[4];
 #pragma unroll
   for (int n = 0; n < 4; ++n) p[n] = __ldg(Hpost + it.b * 4 + n);
-  const int64_t D = g.D;
-  const int64_t tok0 = it.b * g.S + it.s0;
-  const T* r = Hr + tok0 * 4 * D + (int64_t)it.col * V;
-  T* o = Hn + tok0 * 4 * D + (int64_t)it.col * V;
-  const T* q = bo + tok0 * D + (int64_t)it.col * V;
-#pragma unroll 2
-  for (int64_t s = it.s0; s < it.s1; ++s, r += 4 * D, o += 4 * D, q += D) {
-    float x[4][V], y[V];
-    PackIO<T, V>::load(q, y);
+  const int64_t D = g.D, c0 = (int64_t)it.col * V, tok = it.b * g.S;
+  using B5 = Bundle<T, V, 5>;
+  for_tokens_pipelined<B5>(
+      it.s0, it.s1, 1,
+      [&](B5& u, int64_t s) {
+        const T* r = Hr + (tok + s) * 4 * D + c0;
+        u.p[4] = ld_raw<T, V>(bo + (tok + s) * D + c0);
 #pragma unroll
-    for (int n = 0; n < 4; ++n) PackIO<T, V>::load(r + n * D, x[n]);
+        for (int n = 0; n < 4; ++n) u.p[n] = ld_raw<T, V>(r + n * D);
+      },
+      [&](const B5& u, int64_t s) {
+        float y[V], x[V];
+        unpack<T, V>(u.p[4], y);
+        T* o = Hn + (tok + s) * 4 * D + c0;
 #pragma unroll
-    for (int n = 0; n < 4; ++n) {
+        for (int n = 0; n < 4; ++n) {
+          unpack<T, V>(u.p[n], x);
 #pragma unroll
-      for (int e = 0; e < V; ++e) x[n][e] = x[n][e] + p[n] * y[e];
-      PackIO<T, V>::store(o + n * D, x[n]);
-    }
-  }
+          for (int e = 0; e < V; ++e) x[e] = x[e] + p[n] * y[e];
+          PackIO<T, V>::store(o + n * D, x);
+        }
+      });
 }
 
 // d_branch_output[s,d] = sum_n H_post[n] g[s,n,d];  partial dH_post[n] = sum_{s,d} g[s,n,d] bo[s,d].
@@ -89,26 +104,32 @@ k_add_residual_bwd(const T* __restrict__ G, const T* __restrict__ bo, const floa
     float p[4];
 #pragma unroll
     for (int n = 0; n < 4; ++n) p[n] = __ldg(Hpost + it.b * 4 + n);
-    const int64_t D = g.D;
-    const int64_t tok0 = it.b * g.S + it.s0;
-    const T* gp = G + tok0 * 4 * D + (int64_t)it.col * V;
-    const T* q = bo + tok0 * D + (int64_t)it.col * V;
-    T* o = dbo + tok0 * D + (int64_t)it.col * V;
-#pragma unroll 2
-    for (int64_t s = it.s0; s < it.s1; ++s, gp += 4 * D, q += D, o += D) {
-      float x[4][V], y[V], z[V];
-      PackIO<T, V>::load(q, y);
+    const int64_t D = g.D, c0 = (int64_t)it.col * V, tok = it.b * g.S;
+    using B5 = Bundle<T, V, 5>;
+    for_tokens_pipelined<B5>(
+        it.s0, it.s1, 1,
+        [&](B5& u, int64_t s) {
+          const T* gp = G + (tok + s) * 4 * D + c0;
+          u.p[4] = ld_raw<T, V>(bo + (tok + s) * D + c0);
 #pragma unroll
-      for (int n = 0; n < 4; ++n) PackIO<T, V>::load(gp + n * D, x[n]);
+          for (int n = 0; n < 4; ++n) u.p[n] = ld_raw<T, V>(gp + n * D);
+        },
+        [&](const B5& u, int64_t s) {
+          float y[V], z[V], x[V];
+          unpack<T, V>(u.p[4], y);
 #pragma unroll
-      for (int e = 0; e < V; ++e) z[e] = ((p[0] * x[0][e] + p[1] * x[1][e]) + p[2] * x[2][e]) + p[3] * x[3][e];
-      PackIO<T, V>::store(o, z);
+          for (int e = 0; e < V; ++e) z[e] = 0.f;
 #pragma unroll
-      for (int n = 0; n < 4; ++n) {
+          for (int n = 0; n < 4; ++n) {
+            unpack<T, V>(u.p[n], x);
 #pragma unroll
-        for (int e = 0; e < V; ++e) acc[n] = fmaf(x[n][e], y[e], acc[n]);
-      }
-    }
+            for (int e = 0; e < V; ++e) {
+              z[e] = fmaf(p[n], x[e], z[e]);
+              acc[n] = fmaf(x[e], y[e], acc[n]);
+            }
+          }
+          PackIO<T, V>::store(dbo + (tok + s) * D + c0, z);
+        });
   }
   block_reduce_store<4>(acc, part + (it.b * geo_slots_dev(g) + it.slot) * 4, red);
 }
@@ -117,7 +138,7 @@ k_add_residual_bwd(const T* __restrict__ G, const T* __restrict__ bo, const floa
 // MODE 0: dH and partials.  MODE 1: partials only (the apply pass writes dH later).
 // part: [B, slots, 20] = dH_pre[4] then dH_res[4][4] row-major.
 template <typename T, int V, int MODE>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 2)
 k_stream_mix_bwd(const T* __restrict__ dbi, const T* __restrict__ dHr, const T* __restrict__ H,
                  const float* __restrict__ Hpre, const float* __restrict__ Hres, T* __restrict__ dH,
                  float* __restrict__ part, Geo g) {
@@ -134,48 +155,51 @@ k_stream_mix_bwd(const T* __restrict__ dbi, const T* __restrict__ dHr, const T* 
 #pragma unroll
       for (int k = 0; k < 16; ++k) R[k] = __ldg(Hres + it.b * 16 + k);
     }
-    const int64_t D = g.D;
-    const int64_t tok0 = it.b * g.S + it.s0;
-    const int64_t off4 = tok0 * 4 * D + (int64_t)it.col * V;
-    const T* hp = H + off4;
-    const T* rp = dHr + off4;
-    T* op = dH + off4;
-    const T* qp = dbi + tok0 * D + (int64_t)it.col * V;
-    for (int64_t s = it.s0; s < it.s1; ++s, hp += 4 * D, rp += 4 * D, op += 4 * D, qp += D) {
-      float h[4][V], r[4][V], q[V];
-      PackIO<T, V>::load(qp, q);
+    const int64_t D = g.D, c0 = (int64_t)it.col * V, tok = it.b * g.S;
+    using B9 = Bundle<T, V, 9>;  // 0..3 H rows, 4..7 dH_residual rows, 8 d_branch_input
+    for_tokens_pipelined<B9>(
+        it.s0, it.s1, 1,
+        [&](B9& u, int64_t s) {
+          const int64_t o4 = (tok + s) * 4 * D + c0;
+          u.p[8] = ld_raw<T, V>(dbi + (tok + s) * D + c0);
 #pragma unroll
-      for (int n = 0; n < 4; ++n) PackIO<T, V>::load(rp + n * D, r[n]);
+          for (int n = 0; n < 4; ++n) u.p[4 + n] = ld_raw<T, V>(dHr + o4 + n * D);
 #pragma unroll
-      for (int n = 0; n < 4; ++n) PackIO<T, V>::load(hp + n * D, h[n]);
-      if (MODE == 0) {
+          for (int n = 0; n < 4; ++n) u.p[n] = ld_raw<T, V>(H + o4 + n * D);
+        },
+        [&](const B9& u, int64_t s) {
+          float y[4][V];
 #pragma unroll
-        for (int m = 0; m < 4; ++m) {
-          float y[V];
+          for (int e = 0; e < V; ++e) {
+            float h[4], r[4];
+            const float q = raw_get<V>(u.p[8], e);
 #pragma unroll
-          for (int e = 0; e < V; ++e)
-            y[e] = w[m] * q[e] + (((R[m] * r[0][e] + R[4 + m] * r[1][e]) + R[8 + m] * r[2][e]) + R[12 + m] * r[3][e]);
-          PackIO<T, V>::store(op + m * D, y);
-        }
-      }
+            for (int n = 0; n < 4; ++n) { h[n] = raw_get<V>(u.p[n], e); r[n] = raw_get<V>(u.p[4 + n], e); }
+            if (MODE == 0) {
 #pragma unroll
-      for (int n = 0; n < 4; ++n) {
+              for (int m = 0; m < 4; ++m)
+                y[m][e] = w[m] * q + (((R[m] * r[0] + R[4 + m] * r[1]) + R[8 + m] * r[2]) + R[12 + m] * r[3]);
+            }
 #pragma unroll
-        for (int e = 0; e < V; ++e) acc[n] = fmaf(q[e], h[n][e], acc[n]);
+            for (int n = 0; n < 4; ++n) {
+              acc[n] = fmaf(q, h[n], acc[n]);
 #pragma unroll
-        for (int m = 0; m < 4; ++m) {
+              for (int m = 0; m < 4; ++m) acc[4 + 4 * n + m] = fmaf(r[n], h[m], acc[4 + 4 * n + m]);
+            }
+          }
+          if (MODE == 0) {
+            T* op = dH + (tok + s) * 4 * D + c0;
 #pragma unroll
-          for (int e = 0; e < V; ++e) acc[4 + 4 * n + m] = fmaf(r[n][e], h[m][e], acc[4 + 4 * n + m]);
-        }
-      }
-    }
+            for (int m = 0; m < 4; ++m) PackIO<T, V>::store(op + m * D, y[m]);
+          }
+        });
   }
   block_reduce_store<20>(acc, part + (it.b * geo_slots_dev(g) + it.slot) * 20, red);
 }
 
 // dH[s,m,d] = H_pre[m] d_bi[s,d] + sum_n H_res[n,m] dH_residual[s,n,d] + inv_S * gx[m*D + d].
 template <typename T, int V>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 2)
 k_stream_mix_bwd_apply(const T* __restrict__ dbi, const T* __restrict__ dHr, const float* __restrict__ Hpre,
                        const float* __restrict__ Hres, const float* __restrict__ gx, float inv_S,
                        T* __restrict__ dH, Geo g) {
@@ -186,46 +210,48 @@ k_stream_mix_bwd_apply(const T* __restrict__ dbi, const T* __restrict__ dHr, con
   for (int n = 0; n < 4; ++n) w[n] = __ldg(Hpre + it.b * 4 + n);
 #pragma unroll
   for (int k = 0; k < 16; ++k) R[k] = __ldg(Hres + it.b * 16 + k);
-  const int64_t D = g.D;
+  const int64_t D = g.D, c0 = (int64_t)it.col * V, tok = it.b * g.S;
 #pragma unroll
   for (int m = 0; m < 4; ++m) {
 #pragma unroll
-    for (int e = 0; e < V; ++e)
-      c[m][e] = gx ? inv_S * __ldg(gx + it.b * 4 * D + m * D + (int64_t)it.col * V + e) : 0.f;
+    for (int e = 0; e < V; ++e) c[m][e] = gx ? inv_S * __ldg(gx + it.b * 4 * D + m * D + c0 + e) : 0.f;
   }
-  const int64_t tok0 = it.b * g.S + it.s0;
-  const int64_t off4 = tok0 * 4 * D + (int64_t)it.col * V;
-  const T* rp = dHr + off4;
-  T* op = dH + off4;
-  const T* qp = dbi + tok0 * D + (int64_t)it.col * V;
-#pragma unroll 2
-  for (int64_t s = it.s0; s < it.s1; ++s, rp += 4 * D, op += 4 * D, qp += D) {
-    float r[4][V], q[V];
-    PackIO<T, V>::load(qp, q);
+  using B5 = Bundle<T, V, 5>;
+  for_tokens_pipelined<B5>(
+      it.s0, it.s1, 1,
+      [&](B5& u, int64_t s) {
+        const T* rp = dHr + (tok + s) * 4 * D + c0;
+        u.p[4] = ld_raw<T, V>(dbi + (tok + s) * D + c0);
 #pragma unroll
-    for (int n = 0; n < 4; ++n) PackIO<T, V>::load(rp + n * D, r[n]);
+        for (int n = 0; n < 4; ++n) u.p[n] = ld_raw<T, V>(rp + n * D);
+      },
+      [&](const B5& u, int64_t s) {
+        float r[4][V], q[V], y[V];
+        unpack<T, V>(u.p[4], q);
 #pragma unroll
-    for (int m = 0; m < 4; ++m) {
-      float y[V];
+        for (int n = 0; n < 4; ++n) unpack<T, V>(u.p[n], r[n]);
+        T* op = dH + (tok + s) * 4 * D + c0;
 #pragma unroll
-      for (int e = 0; e < V; ++e)
-        y[e] = (w[m] * q[e] + (((R[m] * r[0][e] + R[4 + m] * r[1][e]) + R[8 + m] * r[2][e]) + R[12 + m] * r[3][e])) +
-               c[m][e];
-      PackIO<T, V>::store(op + m * D, y);
-    }
-  }
+        for (int m = 0; m < 4; ++m) {
+#pragma unroll
+          for (int e = 0; e < V; ++e)
+            y[e] = (w[m] * q[e] + (((R[m] * r[0][e] + R[4 + m] * r[1][e]) + R[8 + m] * r[2][e]) + R[12 + m] * r[3][e])) +
+                   c[m][e];
+          PackIO<T, V>::store(op + m * D, y);
+        }
+      });
 }
 
 // --------------------------------------------------------------------------------- mean-pool
 // part[b, chunk, n*D + d] = sum over the chunk's tokens of H[b,s,n,d]  (fp32).
-// blockDim.x = cols * sub: thread (col, j) sums tokens j, j+sub, ... of the chunk; the sub-groups
-// are then added in index order through shared memory.
+// blockDim.x = cols * sub: thread (col, j) sums tokens j, j+sub, ... of the chunk (two tokens in
+// flight); the sub-groups are then added in index order through shared memory.
 template <typename T, int V>
 __global__ void __launch_bounds__(256)
 k_meanpool_partial(const T* __restrict__ H, float* __restrict__ part, Geo g) {
   extern __shared__ float sm[];  // [4*V][sub][cols]
   const Item it = decode_item(g);
-  const int64_t D = g.D;
+  const int64_t D = g.D, c0 = (int64_t)it.col * V, tok = it.b * g.S;
   float acc[4][V];
 #pragma unroll
   for (int n = 0; n < 4; ++n)
@@ -233,18 +259,31 @@ k_meanpool_partial(const T* __restrict__ H, float* __restrict__ part, Geo g) {
     for (int e = 0; e < V; ++e) acc[n][e] = 0.f;
   const bool live = it.col < g.DV;
   if (live) {
-    const T* h = H + ((it.b * g.S + it.s0 + it.sub) * 4) * D + (int64_t)it.col * V;
-    const int64_t step = (int64_t)g.sub * 4 * D;
-#pragma unroll 2
-    for (int64_t s = it.s0 + it.sub; s < it.s1; s += g.sub, h += step) {
-      float x[4][V];
+    using B8 = Bundle<T, V, 8>;  // two tokens per pipeline stage
+    const int64_t step = g.sub;
+    for_tokens_pipelined<B8>(
+        it.s0 + it.sub, it.s1, 2 * step,
+        [&](B8& u, int64_t s) {
+          const T* h = H + (tok + s) * 4 * D + c0;
 #pragma unroll
-      for (int n = 0; n < 4; ++n) PackIO<T, V>::load(h + n * D, x[n]);
+          for (int n = 0; n < 4; ++n) u.p[n] = ld_raw<T, V>(h + n * D);
+          if (s + step < it.s1) {
 #pragma unroll
-      for (int n = 0; n < 4; ++n)
+            for (int n = 0; n < 4; ++n) u.p[4 + n] = ld_raw<T, V>(h + step * 4 * D + n * D);
+          }
+        },
+        [&](const B8& u, int64_t s) {
 #pragma unroll
-        for (int e = 0; e < V; ++e) acc[n][e] += x[n][e];
-    }
+          for (int n = 0; n < 4; ++n)
+#pragma unroll
+            for (int e = 0; e < V; ++e) acc[n][e] += raw_get<V>(u.p[n], e);
+          if (s + step < it.s1) {
+#pragma unroll
+            for (int n = 0; n < 4; ++n)
+#pragma unroll
+              for (int e = 0; e < V; ++e) acc[n][e] += raw_get<V>(u.p[4 + n], e);
+          }
+        });
   }
   const int c = threadIdx.x % g.cols;
   if (g.sub > 1) {
@@ -265,7 +304,7 @@ k_meanpool_partial(const T* __restrict__ H, float* __restrict__ part, Geo g) {
     }
   }
   if (live && it.sub == 0) {
-    float* o = part + (it.b * g.nchunk + it.chunk) * 4 * D + (int64_t)it.col * V;
+    float* o = part + (it.b * g.nchunk + it.chunk) * 4 * D + c0;
 #pragma unroll
     for (int n = 0; n < 4; ++n)
 #pragma unroll
@@ -286,24 +325,31 @@ k_meanpool_finish(const float* __restrict__ part, float* __restrict__ x, int64_t
   x[i] = (float)(s * scale);
 }
 
-// out[b, j] = sum_p part[b, p, j] for j < W, slots added in index order in fp64 (four interleaved
-// chains, combined in a fixed order).  Columns [0, W0) go to out0, the rest to out1.
-__global__ void k_reduce_partials(const float* __restrict__ part, int64_t slots, int W, int W0,
-                                  float* __restrict__ out0, float* __restrict__ out1) {
-  const int j = threadIdx.x;
-  if (j >= W) return;
+// out[b, j] = sum_p part[b, p, j] for j < W (W <= 20).  One CTA of 256 threads per batch element:
+// thread t adds slots t, t+256, ... in fp64, a xor-shuffle tree adds the lanes of each warp, and
+// thread j adds the 8 warp sums in index order.  Columns [0, W0) go to out0, the rest to out1.
+__global__ void __launch_bounds__(256)
+k_reduce_partials(const float* __restrict__ part, int64_t slots, int W, int W0, float* __restrict__ out0,
+                  float* __restrict__ out1) {
+  __shared__ double sm[8][20];
   const int64_t b = blockIdx.x;
-  const float* p = part + b * slots * W + j;
-  double a[4] = {0.0, 0.0, 0.0, 0.0};
-  int64_t s = 0;
-  for (; s + 4 <= slots; s += 4) {
-#pragma unroll
-    for (int u = 0; u < 4; ++u) a[u] += (double)__ldg(p + (s + u) * W);
+  const float* p = part + b * slots * W;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int j = 0; j < W; ++j) {
+    double a = 0.0;
+    for (int64_t s = threadIdx.x; s < slots; s += 256) a += (double)__ldg(p + s * W + j);
+    a = warp_sum_f64(a);
+    if (lane == 0) sm[warp][j] = a;
   }
-  for (int u = 0; s < slots; ++s, ++u) a[u] += (double)__ldg(p + s * W);
-  const float v = (float)((a[0] + a[1]) + (a[2] + a[3]));
-  if (j < W0) out0[b * W0 + j] = v;
-  else out1[b * (W - W0) + (j - W0)] = v;
+  __syncthreads();
+  const int j = threadIdx.x;
+  if (j < W) {
+    double t = 0.0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) t += sm[w][j];
+    if (j < W0) out0[b * W0 + j] = (float)t;
+    else out1[b * (W - W0) + (j - W0)] = (float)t;
+  }
 }
 
 // -------------------------------------------------------------------------------- host side
@@ -363,21 +409,104 @@ static int check_grid(const char* what, int64_t items) {
     }                                                                                       \
   } while (0)
 
+// Launch sequences shared by the single-op and the fused entry points.  Arguments are validated by
+// the callers; these pick the pack width, build the geometry and launch.
+int stream_mix_fwd_impl(const void* H, const float* H_pre, const float* H_res, void* bi, void* Hr, int64_t B, int64_t S,
+                        int64_t D, int dtype, cudaStream_t st) {
+  const int vec = pick_vec(dtype, D, {H, bi, Hr});
+  const Geo g = make_geo(S, D, vec, false);
+  const int64_t items = B * geo_slots(g);
+  if (int e = check_grid("stream_mix_fwd", items)) return e;
+  {
+    ProfScope ps("k_stream_mix_fwd", st);
+    MHC_DISPATCH(dtype, vec, (k_stream_mix_fwd<T, V><<<(unsigned)items, geo_block(g), 0, st>>>(
+                                 (const T*)H, H_pre, H_res, (T*)bi, (T*)Hr, g)));
+  }
+  return check_launch("stream_mix_fwd");
+}
+
+int64_t meanpool_scratch_floats(int64_t B, int64_t S, int64_t D) { return B * make_geo(S, D, 1, true).nchunk * 4 * D; }
+int64_t mix_bwd_scratch_floats(int64_t B, int64_t S, int64_t D) { return B * geo_slots(make_geo(S, D, 1, false)) * 20; }
+
+int meanpool_partial_impl(const void* H, float* part, int64_t B, int64_t S, int64_t D, int dtype, cudaStream_t st,
+                          int* nchunk) {
+  const int vec = pick_vec(dtype, D, {H});
+  const Geo g = make_geo(S, D, vec, true);
+  const int64_t items = B * geo_slots(g);
+  if (int e = check_grid("meanpool_fwd", items)) return e;
+  const size_t smem = (size_t)4 * vec * geo_block(g) * sizeof(float);
+  {
+    ProfScope ps("k_meanpool_partial", st);
+    MHC_DISPATCH(dtype, vec, (k_meanpool_partial<T, V><<<(unsigned)items, geo_block(g), smem, st>>>((const T*)H, part, g)));
+  }
+  *nchunk = g.nchunk;
+  return check_launch("meanpool_fwd");
+}
+
+// mode 0: dH + partials; mode 1: partials only.
+int mix_bwd_partials_impl(int mode, const void* dbi, const void* dHr, const void* H, const float* H_pre,
+                          const float* H_res, void* dH, float* part, int64_t B, int64_t S, int64_t D, int dtype,
+                          cudaStream_t st, int64_t* slots) {
+  const int vec = pick_vec(dtype, D, {dbi, dHr, H, dH});
+  const Geo g = make_geo(S, D, vec, false);
+  *slots = geo_slots(g);
+  const int64_t items = B * *slots;
+  if (int e = check_grid("stream_mix_bwd", items)) return e;
+  if (mode == 0) {
+    ProfScope ps("k_stream_mix_bwd_full", st);
+    MHC_DISPATCH(dtype, vec, (k_stream_mix_bwd<T, V, 0><<<(unsigned)items, geo_block(g), 0, st>>>(
+                                 (const T*)dbi, (const T*)dHr, (const T*)H, H_pre, H_res, (T*)dH, part, g)));
+  } else {
+    ProfScope ps("k_stream_mix_bwd_reduce", st);
+    MHC_DISPATCH(dtype, vec, (k_stream_mix_bwd<T, V, 1><<<(unsigned)items, geo_block(g), 0, st>>>(
+                                 (const T*)dbi, (const T*)dHr, (const T*)H, nullptr, nullptr, nullptr, part, g)));
+  }
+  return check_launch("stream_mix_bwd");
+}
+
+int mix_bwd_apply_impl(const void* dbi, const void* dHr, const float* H_pre, const float* H_res, const float* gx,
+                       float inv_S, void* dH, int64_t B, int64_t S, int64_t D, int dtype, cudaStream_t st) {
+  const int vec = pick_vec(dtype, D, {dbi, dHr, dH});
+  const Geo g = make_geo(S, D, vec, false);
+  const int64_t items = B * geo_slots(g);
+  if (int e = check_grid("stream_mix_bwd_apply", items)) return e;
+  {
+    ProfScope ps("k_stream_mix_bwd_apply", st);
+    MHC_DISPATCH(dtype, vec, (k_stream_mix_bwd_apply<T, V><<<(unsigned)items, geo_block(g), 0, st>>>(
+                                 (const T*)dbi, (const T*)dHr, H_pre, H_res, gx, inv_S, (T*)dH, g)));
+  }
+  return check_launch("stream_mix_bwd_apply");
+}
+
+int check_bsd_pub(const char* what, int64_t B, int64_t S, int64_t D, int dtype) { return check_bsd(what, B, S, D, dtype); }
+
+static int launch_reduce(const float* part, int64_t B, int64_t slots, int W, int W0, float* out0, float* out1,
+                         cudaStream_t st, const char* what) {
+  {
+    ProfScope ps("k_reduce_partials", st);
+    k_reduce_partials<<<(unsigned)B, 256, 0, st>>>(part, slots, W, W0, out0, out1);
+  }
+  return check_launch(what);
+}
+
 }  // namespace mhc
 
 using namespace mhc;
 
 extern "C" int64_t mhc_scratch_bytes(int op, int64_t B, int64_t S, int64_t D, int dtype) {
   if (B < 0 || S < 0 || D < 0) return -1;
-  // Sized for the scalar path (vec = 1), which has the most column groups.
+  (void)dtype;
+  const int64_t f = (int64_t)sizeof(float);
+  // Sized for the scalar path (pack width 1), which has the most column groups.
   switch (op) {
-    case MHC_OP_ADD_RESIDUAL_BWD: return B * geo_slots(make_geo(S, D, 1, false)) * 4 * (int64_t)sizeof(float);
-    case MHC_OP_STREAM_MIX_BWD: return B * geo_slots(make_geo(S, D, 1, false)) * 20 * (int64_t)sizeof(float);
-    case MHC_OP_MEANPOOL_FWD: return B * make_geo(S, D, 1, true).nchunk * 4 * D * (int64_t)sizeof(float);
+    case MHC_OP_ADD_RESIDUAL_BWD: return B * geo_slots(make_geo(S, D, 1, false)) * 4 * f;
+    case MHC_OP_STREAM_MIX_BWD: return mix_bwd_scratch_floats(B, S, D) * f;
+    case MHC_OP_MEANPOOL_FWD: return meanpool_scratch_floats(B, S, D) * f;
     case MHC_OP_DYNAMIC_WEIGHTS_FWD: return weights_fwd_scratch_bytes(B, 4 * D);
     case MHC_OP_DYNAMIC_WEIGHTS_BWD: return weights_bwd_scratch_bytes(B, 4 * D);
+    case MHC_OP_HC_MIX_FWD: return meanpool_scratch_floats(B, S, D) * f + weights_fwd_scratch_bytes(B, 4 * D);
+    case MHC_OP_HC_MIX_BWD: return mix_bwd_scratch_floats(B, S, D) * f + weights_bwd_scratch_bytes(B, 4 * D);
   }
-  (void)dtype;
   return -1;
 }
 
@@ -387,14 +516,7 @@ extern "C" int mhc_stream_mix_fwd(const void* H, const float* H_pre, const float
   if (int e = check_bsd("stream_mix_fwd", B, S, D, dtype)) return e;
   if (B == 0 || S == 0 || D == 0) return MHC_OK;
   if (!H || !H_pre || !H_res || !branch_input || !H_residual) return fail(MHC_ERR_NULL_POINTER, "stream_mix_fwd: null pointer");
-  const int vec = pick_vec(dtype, D, {H, branch_input, H_residual});
-  const Geo g = make_geo(S, D, vec, false);
-  const int64_t items = B * geo_slots(g);
-  if (int e = check_grid("stream_mix_fwd", items)) return e;
-  cudaStream_t st = (cudaStream_t)stream;
-  MHC_DISPATCH(dtype, vec, (k_stream_mix_fwd<T, V><<<(unsigned)items, geo_block(g), 0, st>>>(
-                               (const T*)H, H_pre, H_res, (T*)branch_input, (T*)H_residual, g)));
-  return check_launch("stream_mix_fwd");
+  return stream_mix_fwd_impl(H, H_pre, H_res, branch_input, H_residual, B, S, D, dtype, (cudaStream_t)stream);
 }
 
 extern "C" int mhc_add_residual_fwd(const void* H_residual, const void* branch_output, const float* H_post,
@@ -407,15 +529,12 @@ extern "C" int mhc_add_residual_fwd(const void* H_residual, const void* branch_o
   const int64_t items = B * geo_slots(g);
   if (int e = check_grid("add_residual_fwd", items)) return e;
   cudaStream_t st = (cudaStream_t)stream;
-  MHC_DISPATCH(dtype, vec, (k_add_residual_fwd<T, V><<<(unsigned)items, geo_block(g), 0, st>>>(
-                               (const T*)H_residual, (const T*)branch_output, H_post, (T*)H_new, g)));
+  {
+    ProfScope ps("k_add_residual_fwd", st);
+    MHC_DISPATCH(dtype, vec, (k_add_residual_fwd<T, V><<<(unsigned)items, geo_block(g), 0, st>>>(
+                                 (const T*)H_residual, (const T*)branch_output, H_post, (T*)H_new, g)));
+  }
   return check_launch("add_residual_fwd");
-}
-
-static int launch_reduce(const float* part, int64_t B, int64_t slots, int W, int W0, float* out0, float* out1,
-                         cudaStream_t st, const char* what) {
-  k_reduce_partials<<<(unsigned)B, 32, 0, st>>>(part, slots, W, W0, out0, out1);
-  return check_launch(what);
 }
 
 extern "C" int mhc_add_residual_bwd(const void* dH_new, const void* branch_output, const float* H_post,
@@ -438,9 +557,12 @@ extern "C" int mhc_add_residual_bwd(const void* dH_new, const void* branch_outpu
   if (scratch_bytes < items * 4 * (int64_t)sizeof(float))
     return fail(MHC_ERR_SCRATCH_TOO_SMALL, "add_residual_bwd: scratch %lld < %lld bytes", (long long)scratch_bytes,
                 (long long)(items * 4 * sizeof(float)));
-  MHC_DISPATCH(dtype, vec, (k_add_residual_bwd<T, V><<<(unsigned)items, geo_block(g), 0, st>>>(
-                               (const T*)dH_new, (const T*)branch_output, H_post, (T*)d_branch_output,
-                               (float*)scratch, g)));
+  {
+    ProfScope ps("k_add_residual_bwd", st);
+    MHC_DISPATCH(dtype, vec, (k_add_residual_bwd<T, V><<<(unsigned)items, geo_block(g), 0, st>>>(
+                                 (const T*)dH_new, (const T*)branch_output, H_post, (T*)d_branch_output,
+                                 (float*)scratch, g)));
+  }
   if (int e = check_launch("add_residual_bwd")) return e;
   return launch_reduce((const float*)scratch, B, slots, 4, 4, dH_post, nullptr, st, "add_residual_bwd(reduce)");
 }
@@ -460,22 +582,12 @@ static int mix_bwd_common(const char* what, int mode, const void* dbi, const voi
   }
   if (!dbi || !dHr || !H || !scratch || (mode == 0 && (!dH || !H_pre || !H_res)))
     return fail(MHC_ERR_NULL_POINTER, "%s: null pointer", what);
-  const int vec = pick_vec(dtype, D, {dbi, dHr, H, dH});
-  const Geo g = make_geo(S, D, vec, false);
-  const int64_t slots = geo_slots(g), items = B * slots;
-  if (int e = check_grid(what, items)) return e;
-  if (scratch_bytes < items * 20 * (int64_t)sizeof(float))
+  if (scratch_bytes < mix_bwd_scratch_floats(B, S, D) * (int64_t)sizeof(float))
     return fail(MHC_ERR_SCRATCH_TOO_SMALL, "%s: scratch %lld < %lld bytes", what, (long long)scratch_bytes,
-                (long long)(items * 20 * sizeof(float)));
-  if (mode == 0) {
-    MHC_DISPATCH(dtype, vec, (k_stream_mix_bwd<T, V, 0><<<(unsigned)items, geo_block(g), 0, st>>>(
-                                 (const T*)dbi, (const T*)dHr, (const T*)H, H_pre, H_res, (T*)dH, (float*)scratch, g)));
-  } else {
-    MHC_DISPATCH(dtype, vec, (k_stream_mix_bwd<T, V, 1><<<(unsigned)items, geo_block(g), 0, st>>>(
-                                 (const T*)dbi, (const T*)dHr, (const T*)H, nullptr, nullptr, nullptr,
-                                 (float*)scratch, g)));
-  }
-  if (int e = check_launch(what)) return e;
+                (long long)(mix_bwd_scratch_floats(B, S, D) * sizeof(float)));
+  int64_t slots = 0;
+  if (int e = mix_bwd_partials_impl(mode, dbi, dHr, H, H_pre, H_res, dH, (float*)scratch, B, S, D, dtype, st, &slots))
+    return e;
   return launch_reduce((const float*)scratch, B, slots, 20, 4, dH_pre, dH_res, st, what);
 }
 
@@ -501,15 +613,8 @@ extern "C" int mhc_stream_mix_bwd_apply(const void* d_branch_input, const void* 
   if (B == 0 || S == 0 || D == 0) return MHC_OK;
   if (!d_branch_input || !dH_residual || !H_pre || !H_res || !dH)
     return fail(MHC_ERR_NULL_POINTER, "stream_mix_bwd_apply: null pointer");
-  const int vec = pick_vec(dtype, D, {d_branch_input, dH_residual, dH});
-  const Geo g = make_geo(S, D, vec, false);
-  const int64_t items = B * geo_slots(g);
-  if (int e = check_grid("stream_mix_bwd_apply", items)) return e;
-  cudaStream_t st = (cudaStream_t)stream;
-  MHC_DISPATCH(dtype, vec, (k_stream_mix_bwd_apply<T, V><<<(unsigned)items, geo_block(g), 0, st>>>(
-                               (const T*)d_branch_input, (const T*)dH_residual, H_pre, H_res, grad_x, inv_S,
-                               (T*)dH, g)));
-  return check_launch("stream_mix_bwd_apply");
+  return mix_bwd_apply_impl(d_branch_input, dH_residual, H_pre, H_res, grad_x, inv_S, dH, B, S, D, dtype,
+                            (cudaStream_t)stream);
 }
 
 extern "C" int mhc_meanpool_fwd(const void* H, float* x, void* scratch, int64_t scratch_bytes, int64_t B, int64_t S,
@@ -518,20 +623,17 @@ extern "C" int mhc_meanpool_fwd(const void* H, float* x, void* scratch, int64_t 
   if (B == 0 || D == 0) return MHC_OK;
   if (S == 0) return fail(MHC_ERR_BAD_SHAPE, "meanpool_fwd: empty sequence");
   if (!H || !x || !scratch) return fail(MHC_ERR_NULL_POINTER, "meanpool_fwd: null pointer");
-  const int vec = pick_vec(dtype, D, {H});
-  const Geo g = make_geo(S, D, vec, true);
-  const int64_t items = B * geo_slots(g);
-  if (int e = check_grid("meanpool_fwd", items)) return e;
-  const int64_t need = B * g.nchunk * 4 * D * (int64_t)sizeof(float);
+  const int64_t need = meanpool_scratch_floats(B, S, D) * (int64_t)sizeof(float);
   if (scratch_bytes < need)
     return fail(MHC_ERR_SCRATCH_TOO_SMALL, "meanpool_fwd: scratch %lld < %lld bytes", (long long)scratch_bytes, (long long)need);
   cudaStream_t st = (cudaStream_t)stream;
-  const size_t smem = (size_t)4 * vec * geo_block(g) * sizeof(float);
-  MHC_DISPATCH(dtype, vec, (k_meanpool_partial<T, V><<<(unsigned)items, geo_block(g), smem, st>>>(
-                               (const T*)H, (float*)scratch, g)));
-  if (int e = check_launch("meanpool_fwd")) return e;
+  int nchunk = 0;
+  if (int e = meanpool_partial_impl(H, (float*)scratch, B, S, D, dtype, st, &nchunk)) return e;
   const int64_t total = B * 4 * D;
-  k_meanpool_finish<<<(unsigned)((total + 255) / 256), 256, 0, st>>>((const float*)scratch, x, 4 * D, g.nchunk,
-                                                                      1.0 / (double)S, total);
+  {
+    ProfScope ps("k_meanpool_finish", st);
+    k_meanpool_finish<<<(unsigned)((total + 255) / 256), 256, 0, st>>>((const float*)scratch, x, 4 * D, nchunk,
+                                                                        1.0 / (double)S, total);
+  }
   return check_launch("meanpool_fwd(finish)");
 }

@@ -42,9 +42,12 @@ __device__ __forceinline__ void load_phi_row(const float* __restrict__ phi, int6
 }
 
 // part[row, slice, 0..23] = sum over the slice's k of x[row,k] phi[k,:];  part[row, slice, 24] = sum x^2.
+// x[row,k] = scale * sum_{c < nsrc} xsrc[(row*nsrc + c)*K + k]: with nsrc = 1, scale = 1 this is a plain
+// read of x; with the mean-pool partials as xsrc it finishes the pooling (chunks added in index
+// order, fp64) and writes the pooled state to x_out for the backward.
 __global__ void __launch_bounds__(256)
-k_dw_project(const float* __restrict__ x, const float* __restrict__ phi, float* __restrict__ part, int64_t K,
-             int ks, bool phi_aligned) {
+k_dw_project(const float* __restrict__ xsrc, int nsrc, float scale, float* __restrict__ x_out,
+             const float* __restrict__ phi, float* __restrict__ part, int64_t K, int ks, bool phi_aligned) {
   __shared__ float red[32 * kProjW];
   const int64_t row = blockIdx.x / ks;
   const int slice = (int)(blockIdx.x % ks);
@@ -53,9 +56,17 @@ k_dw_project(const float* __restrict__ x, const float* __restrict__ phi, float* 
   float acc[kProjW];
 #pragma unroll
   for (int i = 0; i < kProjW; ++i) acc[i] = 0.f;
-  const float* xr = x + row * K;
+  const float* xr = xsrc + row * nsrc * K;
   for (int64_t k = k0 + threadIdx.x; k < k1; k += blockDim.x) {
-    const float xv = __ldg(xr + k);
+    float xv;
+    if (nsrc == 1) {
+      xv = __ldg(xr + k) * scale;
+    } else {
+      double t = 0.0;
+      for (int c = 0; c < nsrc; ++c) t += (double)__ldg(xr + (int64_t)c * K + k);
+      xv = (float)(t * (double)scale);
+    }
+    if (x_out) x_out[row * K + k] = xv;
     float p[24];
     load_phi_row(phi, k, phi_aligned, p);
 #pragma unroll
@@ -65,6 +76,10 @@ k_dw_project(const float* __restrict__ x, const float* __restrict__ phi, float* 
   block_reduce_store<kProjW>(acc, part + (row * ks + slice) * kProjW, red);
 }
 
+__device__ __forceinline__ float bias_at(const BiasPtrs& b, int j) {
+  return j < 4 ? __ldg(b.pre + j) : (j < 8 ? __ldg(b.post + (j - 4)) : __ldg(b.res + (j - 8)));
+}
+
 __device__ __forceinline__ float group_alpha(int j, float a_pre, float a_post, float a_res) {
   return j < 4 ? a_pre : (j < 8 ? a_post : a_res);
 }
@@ -72,7 +87,7 @@ __device__ __forceinline__ float group_alpha(int j, float a_pre, float a_post, f
 // One warp per row: lanes 0..24 add the slices (fp64, index order); lanes 0..7 do the sigmoids;
 // lane 8 runs the Sinkhorn projection in registers.
 __global__ void __launch_bounds__(32)
-k_dw_finish(const float* __restrict__ part, const float* __restrict__ bias, const float* __restrict__ alpha_pre,
+k_dw_finish(const float* __restrict__ part, BiasPtrs bias, const float* __restrict__ alpha_pre,
             const float* __restrict__ alpha_post, const float* __restrict__ alpha_res, float* __restrict__ H_pre,
             float* __restrict__ H_post, float* __restrict__ H_res, float* __restrict__ saved, int64_t K, int ks,
             int iters, float eps) {
@@ -91,7 +106,7 @@ k_dw_finish(const float* __restrict__ part, const float* __restrict__ bias, cons
   const float a_pre = __ldg(alpha_pre), a_post = __ldg(alpha_post), a_res = __ldg(alpha_res);
   float sc = 0.f;
   if (lane < 24) {
-    sc = (inv_rms * group_alpha(lane, a_pre, a_post, a_res)) * tot + __ldg(bias + lane);
+    sc = (inv_rms * group_alpha(lane, a_pre, a_post, a_res)) * tot + bias_at(bias, lane);
     s_sc[lane] = sc;
     if (saved) saved[row * kSavedStride + lane] = tot;
   }
@@ -119,30 +134,58 @@ k_dw_finish(const float* __restrict__ part, const float* __restrict__ bias, cons
 // Per row: gradients of the 24 pre-activation values (ds), of the raw projections (d_raw), the
 // coefficient of x in grad_x that comes from the RMS norm, and this row's share of grad_alpha.
 //   buf[row, 0..23] ds   buf[row, 24..47] d_raw   buf[row, 48] coef   buf[row, 49..51] ga(pre,post,res)
-// Lanes 0..7 handle the sigmoid outputs; lane 8 runs the Sinkhorn reverse sweep (states of all
+// One CTA of 256 threads per row.  If part20 is given, dH_pre / dH_res are first summed from the
+// [slots, 20] per-CTA partials of the stream-mix reduction pass (fp64, fixed order) and also
+// written to dH_pre / dH_res; otherwise they are read from there.  Then warp 0 works alone:
+// lanes 0..7 handle the sigmoid outputs, lane 8 runs the Sinkhorn reverse sweep (states of all
 // iterations kept in shared memory when iters <= kMaxStoredIters, else recomputed per step).
-__global__ void __launch_bounds__(32)
-k_dw_bwd_rows(const float* __restrict__ saved, const float* __restrict__ bias, const float* __restrict__ alpha_pre,
+__global__ void __launch_bounds__(256)
+k_dw_bwd_rows(const float* __restrict__ saved, BiasPtrs bias, const float* __restrict__ alpha_pre,
               const float* __restrict__ alpha_post, const float* __restrict__ alpha_res,
-              const float* __restrict__ dH_pre, const float* __restrict__ dH_post, const float* __restrict__ dH_res,
-              float* __restrict__ buf, int64_t K, int iters, float eps, float sign_at_zero) {
-  __shared__ float s_sc[24], s_ds[24];
+              const float* __restrict__ part20, int64_t slots, float* __restrict__ dH_pre,
+              const float* __restrict__ dH_post, float* __restrict__ dH_res, float* __restrict__ buf, int64_t K,
+              int iters, float eps, float sign_at_zero) {
+  __shared__ float s_sc[24], s_ds[24], s_up[20];
+  __shared__ double s_red[8][20];
   __shared__ float s_state[kMaxStoredIters][40];  // r[4] c[4] mr[16] m_out[16]
   const int64_t row = blockIdx.x;
-  const int lane = threadIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (part20) {
+    const float* p = part20 + row * slots * 20;
+    for (int j = 0; j < 20; ++j) {
+      double a = 0.0;
+      for (int64_t s = threadIdx.x; s < slots; s += 256) a += (double)__ldg(p + s * 20 + j);
+      a = warp_sum_f64(a);
+      if (lane == 0) s_red[warp][j] = a;
+    }
+    __syncthreads();
+    if (threadIdx.x < 20) {
+      double t = 0.0;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) t += s_red[w][threadIdx.x];
+      const float v = (float)t;
+      s_up[threadIdx.x] = v;
+      if (threadIdx.x < 4) dH_pre[row * 4 + threadIdx.x] = v;
+      else dH_res[row * 16 + threadIdx.x - 4] = v;
+    }
+  } else if (threadIdx.x < 20) {
+    s_up[threadIdx.x] = threadIdx.x < 4 ? dH_pre[row * 4 + threadIdx.x] : dH_res[row * 16 + threadIdx.x - 4];
+  }
+  __syncthreads();
+  if (warp != 0) return;
   const float inv_rms = __ldg(saved + row * kSavedStride + 25);
   const float a_pre = __ldg(alpha_pre), a_post = __ldg(alpha_post), a_res = __ldg(alpha_res);
   const float alpha = group_alpha(lane, a_pre, a_post, a_res);
   float raw = 0.f, sc = 0.f;
   if (lane < 24) {
     raw = __ldg(saved + row * kSavedStride + lane);
-    sc = (inv_rms * alpha) * raw + __ldg(bias + lane);
+    sc = (inv_rms * alpha) * raw + bias_at(bias, lane);
     s_sc[lane] = sc;
   }
   __syncwarp();
   const float sg = sigmoidf_(sc);
   float g = 0.f;
-  if (lane < 4) g = __ldg(dH_pre + row * 4 + lane);
+  if (lane < 4) g = s_up[lane];
   else if (lane < 8) g = __ldg(dH_post + row * 4 + lane - 4);
   // pre-mix: H_pre = sg / (sum + eps);  d sg = (g - <g, H_pre>) / (sum + eps)
   const float s0 = __shfl_sync(0xffffffffu, sg, 0), s1 = __shfl_sync(0xffffffffu, sg, 1),
@@ -160,7 +203,7 @@ k_dw_bwd_rows(const float* __restrict__ saved, const float* __restrict__ bias, c
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
       m0[i] = s_sc[8 + i];
-      d[i] = __ldg(dH_res + row * 16 + i);
+      d[i] = s_up[4 + i];
     }
     if (iters <= kMaxStoredIters) {
       float m[16];
@@ -292,6 +335,50 @@ k_dw_bwd_main(const float* __restrict__ x, const float* __restrict__ phi, const 
   }
 }
 
+// ------------------------------------------------------------------------------ host side
+int weights_fwd_impl(const float* xsrc, int nsrc, float scale, float* x_out, const float* phi, BiasPtrs bias,
+                     const float* alpha_pre, const float* alpha_post, const float* alpha_res, float* H_pre,
+                     float* H_post, float* H_res, float* saved, float* part, int64_t batch, int64_t K, int iters,
+                     float eps, cudaStream_t st) {
+  const int ks = k_slices(K);
+  if (batch * ks > kMaxGridItems) return fail(MHC_ERR_BAD_SHAPE, "dynamic_weights_fwd: batch too large");
+  {
+    ProfScope ps("k_dw_project", st);
+    k_dw_project<<<(unsigned)(batch * ks), 256, 0, st>>>(xsrc, nsrc, scale, x_out, phi, part, K, ks, is_aligned16(phi));
+  }
+  if (int e = check_launch("dynamic_weights_fwd(project)")) return e;
+  {
+    ProfScope ps("k_dw_finish", st);
+    k_dw_finish<<<(unsigned)batch, 32, 0, st>>>(part, bias, alpha_pre, alpha_post, alpha_res, H_pre, H_post, H_res,
+                                                saved, K, ks, iters, eps);
+  }
+  return check_launch("dynamic_weights_fwd(finish)");
+}
+
+int weights_bwd_impl(const float* x, const float* phi, BiasPtrs bias, const float* alpha_pre, const float* alpha_post,
+                     const float* alpha_res, const float* saved, const float* part20, int64_t slots, float* dH_pre,
+                     const float* dH_post, float* dH_res, float* grad_x, float* grad_phi, float* grad_bias,
+                     float* grad_alpha, float* buf, int64_t batch, int64_t K, int iters, float eps,
+                     int abs_grad_at_zero, int accumulate_params, cudaStream_t st) {
+  if (batch > kMaxGridItems) return fail(MHC_ERR_BAD_SHAPE, "dynamic_weights_bwd: batch too large");
+  if (batch) {
+    {
+      ProfScope ps("k_dw_bwd_rows", st);
+      k_dw_bwd_rows<<<(unsigned)batch, 256, 0, st>>>(saved, bias, alpha_pre, alpha_post, alpha_res, part20, slots,
+                                                     dH_pre, dH_post, dH_res, buf, K, iters, eps,
+                                                     abs_grad_at_zero == MHC_ABS0_PLUS_ONE ? 1.f : 0.f);
+    }
+    if (int e = check_launch("dynamic_weights_bwd(rows)")) return e;
+  }
+  const int64_t kblocks = (K + 255) / 256;
+  {
+    ProfScope ps("k_dw_bwd_main", st);
+    k_dw_bwd_main<<<(unsigned)(kblocks + 1), 256, 0, st>>>(x, phi, buf, grad_x, grad_phi, grad_bias, grad_alpha, batch, K,
+                                                           is_aligned16(phi), is_aligned16(grad_phi), accumulate_params);
+  }
+  return check_launch("dynamic_weights_bwd(main)");
+}
+
 }  // namespace mhc
 
 using namespace mhc;
@@ -305,17 +392,11 @@ extern "C" int mhc_dynamic_weights_fwd(const float* x, const float* phi, const f
   if (batch == 0) return MHC_OK;
   if (!x || !phi || !bias || !alpha_pre || !alpha_post || !alpha_res || !H_pre || !H_post || !H_res || !scratch)
     return fail(MHC_ERR_NULL_POINTER, "dynamic_weights_fwd: null pointer");
-  const int ks = k_slices(K);
-  if (batch * ks > kMaxGridItems) return fail(MHC_ERR_BAD_SHAPE, "dynamic_weights_fwd: batch too large");
   if (scratch_bytes < weights_fwd_scratch_bytes(batch, K))
     return fail(MHC_ERR_SCRATCH_TOO_SMALL, "dynamic_weights_fwd: scratch %lld < %lld bytes", (long long)scratch_bytes,
                 (long long)weights_fwd_scratch_bytes(batch, K));
-  cudaStream_t st = (cudaStream_t)stream;
-  k_dw_project<<<(unsigned)(batch * ks), 256, 0, st>>>(x, phi, (float*)scratch, K, ks, is_aligned16(phi));
-  if (int e = check_launch("dynamic_weights_fwd(project)")) return e;
-  k_dw_finish<<<(unsigned)batch, 32, 0, st>>>((const float*)scratch, bias, alpha_pre, alpha_post, alpha_res, H_pre,
-                                              H_post, H_res, saved, K, ks, iters, eps);
-  return check_launch("dynamic_weights_fwd(finish)");
+  return weights_fwd_impl(x, 1, 1.f, nullptr, phi, BiasPtrs{bias, bias + 4, bias + 8}, alpha_pre, alpha_post, alpha_res,
+                          H_pre, H_post, H_res, saved, (float*)scratch, batch, K, iters, eps, (cudaStream_t)stream);
 }
 
 extern "C" int mhc_dynamic_weights_bwd(const float* x, const float* phi, const float* bias, const float* alpha_pre,
@@ -333,20 +414,11 @@ extern "C" int mhc_dynamic_weights_bwd(const float* x, const float* phi, const f
     return fail(MHC_ERR_NULL_POINTER, "dynamic_weights_bwd: null pointer");
   if (batch && (!saved || !dH_pre || !dH_post || !dH_res || !grad_x || !scratch))
     return fail(MHC_ERR_NULL_POINTER, "dynamic_weights_bwd: null pointer");
-  if (batch > kMaxGridItems) return fail(MHC_ERR_BAD_SHAPE, "dynamic_weights_bwd: batch too large");
   if (scratch_bytes < weights_bwd_scratch_bytes(batch, K))
     return fail(MHC_ERR_SCRATCH_TOO_SMALL, "dynamic_weights_bwd: scratch %lld < %lld bytes", (long long)scratch_bytes,
                 (long long)weights_bwd_scratch_bytes(batch, K));
-  cudaStream_t st = (cudaStream_t)stream;
-  if (batch) {
-    k_dw_bwd_rows<<<(unsigned)batch, 32, 0, st>>>(saved, bias, alpha_pre, alpha_post, alpha_res, dH_pre, dH_post,
-                                                  dH_res, (float*)scratch, K, iters, eps,
-                                                  abs_grad_at_zero == MHC_ABS0_PLUS_ONE ? 1.f : 0.f);
-    if (int e = check_launch("dynamic_weights_bwd(rows)")) return e;
-  }
-  const int64_t kblocks = (K + 255) / 256;
-  k_dw_bwd_main<<<(unsigned)(kblocks + 1), 256, 0, st>>>(x, phi, (const float*)scratch, grad_x, grad_phi, grad_bias,
-                                                         grad_alpha, batch, K, is_aligned16(phi),
-                                                         is_aligned16(grad_phi), accumulate_params);
-  return check_launch("dynamic_weights_bwd(main)");
+  return weights_bwd_impl(x, phi, BiasPtrs{bias, bias + 4, bias + 8}, alpha_pre, alpha_post, alpha_res, saved, nullptr,
+                          0, const_cast<float*>(dH_pre), dH_post, const_cast<float*>(dH_res), grad_x, grad_phi,
+                          grad_bias, grad_alpha, (float*)scratch, batch, K, iters, eps, abs_grad_at_zero,
+                          accumulate_params, (cudaStream_t)stream);
 }

@@ -148,3 +148,37 @@ def fused_dynamic_weights_backward(x, phi, bias, alpha_pre, alpha_post, alpha_re
             L.ptr(dH_post), L.ptr(dH_res), L.ptr(grad_x), L.ptr(g_phi), L.ptr(g_bias), L.ptr(g_alpha), L.ptr(buf),
             nbytes, B, K, int(sinkhorn_iters), float(eps), _ABS0[_abs_grad_at_zero], 0)
     return grad_x, g_phi, g_bias, g_alpha
+
+
+def hc_mix_backward(d_branch_input, dH_residual, dH_post, H, x, phi, H_pre_base, H_post_base, H_res_base,
+                    alpha_pre, alpha_post, alpha_res, saved, H_pre, H_res, sinkhorn_iters: int = 20,
+                    eps: float = 1e-6, param_grads=None, accumulate: bool = False):
+    """Fused backward of hc_mix_forward in ONE library call.  Returns
+    (dH, grad_phi [4D,24], grad_bias [24], grad_alpha [3]) with the last three being views of the
+    flat fp32 record `param_grads` (allocated here when not given; layout phi | bias | alpha)."""
+    B, S, _, D = H.shape
+    K = 4 * D
+    d_bi, dHr, H = _mix_bwd_inputs(d_branch_input, dH_residual, H)
+    L.require_cuda(dH_post, x, phi, saved, H_pre, H_res)
+    phi, pre_b, post_b, res_b = L.f32c(phi), L.f32c(H_pre_base), L.f32c(H_post_base), L.f32c(H_res_base)
+    a = [_alpha_dev(v, H) for v in (alpha_pre, alpha_post, alpha_res)]
+    dH_post = L.f32c(dH_post)
+    if param_grads is None:
+        param_grads = torch.empty(K * 24 + 27, device=H.device, dtype=torch.float32)
+        accumulate = False
+    _check(param_grads.numel() == K * 24 + 27 and param_grads.dtype == torch.float32 and param_grads.is_contiguous(),
+           "param_grads must be a contiguous fp32 buffer of 4*D*24 + 27 elements")
+    g_phi = param_grads[:K * 24].view(K, 24)
+    g_bias = param_grads[K * 24:K * 24 + 24]
+    g_alpha = param_grads[K * 24 + 24:]
+    dH = torch.empty_like(H)
+    small = torch.empty(B * (K + 20), device=H.device, dtype=torch.float32)
+    grad_x, dH_pre, dH_res = small[:B * K], small[B * K:B * K + 4 * B], small[B * K + 4 * B:]
+    buf, nbytes = L.scratch(L.OP_HC_MIX_BWD, B, S, D, H)
+    with torch.cuda.device(H.device):
+        L.call("mhc_hc_mix_bwd", L.stream_of(H), L.ptr(d_bi), L.ptr(dHr), L.ptr(dH_post), L.ptr(H), L.ptr(x), L.ptr(phi),
+               L.ptr(pre_b), L.ptr(post_b), L.ptr(res_b), L.ptr(a[0]), L.ptr(a[1]), L.ptr(a[2]), L.ptr(saved),
+               L.ptr(H_pre), L.ptr(H_res), L.ptr(dH), L.ptr(g_phi), L.ptr(g_bias), L.ptr(g_alpha), L.ptr(grad_x),
+               L.ptr(dH_pre), L.ptr(dH_res), L.ptr(buf), nbytes, B, S, D, L.dtype_code(H), int(sinkhorn_iters),
+               float(eps), _ABS0[_abs_grad_at_zero], 1 if accumulate else 0)
+    return dH, g_phi, g_bias, g_alpha

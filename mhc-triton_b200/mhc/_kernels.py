@@ -118,3 +118,33 @@ def fused_dynamic_weights_forward(x: torch.Tensor, phi: torch.Tensor, bias: torc
     if return_saved:
         return H_pre, H_post, H_res, saved
     return H_pre, H_post, H_res
+
+
+def hc_mix_forward(H, H_pre_base, H_post_base, H_res_base, phi, alpha_pre, alpha_post, alpha_res,
+                   sinkhorn_iters: int = 20, eps: float = 1e-6):
+    """Fused forward of the module's dynamic path in ONE library call: sequence mean-pool,
+    dynamic weights, stream mix.  Returns
+    (branch_input, H_residual, H_post, H_pre, H_res, x, saved); x [B,4D] and saved [B,32]
+    are what the fused backward needs."""
+    _check(H.dim() == 4 and H.shape[2] == 4, "H must be [batch, seq, 4, dim]")
+    B, S, _, D = H.shape
+    _check(S > 0 and D > 0, "empty sequence or width")
+    _check(tuple(phi.shape) == (4 * D, 24), f"phi shape mismatch: {tuple(phi.shape)} vs ({4 * D}, 24)")
+    _check(H_pre_base.numel() == 4 and H_post_base.numel() == 4 and H_res_base.numel() == 16, "base parameter shapes")
+    L.require_cuda(H, phi, H_pre_base, H_post_base, H_res_base)
+    H = H.contiguous()
+    phi, pre_b, post_b, res_b = L.f32c(phi), L.f32c(H_pre_base), L.f32c(H_post_base), L.f32c(H_res_base)
+    a = [_alpha_dev(v, H) for v in (alpha_pre, alpha_post, alpha_res)]
+    dev = H.device
+    small = torch.empty(B * 56, device=dev, dtype=torch.float32)   # one allocation for the small outputs
+    H_pre, H_post = small[:4 * B].view(B, 4), small[4 * B:8 * B].view(B, 4)
+    H_res, saved = small[8 * B:24 * B].view(B, 4, 4), small[24 * B:].view(B, 32)
+    x = torch.empty(B, 4 * D, device=dev, dtype=torch.float32)
+    bi = torch.empty(B, S, D, device=dev, dtype=H.dtype)
+    Hr = torch.empty_like(H)
+    buf, nbytes = L.scratch(L.OP_HC_MIX_FWD, B, S, D, H)
+    with torch.cuda.device(dev):
+        L.call("mhc_hc_mix_fwd", L.stream_of(H), L.ptr(H), L.ptr(phi), L.ptr(pre_b), L.ptr(post_b), L.ptr(res_b),
+               L.ptr(a[0]), L.ptr(a[1]), L.ptr(a[2]), L.ptr(x), L.ptr(H_pre), L.ptr(H_post), L.ptr(H_res), L.ptr(saved),
+               L.ptr(bi), L.ptr(Hr), L.ptr(buf), nbytes, B, S, D, L.dtype_code(H), int(sinkhorn_iters), float(eps))
+    return bi, Hr, H_post, H_pre, H_res, x, saved

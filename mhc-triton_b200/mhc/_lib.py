@@ -16,7 +16,8 @@ LIB_PATH = os.path.join(_HERE, "libmhc_b200.so")
 MHC_F32, MHC_BF16, MHC_F16 = 0, 1, 2
 _DTYPE_CODE = {torch.float32: MHC_F32, torch.bfloat16: MHC_BF16, torch.float16: MHC_F16}
 
-OP_ADD_RESIDUAL_BWD, OP_STREAM_MIX_BWD, OP_MEANPOOL_FWD, OP_DYNAMIC_WEIGHTS_FWD, OP_DYNAMIC_WEIGHTS_BWD = range(5)
+(OP_ADD_RESIDUAL_BWD, OP_STREAM_MIX_BWD, OP_MEANPOOL_FWD, OP_DYNAMIC_WEIGHTS_FWD, OP_DYNAMIC_WEIGHTS_BWD,
+ OP_HC_MIX_FWD, OP_HC_MIX_BWD) = range(7)
 
 ABS0_ZERO, ABS0_PLUS_ONE = 0, 1
 
@@ -35,10 +36,13 @@ _PROTOTYPES = {
     "mhc_meanpool_fwd": [_P, _P, _P, _L, _L, _L, _L, _I, _P],
     "mhc_dynamic_weights_fwd": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _I, _F, _P],
     "mhc_dynamic_weights_bwd": [_P] * 15 + [_L, _L, _L, _I, _F, _I, _I, _P],
+    "mhc_hc_mix_fwd": [_P] * 16 + [_L, _L, _L, _L, _I, _I, _F, _P],
+    "mhc_hc_mix_bwd": [_P] * 23 + [_L, _L, _L, _L, _I, _I, _F, _I, _I, _P],
 }
 
 EXPORTS = sorted(list(_PROTOTYPES) + ["mhc_version", "mhc_last_error_string", "mhc_status_name", "mhc_scratch_bytes",
-                                          "mhc_launch_count"])
+                                          "mhc_launch_count", "mhc_profile_enable", "mhc_profile_count",
+                                          "mhc_profile_get"])
 
 _lib = None
 
@@ -67,6 +71,12 @@ def load():
     lib.mhc_last_error_string.restype = c_char_p
     lib.mhc_status_name.argtypes = [c_int]
     lib.mhc_status_name.restype = c_char_p
+    lib.mhc_profile_enable.argtypes = [c_int]
+    lib.mhc_profile_enable.restype = c_int
+    lib.mhc_profile_count.argtypes = []
+    lib.mhc_profile_count.restype = c_int64
+    lib.mhc_profile_get.argtypes = [c_int64, ctypes.POINTER(c_char_p), ctypes.POINTER(c_float)]
+    lib.mhc_profile_get.restype = c_int
     lib.mhc_launch_count.argtypes = []
     lib.mhc_launch_count.restype = c_int64
     lib.mhc_scratch_bytes.argtypes = [c_int, c_int64, c_int64, c_int64, c_int]
@@ -75,36 +85,28 @@ def load():
     return lib
 
 
-class KernelTimer:
-    """Collects CUDA-event pairs around every C-ABI call made while it is installed
-    (`_lib.timer = KernelTimer()`), on the stream the kernels are launched on."""
-
-    def __init__(self):
-        self.records = {}
-
-    def add(self, name, start, end):
-        self.records.setdefault(name, []).append((start, end))
-
-    def summary(self):
-        """name -> (calls, total milliseconds); call after a device synchronize."""
-        return {k: (len(v), sum(a.elapsed_time(b) for a, b in v)) for k, v in self.records.items()}
-
-
-timer = None
-
-
 def call(name, stream, *args):
-    """Invoke an entry point (its last argument is the stream) and raise on a non-zero status."""
-    fn = getattr(load(), name)
-    if timer is None:
-        return check(fn(*args, stream))
-    ext = torch.cuda.ExternalStream(stream) if stream else torch.cuda.current_stream()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record(ext)
-    status = fn(*args, stream)
-    b.record(ext)
-    timer.add(name, a, b)
-    return check(status)
+    """Invoke an entry point (the stream is its last argument) and raise on a non-zero status."""
+    return check(getattr(load(), name)(*args, stream))
+
+
+def profile_start():
+    """Start per-kernel timing inside the library (CUDA events around every kernel launch)."""
+    check(load().mhc_profile_enable(1))
+
+
+def profile_stop():
+    """Stop timing and return {kernel name: (launches, total milliseconds)}.  Synchronises the device."""
+    lib = load()
+    check(lib.mhc_profile_enable(0))
+    torch.cuda.synchronize()
+    out = {}
+    name, ms = c_char_p(), c_float()
+    for i in range(lib.mhc_profile_count()):
+        check(lib.mhc_profile_get(i, ctypes.byref(name), ctypes.byref(ms)))
+        n, t = out.get(name.value.decode(), (0, 0.0))
+        out[name.value.decode()] = (n + 1, t + ms.value)
+    return out
 
 
 def check(status):

@@ -11,10 +11,10 @@ from typing import Tuple
 
 import torch
 
-from ._backward import (add_residual_backward, fused_dynamic_weights_backward, sinkhorn_backward,
-                        stream_mix_backward, stream_mix_backward_apply, stream_mix_backward_reduce)
-from ._kernels import (add_residual_forward, fused_dynamic_weights_forward, meanpool_forward, sinkhorn_forward,
-                       stream_mix_forward)
+from ._backward import (add_residual_backward, fused_dynamic_weights_backward, hc_mix_backward, sinkhorn_backward,
+                        stream_mix_backward)
+from ._kernels import (add_residual_forward, fused_dynamic_weights_forward, hc_mix_forward, meanpool_forward,
+                       sinkhorn_forward, stream_mix_forward)
 
 
 class _SinkhornKnopp(torch.autograd.Function):
@@ -107,8 +107,9 @@ class _HyperConnectionMix(torch.autograd.Function):
 
     Inputs : H, H_pre_base, H_post_base, H_res_base, phi, alpha_pre, alpha_post, alpha_res
     Outputs: branch_input, H_residual, H_post
-    Backward: one reduction pass (dH_pre, dH_res), the small weights backward, then one
-    apply pass that writes dH once, including grad_x / S.  When `grad_sink` (a flat fp32
+    Forward and backward are one library call each.  Backward: one reduction pass (dH_pre,
+    dH_res), the small weights backward, then one apply pass that writes dH once, including
+    grad_x / S.  When `grad_sink` (a flat fp32
     buffer of 4*D*24 + 27 elements) is given, grad_phi / grad_bias / grad_alpha are written
     straight into it, ready for one all-reduce, and `ready_hook` is told so.
     """
@@ -116,32 +117,27 @@ class _HyperConnectionMix(torch.autograd.Function):
     @staticmethod
     def forward(ctx, H, H_pre_base, H_post_base, H_res_base, phi, alpha_pre, alpha_post, alpha_res,
                 sinkhorn_iters, eps, grad_sink, ready_hook):
-        x = meanpool_forward(H)
-        bias = torch.cat([H_pre_base.reshape(-1), H_post_base.reshape(-1), H_res_base.reshape(-1)]).float()
-        H_pre, H_post, H_res, saved = fused_dynamic_weights_forward(
-            x, phi, bias, alpha_pre, alpha_post, alpha_res, sinkhorn_iters, eps, return_saved=True)
-        branch_input, H_residual = stream_mix_forward(H, H_pre, H_res)
-        ctx.save_for_backward(H, x, phi, bias, alpha_pre, alpha_post, alpha_res, saved, H_pre, H_res)
+        branch_input, H_residual, H_post, H_pre, H_res, x, saved = hc_mix_forward(
+            H, H_pre_base, H_post_base, H_res_base, phi, alpha_pre, alpha_post, alpha_res, sinkhorn_iters, eps)
+        ctx.save_for_backward(H, x, phi, H_pre_base, H_post_base, H_res_base, alpha_pre, alpha_post, alpha_res,
+                              saved, H_pre, H_res)
         ctx.sinkhorn_iters, ctx.eps, ctx.grad_sink, ctx.ready_hook = sinkhorn_iters, eps, grad_sink, ready_hook
-        ctx.param_meta = [(p.shape, p.dtype) for p in (H_pre_base, H_post_base, H_res_base)]
         ctx.mark_non_differentiable(H_pre, H_res)
         return branch_input, H_residual, H_post, H_pre, H_res
 
     @staticmethod
     def backward(ctx, d_branch_input, dH_residual, dH_post, _unused_pre, _unused_res):
-        H, x, phi, bias, alpha_pre, alpha_post, alpha_res, saved, H_pre, H_res = ctx.saved_tensors
-        dH_pre, dH_res = stream_mix_backward_reduce(d_branch_input, dH_residual, H)
-        gx, gphi, gbias, galpha = fused_dynamic_weights_backward(
-            x, phi, bias, alpha_pre, alpha_post, alpha_res, saved, dH_pre, dH_post, dH_res,
-            ctx.sinkhorn_iters, ctx.eps, param_grads=ctx.grad_sink)
+        (H, x, phi, pre_b, post_b, res_b, alpha_pre, alpha_post, alpha_res, saved, H_pre, H_res) = ctx.saved_tensors
+        dH, gphi, gbias, galpha = hc_mix_backward(
+            d_branch_input, dH_residual, dH_post, H, x, phi, pre_b, post_b, res_b, alpha_pre, alpha_post, alpha_res,
+            saved, H_pre, H_res, ctx.sinkhorn_iters, ctx.eps, param_grads=ctx.grad_sink)
         if ctx.ready_hook is not None:
             ctx.ready_hook(ctx.grad_sink)
-        dH = stream_mix_backward_apply(d_branch_input, dH_residual, H_pre, H_res, gx, H)
         if ctx.grad_sink is not None:  # the parameters' .grad tensors are views of the sink already
             return (dH,) + (None,) * 11
-        (s0, t0), (s1, t1), (s2, t2) = ctx.param_meta
-        return (dH, gbias[0:4].reshape(s0).to(t0), gbias[4:8].reshape(s1).to(t1), gbias[8:24].reshape(s2).to(t2),
-                gphi.to(phi.dtype), galpha[0:1].reshape_as(alpha_pre).to(alpha_pre.dtype),
+        return (dH, gbias[0:4].reshape(pre_b.shape).to(pre_b.dtype), gbias[4:8].reshape(post_b.shape).to(post_b.dtype),
+                gbias[8:24].reshape(res_b.shape).to(res_b.dtype), gphi.to(phi.dtype),
+                galpha[0:1].reshape_as(alpha_pre).to(alpha_pre.dtype),
                 galpha[1:2].reshape_as(alpha_post).to(alpha_post.dtype),
                 galpha[2:3].reshape_as(alpha_res).to(alpha_res.dtype), None, None, None, None)
 
