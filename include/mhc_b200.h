@@ -75,6 +75,9 @@ int64_t mhc_launch_count(void);
  * events on the stream it is launched on.  enable(1) drops earlier records and starts; enable(0)
  * stops.  After the device is synchronised, record i gives the kernel's name and its duration. */
 int mhc_profile_enable(int on);
+/* Restrict timing to the kernel with this name (NULL or "" = every kernel); the events of a timed
+ * kernel sit between it and its neighbours on the stream, so timing one kernel perturbs least. */
+int mhc_profile_select(const char* kernel_name);
 int64_t mhc_profile_count(void);
 int mhc_profile_get(int64_t index, const char** name, float* milliseconds);
 

@@ -34,27 +34,30 @@ def up_to_date():
     return all(os.path.getmtime(d) <= t for d in deps)
 
 
-def build(force=False, verbose=False):
-    if not force and up_to_date():
+def build(force=False, verbose=False, defines=(), out=OUT):
+    if not force and out == OUT and up_to_date():
         return OUT
     cmd = [nvcc_path(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
            "--use_fast_math=false", "-shared", "-Xcompiler", "-fPIC", "-cudart", "static"]
     cmd = [c for c in cmd if c != "--use_fast_math=false"]
     if verbose:
         cmd += ["-Xptxas", "-v"]
-    cmd += [os.path.join(CSRC, s) for s in SOURCES] + ["-o", OUT]
+    cmd += [f"-D{d}" for d in defines]
+    cmd += [os.path.join(CSRC, s) for s in SOURCES] + ["-o", out]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         sys.stderr.write(res.stdout + res.stderr)
         raise RuntimeError("nvcc failed")
     if verbose:
         print(res.stdout + res.stderr)
-    return OUT
+    return out
 
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
+    ap.add_argument("-D", dest="defines", action="append", default=[], help="tuning macro, e.g. -D MHC_TPC_MAX=16")
+    ap.add_argument("--out", default=OUT)
     a = ap.parse_args()
-    print(build(a.force, a.verbose))
+    print(build(a.force or bool(a.defines) or a.out != OUT, a.verbose, a.defines, a.out))

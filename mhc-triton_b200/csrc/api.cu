@@ -2,6 +2,8 @@
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
+#include <cstring>
 #include <mutex>
 #include <vector>
 
@@ -20,6 +22,14 @@ int fail(int status, const char* fmt, ...) {
   return status;
 }
 
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* e = std::getenv("MHC_PDL");
+    return !(e && std::strcmp(e, "0") == 0);
+  }();
+  return on;
+}
+
 int check_launch(const char* what) {
   const cudaError_t e = cudaGetLastError();
   if (e == cudaSuccess) {
@@ -34,9 +44,11 @@ struct ProfRec { const char* name; cudaEvent_t a, b; };
 static std::atomic<int> g_prof_on{0};
 static std::mutex g_prof_mu;
 static std::vector<ProfRec> g_prof;
+static char g_prof_only[64] = "";  // when non-empty, only this kernel is timed
 
 ProfScope::ProfScope(const char* name, cudaStream_t s) : slot(-1), st(s) {
   if (!g_prof_on.load(std::memory_order_relaxed)) return;
+  if (g_prof_only[0] && std::strcmp(g_prof_only, name) != 0) return;
   ProfRec r{name, nullptr, nullptr};
   if (cudaEventCreate(&r.a) != cudaSuccess || cudaEventCreate(&r.b) != cudaSuccess) {
     (void)cudaGetLastError();
@@ -68,6 +80,12 @@ static void prof_clear() {
 extern "C" int mhc_profile_enable(int on) {
   if (on) mhc::prof_clear();
   mhc::g_prof_on.store(on ? 1 : 0);
+  return MHC_OK;
+}
+
+extern "C" int mhc_profile_select(const char* kernel_name) {
+  std::lock_guard<std::mutex> lk(mhc::g_prof_mu);
+  std::snprintf(mhc::g_prof_only, sizeof(mhc::g_prof_only), "%s", kernel_name ? kernel_name : "");
   return MHC_OK;
 }
 

@@ -10,6 +10,14 @@
 
 namespace mhc {
 
+// First statement of every kernel: let the next kernel on the stream start being scheduled, then
+// wait until the previous kernel has completed and its writes are visible (both are no-ops for a
+// launch without the programmatic-serialization attribute).
+__device__ __forceinline__ void pdl_prologue() {
+  asm volatile("griddepcontrol.launch_dependents;");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 constexpr int kStreams = 4;
 constexpr int kOut = 24;        // 4 pre + 4 post + 16 res
 constexpr int kSavedStride = 32;  // floats per row of the forward's saved buffer
@@ -40,9 +48,17 @@ __device__ __forceinline__ uint4 ld_stream16(const void* p) {
       : "l"(p));
   return r;
 }
+#ifndef MHC_ST_MODE
+#define MHC_ST_MODE 0
+#endif
 __device__ __forceinline__ void st_stream16(void* p, uint4 v) {
-  asm volatile("st.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
-               : "memory");
+#if MHC_ST_MODE == 1
+  asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+#elif MHC_ST_MODE == 2
+  asm volatile("st.global.L1::no_allocate.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+#else
+  asm volatile("st.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+#endif
 }
 
 template <typename T, int V> struct PackIO;
@@ -148,6 +164,16 @@ template <int V> __device__ __forceinline__ float raw_get(const RawPack<__half, 
   }
 }
 
+// Plain token loop: load, then compute (more resident CTAs cover the latency instead).
+template <class Bundle, class Load, class Compute>
+__device__ __forceinline__ void for_tokens_simple(int64_t s0, int64_t s1, int64_t step, Load load, Compute compute) {
+  for (int64_t s = s0; s < s1; s += step) {
+    Bundle a;
+    load(a, s);
+    compute(a, s);
+  }
+}
+
 // Software pipeline over the tokens s0, s0+step, ... < s1: the loads of the next token are issued
 // before the arithmetic of the current one, so every thread always has one token's packs in flight.
 template <class Bundle, class Load, class Compute>
@@ -166,6 +192,12 @@ __device__ __forceinline__ void for_tokens_pipelined(int64_t s0, int64_t s1, int
   }
 }
 
+template <bool PIPE, class Bundle, class Load, class Compute>
+__device__ __forceinline__ void for_tokens(int64_t s0, int64_t s1, int64_t step, Load load, Compute compute) {
+  if constexpr (PIPE) for_tokens_pipelined<Bundle>(s0, s1, step, load, compute);
+  else for_tokens_simple<Bundle>(s0, s1, step, load, compute);
+}
+
 // ---------------------------------------------------------------------------------------
 // Work decomposition.  One CTA = one (batch element b, chunk of `tpc` consecutive tokens,
 // group of blockDim.x consecutive packs along D).  The layout of the per-CTA partial sums
@@ -181,6 +213,7 @@ struct Geo {
   int32_t nchunk;  // ceil(S / tpc)
   int32_t cols;    // columns (packs) per CTA
   int32_t sub;     // token sub-groups inside a CTA (blockDim.x = cols * sub)
+  int32_t reverse; // walk the work items from the end of the tensor towards its start
 };
 
 struct Item {
@@ -194,7 +227,7 @@ struct Item {
 
 __device__ __forceinline__ Item decode_item(const Geo& g) {
   Item it;
-  const int64_t w = blockIdx.x;
+  const int64_t w = g.reverse ? (int64_t)gridDim.x - 1 - blockIdx.x : (int64_t)blockIdx.x;
   it.cg = (int32_t)(w % g.CG);
   const int64_t r = w / g.CG;
   it.chunk = (int32_t)(r % g.nchunk);
@@ -248,6 +281,32 @@ __device__ __forceinline__ double warp_sum_f64(double v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   return v;
+}
+
+// Column sums of a [slots, W] fp32 array (W <= 20) by a CTA of 256 threads: thread t adds rows
+// t, t+256, ... (all loads issued before any use), a xor-shuffle tree adds the lanes of each warp,
+// and after the barrier sm[w][j] holds warp w's sum of column j; callers add the 8 warps in index
+// order.  fp64 throughout; the order depends only on `slots`.
+__device__ __forceinline__ void block_column_sums_f64(const float* __restrict__ p, int64_t slots, int W,
+                                                      double (*sm)[20]) {
+  double a[20];
+#pragma unroll
+  for (int j = 0; j < 20; ++j) a[j] = 0.0;
+  for (int64_t s = threadIdx.x; s < slots; s += 256) {
+    const float* q = p + s * W;
+#pragma unroll
+    for (int j = 0; j < 20; ++j)
+      if (j < W) a[j] += (double)__ldg(q + j);
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll
+  for (int j = 0; j < 20; ++j) {
+    if (j < W) {
+      const double t = warp_sum_f64(a[j]);
+      if (lane == 0) sm[warp][j] = t;
+    }
+  }
+  __syncthreads();
 }
 
 // ---------------------------------------------------------------------------------------

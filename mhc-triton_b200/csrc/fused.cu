@@ -30,7 +30,7 @@ extern "C" int mhc_hc_mix_fwd(const void* H, const float* phi, const float* H_pr
   float* proj_part = pool_part + pool_floats;
   int nchunk = 0;
   if (int e = meanpool_partial_impl(H, pool_part, B, S, D, dtype, st, &nchunk)) return e;
-  if (int e = weights_fwd_impl(pool_part, nchunk, 1.f / (float)S, x, phi, BiasPtrs{H_pre_base, H_post_base, H_res_base},
+  if (int e = weights_fwd_impl(pool_part, nchunk, 1.0 / (double)S, x, phi, BiasPtrs{H_pre_base, H_post_base, H_res_base},
                                alpha_pre, alpha_post, alpha_res, H_pre, H_post, H_res, saved, proj_part, B, 4 * D,
                                iters, eps, st))
     return e;

@@ -29,6 +29,28 @@ inline int64_t geo_slots(const Geo& g) { return (int64_t)g.nchunk * g.CG; }  // 
 // Pack width usable for a row length D of `dtype` given the pointers involved.
 int pick_vec(int dtype, int64_t D, std::initializer_list<const void*> ptrs);
 
+// Programmatic dependent launch (on unless MHC_PDL=0 is set in the environment): every kernel of
+// this library may be scheduled while the previous kernel on the stream is still draining; each
+// kernel starts with griddepcontrol.wait, so it touches memory only after its predecessor has
+// completed and flushed.
+bool pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+inline void launch_k(void (*kernel)(KArgs...), unsigned grid, unsigned block, size_t smem, cudaStream_t st,
+                     Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(block);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  (void)cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);  // errors surface in check_launch()
+}
+
 // The 24 bias entries as three device arrays (pre-mix base [4], post base [4], residual base [16]).
 struct BiasPtrs { const float *pre, *post, *res; };
 
@@ -54,7 +76,7 @@ int mix_bwd_apply_impl(const void* dbi, const void* dHr, const float* H_pre, con
                        float inv_S, void* dH, int64_t B, int64_t S, int64_t D, int dtype, cudaStream_t st);
 int64_t meanpool_scratch_floats(int64_t B, int64_t S, int64_t D);
 int64_t mix_bwd_scratch_floats(int64_t B, int64_t S, int64_t D);
-int weights_fwd_impl(const float* xsrc, int nsrc, float scale, float* x_out, const float* phi, BiasPtrs bias,
+int weights_fwd_impl(const float* xsrc, int nsrc, double scale, float* x_out, const float* phi, BiasPtrs bias,
                      const float* alpha_pre, const float* alpha_post, const float* alpha_res, float* H_pre,
                      float* H_post, float* H_res, float* saved, float* part, int64_t batch, int64_t K, int iters,
                      float eps, cudaStream_t st);

@@ -43,6 +43,7 @@ __device__ __forceinline__ void store_matrix(T* __restrict__ p, const float (&m)
 template <typename T>
 __global__ void __launch_bounds__(128) k_sinkhorn_fwd(const T* __restrict__ M, T* __restrict__ P, int64_t batch,
                                                       int iters, float eps, bool aligned) {
+  pdl_prologue();
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= batch) return;
   float m[16];
@@ -60,6 +61,7 @@ template <typename T>
 __global__ void __launch_bounds__(128) k_sinkhorn_bwd(const T* __restrict__ M, const T* __restrict__ dP,
                                                       T* __restrict__ dM, int64_t batch, int iters, float eps,
                                                       float sign_at_zero, bool aligned) {
+  pdl_prologue();
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= batch) return;
   float m0[16], d[16];
@@ -88,7 +90,7 @@ static int launch_fwd(const void* M, void* P, int64_t batch, int iters, float ep
   const int64_t grid = (batch + block - 1) / block;
   {
     ProfScope ps("k_sinkhorn_fwd", st);
-    k_sinkhorn_fwd<T><<<(unsigned)grid, block, 0, st>>>((const T*)M, (T*)P, batch, iters, eps, aligned);
+    launch_k(k_sinkhorn_fwd<T>, (unsigned)grid, block, 0, st, (const T*)M, (T*)P, batch, iters, eps, aligned);
   }
   return check_launch("sinkhorn_fwd");
 }
@@ -101,7 +103,7 @@ static int launch_bwd(const void* M, const void* dP, void* dM, int64_t batch, in
   const int64_t grid = (batch + block - 1) / block;
   {
     ProfScope ps("k_sinkhorn_bwd", st);
-    k_sinkhorn_bwd<T><<<(unsigned)grid, block, 0, st>>>((const T*)M, (const T*)dP, (T*)dM, batch, iters, eps, sz,
+    launch_k(k_sinkhorn_bwd<T>, (unsigned)grid, block, 0, st, (const T*)M, (const T*)dP, (T*)dM, batch, iters, eps, sz,
                                                          aligned);
   }
   return check_launch("sinkhorn_bwd");

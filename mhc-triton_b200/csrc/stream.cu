@@ -10,6 +10,42 @@
 
 namespace mhc {
 
+// Tuning knobs (compile-time): software pipelining and minimum resident CTAs per kernel.
+#ifndef MHC_MIXFWD_PIPE
+#define MHC_MIXFWD_PIPE 1
+#endif
+#ifndef MHC_MIXFWD_MINB
+#define MHC_MIXFWD_MINB 3
+#endif
+#ifndef MHC_ADDFWD_PIPE
+#define MHC_ADDFWD_PIPE 1
+#endif
+#ifndef MHC_ADDFWD_MINB
+#define MHC_ADDFWD_MINB 4
+#endif
+#ifndef MHC_APPLY_PIPE
+#define MHC_APPLY_PIPE 0
+#endif
+#ifndef MHC_APPLY_MINB
+#define MHC_APPLY_MINB 3
+#endif
+#ifndef MHC_POOL_TPC
+#define MHC_POOL_TPC 256
+#endif
+#ifndef MHC_POOL_COLS
+#define MHC_POOL_COLS 64
+#endif
+// Walking direction per kernel (bit set = from the end of the tensor to its start): bit 0 mean-pool,
+// 1 stream mix, 2 add residual, 3 add-residual backward, 4 stream-mix backward reduce / full,
+// 5 stream-mix backward apply.  Consecutive kernels of a layer step walk in opposite directions so
+// that what the previous kernel touched last (still in L2) is what the next one touches first.
+#ifndef MHC_REV_MASK
+#define MHC_REV_MASK 18
+#endif
+#ifndef MHC_TPC_MAX
+#define MHC_TPC_MAX 32
+#endif
+
 template <typename T, int V, int N> struct Bundle { RawPack<T, V> p[N]; };
 
 template <typename T, int V>
@@ -20,9 +56,10 @@ __device__ __forceinline__ void unpack(const RawPack<T, V>& r, float (&o)[V]) {
 
 // ------------------------------------------------------------------------------- stream mix
 template <typename T, int V>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, MHC_MIXFWD_MINB)
 k_stream_mix_fwd(const T* __restrict__ H, const float* __restrict__ Hpre, const float* __restrict__ Hres,
                  T* __restrict__ bi, T* __restrict__ Hr, Geo g) {
+  pdl_prologue();
   const Item it = decode_item(g);
   if (it.col >= g.DV) return;
   float w[4], R[16];
@@ -32,7 +69,7 @@ k_stream_mix_fwd(const T* __restrict__ H, const float* __restrict__ Hpre, const 
   for (int k = 0; k < 16; ++k) R[k] = __ldg(Hres + it.b * 16 + k);
   const int64_t D = g.D, c0 = (int64_t)it.col * V, tok = it.b * g.S;
   using B4 = Bundle<T, V, 4>;
-  for_tokens_pipelined<B4>(
+  for_tokens<MHC_MIXFWD_PIPE != 0, B4>(
       it.s0, it.s1, 1,
       [&](B4& u, int64_t s) {
         const T* h = H + (tok + s) * 4 * D + c0;
@@ -59,9 +96,10 @@ k_stream_mix_fwd(const T* __restrict__ H, const float* __restrict__ Hpre, const 
 
 // ------------------------------------------------------------------------------ add residual
 template <typename T, int V>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, MHC_ADDFWD_MINB)
 k_add_residual_fwd(const T* __restrict__ Hr, const T* __restrict__ bo, const float* __restrict__ Hpost,
                    T* __restrict__ Hn, Geo g) {
+  pdl_prologue();
   const Item it = decode_item(g);
   if (it.col >= g.DV) return;
   float p[4];
@@ -69,7 +107,7 @@ k_add_residual_fwd(const T* __restrict__ Hr, const T* __restrict__ bo, const flo
   for (int n = 0; n < 4; ++n) p[n] = __ldg(Hpost + it.b * 4 + n);
   const int64_t D = g.D, c0 = (int64_t)it.col * V, tok = it.b * g.S;
   using B5 = Bundle<T, V, 5>;
-  for_tokens_pipelined<B5>(
+  for_tokens<MHC_ADDFWD_PIPE != 0, B5>(
       it.s0, it.s1, 1,
       [&](B5& u, int64_t s) {
         const T* r = Hr + (tok + s) * 4 * D + c0;
@@ -97,6 +135,7 @@ template <typename T, int V>
 __global__ void __launch_bounds__(256)
 k_add_residual_bwd(const T* __restrict__ G, const T* __restrict__ bo, const float* __restrict__ Hpost,
                    T* __restrict__ dbo, float* __restrict__ part, Geo g) {
+  pdl_prologue();
   __shared__ float red[32 * 4];
   const Item it = decode_item(g);
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
@@ -142,6 +181,7 @@ __global__ void __launch_bounds__(256, 2)
 k_stream_mix_bwd(const T* __restrict__ dbi, const T* __restrict__ dHr, const T* __restrict__ H,
                  const float* __restrict__ Hpre, const float* __restrict__ Hres, T* __restrict__ dH,
                  float* __restrict__ part, Geo g) {
+  pdl_prologue();
   __shared__ float red[32 * 20];
   const Item it = decode_item(g);
   float acc[20];
@@ -199,10 +239,11 @@ k_stream_mix_bwd(const T* __restrict__ dbi, const T* __restrict__ dHr, const T* 
 
 // dH[s,m,d] = H_pre[m] d_bi[s,d] + sum_n H_res[n,m] dH_residual[s,n,d] + inv_S * gx[m*D + d].
 template <typename T, int V>
-__global__ void __launch_bounds__(256, 2)
+__global__ void __launch_bounds__(256, MHC_APPLY_MINB)
 k_stream_mix_bwd_apply(const T* __restrict__ dbi, const T* __restrict__ dHr, const float* __restrict__ Hpre,
                        const float* __restrict__ Hres, const float* __restrict__ gx, float inv_S,
                        T* __restrict__ dH, Geo g) {
+  pdl_prologue();
   const Item it = decode_item(g);
   if (it.col >= g.DV) return;
   float w[4], R[16], c[4][V];
@@ -217,7 +258,7 @@ k_stream_mix_bwd_apply(const T* __restrict__ dbi, const T* __restrict__ dHr, con
     for (int e = 0; e < V; ++e) c[m][e] = gx ? inv_S * __ldg(gx + it.b * 4 * D + m * D + c0 + e) : 0.f;
   }
   using B5 = Bundle<T, V, 5>;
-  for_tokens_pipelined<B5>(
+  for_tokens<MHC_APPLY_PIPE != 0, B5>(
       it.s0, it.s1, 1,
       [&](B5& u, int64_t s) {
         const T* rp = dHr + (tok + s) * 4 * D + c0;
@@ -249,6 +290,7 @@ k_stream_mix_bwd_apply(const T* __restrict__ dbi, const T* __restrict__ dHr, con
 template <typename T, int V>
 __global__ void __launch_bounds__(256)
 k_meanpool_partial(const T* __restrict__ H, float* __restrict__ part, Geo g) {
+  pdl_prologue();
   extern __shared__ float sm[];  // [4*V][sub][cols]
   const Item it = decode_item(g);
   const int64_t D = g.D, c0 = (int64_t)it.col * V, tok = it.b * g.S;
@@ -316,6 +358,7 @@ k_meanpool_partial(const T* __restrict__ H, float* __restrict__ part, Geo g) {
 __global__ void __launch_bounds__(256)
 k_meanpool_finish(const float* __restrict__ part, float* __restrict__ x, int64_t K, int nchunk, double scale,
                   int64_t total) {
+  pdl_prologue();
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   const int64_t b = i / K, k = i - b * K;
@@ -331,17 +374,11 @@ k_meanpool_finish(const float* __restrict__ part, float* __restrict__ x, int64_t
 __global__ void __launch_bounds__(256)
 k_reduce_partials(const float* __restrict__ part, int64_t slots, int W, int W0, float* __restrict__ out0,
                   float* __restrict__ out1) {
+  pdl_prologue();
   __shared__ double sm[8][20];
   const int64_t b = blockIdx.x;
   const float* p = part + b * slots * W;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int j = 0; j < W; ++j) {
-    double a = 0.0;
-    for (int64_t s = threadIdx.x; s < slots; s += 256) a += (double)__ldg(p + s * W + j);
-    a = warp_sum_f64(a);
-    if (lane == 0) sm[warp][j] = a;
-  }
-  __syncthreads();
+  block_column_sums_f64(p, slots, W, sm);
   const int j = threadIdx.x;
   if (j < W) {
     double t = 0.0;
@@ -355,21 +392,22 @@ k_reduce_partials(const float* __restrict__ part, int64_t slots, int W, int W0, 
 // -------------------------------------------------------------------------------- host side
 Geo make_geo(int64_t S, int64_t D, int vec, bool pool) {
   Geo g;
+  g.reverse = 0;
   g.S = S;
   g.D = D;
   g.DV = (int32_t)(D / vec);
-  const int max_cols = pool ? 64 : 256;
+  const int max_cols = pool ? MHC_POOL_COLS : 256;
   int cols = 32;
   while (cols < max_cols && cols < g.DV) cols <<= 1;
   g.cols = cols;
   g.CG = (g.DV + cols - 1) / cols;
   if (pool) {
     g.sub = 256 / cols;
-    g.tpc = 128;
+    g.tpc = MHC_POOL_TPC;
   } else {
     g.sub = 1;
     int64_t t = S / 256;
-    g.tpc = (int32_t)(t < 4 ? 4 : (t > 32 ? 32 : t));
+    g.tpc = (int32_t)(t < 4 ? 4 : (t > MHC_TPC_MAX ? MHC_TPC_MAX : t));
   }
   g.nchunk = (int32_t)((S + g.tpc - 1) / g.tpc);
   return g;
@@ -414,12 +452,13 @@ static int check_grid(const char* what, int64_t items) {
 int stream_mix_fwd_impl(const void* H, const float* H_pre, const float* H_res, void* bi, void* Hr, int64_t B, int64_t S,
                         int64_t D, int dtype, cudaStream_t st) {
   const int vec = pick_vec(dtype, D, {H, bi, Hr});
-  const Geo g = make_geo(S, D, vec, false);
+  Geo g = make_geo(S, D, vec, false);
+  g.reverse = (MHC_REV_MASK >> 1) & 1;
   const int64_t items = B * geo_slots(g);
   if (int e = check_grid("stream_mix_fwd", items)) return e;
   {
     ProfScope ps("k_stream_mix_fwd", st);
-    MHC_DISPATCH(dtype, vec, (k_stream_mix_fwd<T, V><<<(unsigned)items, geo_block(g), 0, st>>>(
+    MHC_DISPATCH(dtype, vec, (launch_k(k_stream_mix_fwd<T, V>, (unsigned)items, geo_block(g), 0, st, 
                                  (const T*)H, H_pre, H_res, (T*)bi, (T*)Hr, g)));
   }
   return check_launch("stream_mix_fwd");
@@ -431,13 +470,14 @@ int64_t mix_bwd_scratch_floats(int64_t B, int64_t S, int64_t D) { return B * geo
 int meanpool_partial_impl(const void* H, float* part, int64_t B, int64_t S, int64_t D, int dtype, cudaStream_t st,
                           int* nchunk) {
   const int vec = pick_vec(dtype, D, {H});
-  const Geo g = make_geo(S, D, vec, true);
+  Geo g = make_geo(S, D, vec, true);
+  g.reverse = MHC_REV_MASK & 1;
   const int64_t items = B * geo_slots(g);
   if (int e = check_grid("meanpool_fwd", items)) return e;
   const size_t smem = (size_t)4 * vec * geo_block(g) * sizeof(float);
   {
     ProfScope ps("k_meanpool_partial", st);
-    MHC_DISPATCH(dtype, vec, (k_meanpool_partial<T, V><<<(unsigned)items, geo_block(g), smem, st>>>((const T*)H, part, g)));
+    MHC_DISPATCH(dtype, vec, (launch_k(k_meanpool_partial<T, V>, (unsigned)items, geo_block(g), smem, st, (const T*)H, part, g)));
   }
   *nchunk = g.nchunk;
   return check_launch("meanpool_fwd");
@@ -448,17 +488,18 @@ int mix_bwd_partials_impl(int mode, const void* dbi, const void* dHr, const void
                           const float* H_res, void* dH, float* part, int64_t B, int64_t S, int64_t D, int dtype,
                           cudaStream_t st, int64_t* slots) {
   const int vec = pick_vec(dtype, D, {dbi, dHr, H, dH});
-  const Geo g = make_geo(S, D, vec, false);
+  Geo g = make_geo(S, D, vec, false);
+  g.reverse = (MHC_REV_MASK >> 4) & 1;
   *slots = geo_slots(g);
   const int64_t items = B * *slots;
   if (int e = check_grid("stream_mix_bwd", items)) return e;
   if (mode == 0) {
     ProfScope ps("k_stream_mix_bwd_full", st);
-    MHC_DISPATCH(dtype, vec, (k_stream_mix_bwd<T, V, 0><<<(unsigned)items, geo_block(g), 0, st>>>(
+    MHC_DISPATCH(dtype, vec, (launch_k(k_stream_mix_bwd<T, V, 0>, (unsigned)items, geo_block(g), 0, st, 
                                  (const T*)dbi, (const T*)dHr, (const T*)H, H_pre, H_res, (T*)dH, part, g)));
   } else {
     ProfScope ps("k_stream_mix_bwd_reduce", st);
-    MHC_DISPATCH(dtype, vec, (k_stream_mix_bwd<T, V, 1><<<(unsigned)items, geo_block(g), 0, st>>>(
+    MHC_DISPATCH(dtype, vec, (launch_k(k_stream_mix_bwd<T, V, 1>, (unsigned)items, geo_block(g), 0, st, 
                                  (const T*)dbi, (const T*)dHr, (const T*)H, nullptr, nullptr, nullptr, part, g)));
   }
   return check_launch("stream_mix_bwd");
@@ -467,12 +508,13 @@ int mix_bwd_partials_impl(int mode, const void* dbi, const void* dHr, const void
 int mix_bwd_apply_impl(const void* dbi, const void* dHr, const float* H_pre, const float* H_res, const float* gx,
                        float inv_S, void* dH, int64_t B, int64_t S, int64_t D, int dtype, cudaStream_t st) {
   const int vec = pick_vec(dtype, D, {dbi, dHr, dH});
-  const Geo g = make_geo(S, D, vec, false);
+  Geo g = make_geo(S, D, vec, false);
+  g.reverse = (MHC_REV_MASK >> 5) & 1;
   const int64_t items = B * geo_slots(g);
   if (int e = check_grid("stream_mix_bwd_apply", items)) return e;
   {
     ProfScope ps("k_stream_mix_bwd_apply", st);
-    MHC_DISPATCH(dtype, vec, (k_stream_mix_bwd_apply<T, V><<<(unsigned)items, geo_block(g), 0, st>>>(
+    MHC_DISPATCH(dtype, vec, (launch_k(k_stream_mix_bwd_apply<T, V>, (unsigned)items, geo_block(g), 0, st, 
                                  (const T*)dbi, (const T*)dHr, H_pre, H_res, gx, inv_S, (T*)dH, g)));
   }
   return check_launch("stream_mix_bwd_apply");
@@ -484,7 +526,7 @@ static int launch_reduce(const float* part, int64_t B, int64_t slots, int W, int
                          cudaStream_t st, const char* what) {
   {
     ProfScope ps("k_reduce_partials", st);
-    k_reduce_partials<<<(unsigned)B, 256, 0, st>>>(part, slots, W, W0, out0, out1);
+    launch_k(k_reduce_partials, (unsigned)B, 256, 0, st, part, slots, W, W0, out0, out1);
   }
   return check_launch(what);
 }
@@ -525,13 +567,14 @@ extern "C" int mhc_add_residual_fwd(const void* H_residual, const void* branch_o
   if (B == 0 || S == 0 || D == 0) return MHC_OK;
   if (!H_residual || !branch_output || !H_post || !H_new) return fail(MHC_ERR_NULL_POINTER, "add_residual_fwd: null pointer");
   const int vec = pick_vec(dtype, D, {H_residual, branch_output, H_new});
-  const Geo g = make_geo(S, D, vec, false);
+  Geo g = make_geo(S, D, vec, false);
+  g.reverse = (MHC_REV_MASK >> 2) & 1;
   const int64_t items = B * geo_slots(g);
   if (int e = check_grid("add_residual_fwd", items)) return e;
   cudaStream_t st = (cudaStream_t)stream;
   {
     ProfScope ps("k_add_residual_fwd", st);
-    MHC_DISPATCH(dtype, vec, (k_add_residual_fwd<T, V><<<(unsigned)items, geo_block(g), 0, st>>>(
+    MHC_DISPATCH(dtype, vec, (launch_k(k_add_residual_fwd<T, V>, (unsigned)items, geo_block(g), 0, st, 
                                  (const T*)H_residual, (const T*)branch_output, H_post, (T*)H_new, g)));
   }
   return check_launch("add_residual_fwd");
@@ -551,7 +594,8 @@ extern "C" int mhc_add_residual_bwd(const void* dH_new, const void* branch_outpu
   if (!dH_new || !branch_output || !H_post || !d_branch_output || !scratch)
     return fail(MHC_ERR_NULL_POINTER, "add_residual_bwd: null pointer");
   const int vec = pick_vec(dtype, D, {dH_new, branch_output, d_branch_output});
-  const Geo g = make_geo(S, D, vec, false);
+  Geo g = make_geo(S, D, vec, false);
+  g.reverse = (MHC_REV_MASK >> 3) & 1;
   const int64_t slots = geo_slots(g), items = B * slots;
   if (int e = check_grid("add_residual_bwd", items)) return e;
   if (scratch_bytes < items * 4 * (int64_t)sizeof(float))
@@ -559,7 +603,7 @@ extern "C" int mhc_add_residual_bwd(const void* dH_new, const void* branch_outpu
                 (long long)(items * 4 * sizeof(float)));
   {
     ProfScope ps("k_add_residual_bwd", st);
-    MHC_DISPATCH(dtype, vec, (k_add_residual_bwd<T, V><<<(unsigned)items, geo_block(g), 0, st>>>(
+    MHC_DISPATCH(dtype, vec, (launch_k(k_add_residual_bwd<T, V>, (unsigned)items, geo_block(g), 0, st, 
                                  (const T*)dH_new, (const T*)branch_output, H_post, (T*)d_branch_output,
                                  (float*)scratch, g)));
   }
@@ -632,7 +676,7 @@ extern "C" int mhc_meanpool_fwd(const void* H, float* x, void* scratch, int64_t 
   const int64_t total = B * 4 * D;
   {
     ProfScope ps("k_meanpool_finish", st);
-    k_meanpool_finish<<<(unsigned)((total + 255) / 256), 256, 0, st>>>((const float*)scratch, x, 4 * D, nchunk,
+    launch_k(k_meanpool_finish, (unsigned)((total + 255) / 256), 256, 0, st, (const float*)scratch, x, 4 * D, nchunk,
                                                                         1.0 / (double)S, total);
   }
   return check_launch("meanpool_fwd(finish)");

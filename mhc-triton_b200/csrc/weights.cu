@@ -46,8 +46,9 @@ __device__ __forceinline__ void load_phi_row(const float* __restrict__ phi, int6
 // read of x; with the mean-pool partials as xsrc it finishes the pooling (chunks added in index
 // order, fp64) and writes the pooled state to x_out for the backward.
 __global__ void __launch_bounds__(256)
-k_dw_project(const float* __restrict__ xsrc, int nsrc, float scale, float* __restrict__ x_out,
+k_dw_project(const float* __restrict__ xsrc, int nsrc, double scale, float* __restrict__ x_out,
              const float* __restrict__ phi, float* __restrict__ part, int64_t K, int ks, bool phi_aligned) {
+  pdl_prologue();
   __shared__ float red[32 * kProjW];
   const int64_t row = blockIdx.x / ks;
   const int slice = (int)(blockIdx.x % ks);
@@ -60,11 +61,11 @@ k_dw_project(const float* __restrict__ xsrc, int nsrc, float scale, float* __res
   for (int64_t k = k0 + threadIdx.x; k < k1; k += blockDim.x) {
     float xv;
     if (nsrc == 1) {
-      xv = __ldg(xr + k) * scale;
+      xv = scale == 1.0 ? __ldg(xr + k) : (float)((double)__ldg(xr + k) * scale);
     } else {
       double t = 0.0;
       for (int c = 0; c < nsrc; ++c) t += (double)__ldg(xr + (int64_t)c * K + k);
-      xv = (float)(t * (double)scale);
+      xv = (float)(t * scale);
     }
     if (x_out) x_out[row * K + k] = xv;
     float p[24];
@@ -91,6 +92,7 @@ k_dw_finish(const float* __restrict__ part, BiasPtrs bias, const float* __restri
             const float* __restrict__ alpha_post, const float* __restrict__ alpha_res, float* __restrict__ H_pre,
             float* __restrict__ H_post, float* __restrict__ H_res, float* __restrict__ saved, int64_t K, int ks,
             int iters, float eps) {
+  pdl_prologue();
   __shared__ float s_sc[24];
   const int64_t row = blockIdx.x;
   const int lane = threadIdx.x;
@@ -145,20 +147,14 @@ k_dw_bwd_rows(const float* __restrict__ saved, BiasPtrs bias, const float* __res
               const float* __restrict__ part20, int64_t slots, float* __restrict__ dH_pre,
               const float* __restrict__ dH_post, float* __restrict__ dH_res, float* __restrict__ buf, int64_t K,
               int iters, float eps, float sign_at_zero) {
+  pdl_prologue();
   __shared__ float s_sc[24], s_ds[24], s_up[20];
   __shared__ double s_red[8][20];
   __shared__ float s_state[kMaxStoredIters][40];  // r[4] c[4] mr[16] m_out[16]
   const int64_t row = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (part20) {
-    const float* p = part20 + row * slots * 20;
-    for (int j = 0; j < 20; ++j) {
-      double a = 0.0;
-      for (int64_t s = threadIdx.x; s < slots; s += 256) a += (double)__ldg(p + s * 20 + j);
-      a = warp_sum_f64(a);
-      if (lane == 0) s_red[warp][j] = a;
-    }
-    __syncthreads();
+    block_column_sums_f64(part20 + row * slots * 20, slots, 20, s_red);
     if (threadIdx.x < 20) {
       double t = 0.0;
 #pragma unroll
@@ -278,6 +274,7 @@ k_dw_bwd_main(const float* __restrict__ x, const float* __restrict__ phi, const 
               float* __restrict__ grad_x, float* __restrict__ grad_phi, float* __restrict__ grad_bias,
               float* __restrict__ grad_alpha, int64_t batch, int64_t K, bool phi_aligned, bool gphi_aligned,
               int accumulate) {
+  pdl_prologue();
   __shared__ float s_draw[kRowTile][25];
   if (blockIdx.x == gridDim.x - 1) {  // parameter sums over rows
     const int j = threadIdx.x;
@@ -336,7 +333,7 @@ k_dw_bwd_main(const float* __restrict__ x, const float* __restrict__ phi, const 
 }
 
 // ------------------------------------------------------------------------------ host side
-int weights_fwd_impl(const float* xsrc, int nsrc, float scale, float* x_out, const float* phi, BiasPtrs bias,
+int weights_fwd_impl(const float* xsrc, int nsrc, double scale, float* x_out, const float* phi, BiasPtrs bias,
                      const float* alpha_pre, const float* alpha_post, const float* alpha_res, float* H_pre,
                      float* H_post, float* H_res, float* saved, float* part, int64_t batch, int64_t K, int iters,
                      float eps, cudaStream_t st) {
@@ -344,12 +341,12 @@ int weights_fwd_impl(const float* xsrc, int nsrc, float scale, float* x_out, con
   if (batch * ks > kMaxGridItems) return fail(MHC_ERR_BAD_SHAPE, "dynamic_weights_fwd: batch too large");
   {
     ProfScope ps("k_dw_project", st);
-    k_dw_project<<<(unsigned)(batch * ks), 256, 0, st>>>(xsrc, nsrc, scale, x_out, phi, part, K, ks, is_aligned16(phi));
+    launch_k(k_dw_project, (unsigned)(batch * ks), 256, 0, st, xsrc, nsrc, scale, x_out, phi, part, K, ks, is_aligned16(phi));
   }
   if (int e = check_launch("dynamic_weights_fwd(project)")) return e;
   {
     ProfScope ps("k_dw_finish", st);
-    k_dw_finish<<<(unsigned)batch, 32, 0, st>>>(part, bias, alpha_pre, alpha_post, alpha_res, H_pre, H_post, H_res,
+    launch_k(k_dw_finish, (unsigned)batch, 32, 0, st, part, bias, alpha_pre, alpha_post, alpha_res, H_pre, H_post, H_res,
                                                 saved, K, ks, iters, eps);
   }
   return check_launch("dynamic_weights_fwd(finish)");
@@ -364,7 +361,7 @@ int weights_bwd_impl(const float* x, const float* phi, BiasPtrs bias, const floa
   if (batch) {
     {
       ProfScope ps("k_dw_bwd_rows", st);
-      k_dw_bwd_rows<<<(unsigned)batch, 256, 0, st>>>(saved, bias, alpha_pre, alpha_post, alpha_res, part20, slots,
+      launch_k(k_dw_bwd_rows, (unsigned)batch, 256, 0, st, saved, bias, alpha_pre, alpha_post, alpha_res, part20, slots,
                                                      dH_pre, dH_post, dH_res, buf, K, iters, eps,
                                                      abs_grad_at_zero == MHC_ABS0_PLUS_ONE ? 1.f : 0.f);
     }
@@ -373,7 +370,7 @@ int weights_bwd_impl(const float* x, const float* phi, BiasPtrs bias, const floa
   const int64_t kblocks = (K + 255) / 256;
   {
     ProfScope ps("k_dw_bwd_main", st);
-    k_dw_bwd_main<<<(unsigned)(kblocks + 1), 256, 0, st>>>(x, phi, buf, grad_x, grad_phi, grad_bias, grad_alpha, batch, K,
+    launch_k(k_dw_bwd_main, (unsigned)(kblocks + 1), 256, 0, st, x, phi, buf, grad_x, grad_phi, grad_bias, grad_alpha, batch, K,
                                                            is_aligned16(phi), is_aligned16(grad_phi), accumulate_params);
   }
   return check_launch("dynamic_weights_bwd(main)");
@@ -395,7 +392,7 @@ extern "C" int mhc_dynamic_weights_fwd(const float* x, const float* phi, const f
   if (scratch_bytes < weights_fwd_scratch_bytes(batch, K))
     return fail(MHC_ERR_SCRATCH_TOO_SMALL, "dynamic_weights_fwd: scratch %lld < %lld bytes", (long long)scratch_bytes,
                 (long long)weights_fwd_scratch_bytes(batch, K));
-  return weights_fwd_impl(x, 1, 1.f, nullptr, phi, BiasPtrs{bias, bias + 4, bias + 8}, alpha_pre, alpha_post, alpha_res,
+  return weights_fwd_impl(x, 1, 1.0, nullptr, phi, BiasPtrs{bias, bias + 4, bias + 8}, alpha_pre, alpha_post, alpha_res,
                           H_pre, H_post, H_res, saved, (float*)scratch, batch, K, iters, eps, (cudaStream_t)stream);
 }
 

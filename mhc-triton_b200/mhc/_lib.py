@@ -11,7 +11,8 @@ from ctypes import c_char_p, c_float, c_int, c_int64, c_void_p
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libmhc_b200.so")
+# MHC_B200_LIB overrides the location of the shared object (e.g. a build with other tuning macros).
+LIB_PATH = os.environ.get("MHC_B200_LIB") or os.path.join(_HERE, "libmhc_b200.so")
 
 MHC_F32, MHC_BF16, MHC_F16 = 0, 1, 2
 _DTYPE_CODE = {torch.float32: MHC_F32, torch.bfloat16: MHC_BF16, torch.float16: MHC_F16}
@@ -42,7 +43,7 @@ _PROTOTYPES = {
 
 EXPORTS = sorted(list(_PROTOTYPES) + ["mhc_version", "mhc_last_error_string", "mhc_status_name", "mhc_scratch_bytes",
                                           "mhc_launch_count", "mhc_profile_enable", "mhc_profile_count",
-                                          "mhc_profile_get"])
+                                          "mhc_profile_get", "mhc_profile_select"])
 
 _lib = None
 
@@ -73,6 +74,8 @@ def load():
     lib.mhc_status_name.restype = c_char_p
     lib.mhc_profile_enable.argtypes = [c_int]
     lib.mhc_profile_enable.restype = c_int
+    lib.mhc_profile_select.argtypes = [c_char_p]
+    lib.mhc_profile_select.restype = c_int
     lib.mhc_profile_count.argtypes = []
     lib.mhc_profile_count.restype = c_int64
     lib.mhc_profile_get.argtypes = [c_int64, ctypes.POINTER(c_char_p), ctypes.POINTER(c_float)]
@@ -90,8 +93,10 @@ def call(name, stream, *args):
     return check(getattr(load(), name)(*args, stream))
 
 
-def profile_start():
-    """Start per-kernel timing inside the library (CUDA events around every kernel launch)."""
+def profile_start(only=None):
+    """Start per-kernel timing inside the library (CUDA events around every kernel launch, or
+    around the launches of the kernel named `only`)."""
+    check(load().mhc_profile_select(only.encode() if only else None))
     check(load().mhc_profile_enable(1))
 
 
