@@ -141,6 +141,22 @@ int mhc_add_residual_bwd(const void* dH_new, const void* branch_output, const fl
                          int64_t scratch_bytes, int64_t B, int64_t S, int64_t D, int dtype,
                          mhc_stream_t stream);
 
+/* Same result as mhc_add_residual_bwd for callers that cannot supply scratch memory because they
+ * have no way to allocate on the device (a C/C++ host without a caching allocator whose serving
+ * loop must not call cudaMalloc, or a plugin that only receives input and output buffers).  The
+ * partial sums go to a fixed 1 MiB array inside the library image, which every GPU that loads the
+ * library holds until the process exits; shapes whose partial sums need more
+ * (mhc_scratch_bytes(MHC_OP_ADD_RESIDUAL_BWD, ...) > mhc_add_residual_bwd_noalloc_max_bytes())
+ * are rejected with MHC_ERR_SCRATCH_TOO_SMALL.  The call allocates and frees nothing.  The first
+ * call on each device looks up the array's device address (with that device current) and should
+ * therefore come before any stream capture.  All calls on a device share the one array: two calls
+ * that may overlap on the GPU (different streams) race and must be ordered by the caller.
+ * This entry point has no counterpart in the reference. */
+int mhc_add_residual_bwd_noalloc(const void* dH_new, const void* branch_output, const float* H_post,
+                                 void* d_branch_output, float* dH_post, int64_t B, int64_t S,
+                                 int64_t D, int dtype, mhc_stream_t stream);
+int64_t mhc_add_residual_bwd_noalloc_max_bytes(void);
+
 /* ---- Sequence mean-pool ---------------------------------------------------------
  * x[b, n*D + d] = (1/S) sum_s H[b,s,n,d], fp32 output.
  * Replaces H.mean(dim=1).reshape(B, 4*D), src/mhc/module.py:123. */
