@@ -1,0 +1,77 @@
+"""Two GPU ranks over NCCL: batch-sharded HyperConnection with the in-backward gradient all-reduce
+against the unsharded CPU oracle.  Skipped on boxes with fewer than two GPUs."""
+
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import mhc_oracle as O
+from tests import cases
+from tests.util import to_module
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        import mhc
+        from mhc.parallel import GradSync, shard_batch
+        torch.manual_seed(0)
+        B, S, D = 6, 200, 128
+        H = torch.randn(B, S, 4, D)
+        g = torch.randn(B, S, 4, D)
+        p = cases.perturb_params_(O.default_params(D, 0, 0.1), 3)
+        full = O.layer_fwd_bwd(p, H, g, None, "fused", dtype=torch.float64)
+        hc = to_module(mhc.HyperConnection(dim=D), p).to(dev)
+        sync = GradSync([hc])
+        Hs = shard_batch(H, rank, world).to(dev).requires_grad_(True)
+        gs = shard_batch(g, rank, world).to(dev)
+        lo = sum(shard_batch(H, r, world).shape[0] for r in range(rank))
+        for _ in range(2):                      # the second pass overwrites the record, it must not accumulate
+            Hs.grad = None
+            bi, add = hc(Hs)
+            H_new = add(bi)
+            H_new.backward(gs)
+            sync.finish()
+        torch.cuda.synchronize()
+        n = Hs.shape[0]
+        for k, v in (("branch_input", bi), ("H_new", H_new), ("dH", Hs.grad)):
+            ref = full[k][lo:lo + n]
+            assert (v.double().cpu() - ref).abs().max() <= 2e-6 + 1e-5 * ref.abs().max(), k
+        for name, q_ in hc.named_parameters():
+            ref = full["d" + name]
+            assert (q_.grad.double().cpu() - ref).abs().max() <= 1e-6 + 1e-5 * ref.abs().max(), name
+        q.put((rank, "ok"))
+    except Exception as e:
+        q.put((rank, f"{type(e).__name__}: {e}"))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gpu_sharded_layer_matches_oracle():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for pr in procs:
+        pr.start()
+    results = [q.get(timeout=300) for _ in procs]
+    for pr in procs:
+        pr.join(timeout=60)
+    assert sorted(results) == [(0, "ok"), (1, "ok")], results
