@@ -292,14 +292,11 @@ def main():
         h2d = H_host.numel() * esz * 2
         d2h = H_host.numel() * esz * 2 + out_grads.numel() * 4
 
+        from mhc.host import HostStreamedStep
+        streamed = HostStreamedStep(hc, sync, group=1)
+
         def e2e_step():
-            with torch.no_grad():
-                H.copy_(H_host, non_blocking=True)
-                g.copy_(g_host, non_blocking=True)
-            H_new = step()
-            out_new.copy_(H_new.detach(), non_blocking=True)
-            out_dH.copy_(H.grad, non_blocking=True)
-            out_grads.copy_(sync.flat, non_blocking=True)
+            streamed(H_host, g_host, out_new, out_dH, out_grads)
 
         e2e_step()
         barrier()
@@ -315,7 +312,8 @@ def main():
         e2e_ms = float(t.item()) / args.e2e_steps
         e2e = {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world,
-               "what": "pinned host H and upstream grad -> device, module fwd+bwd, H_new + dH + parameter grads -> pinned host"}
+               "what": "mhc.HostStreamedStep: pinned host H and upstream grad -> device, module fwd+bwd per batch element, "
+                       "H_new + dH + parameter grads -> pinned host, copies overlapped with kernels on three streams"}
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:

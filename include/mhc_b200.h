@@ -145,9 +145,10 @@ int mhc_add_residual_bwd(const void* dH_new, const void* branch_output, const fl
  * have no way to allocate on the device (a C/C++ host without a caching allocator whose serving
  * loop must not call cudaMalloc, or a plugin that only receives input and output buffers).  The
  * partial sums go to a fixed 1 MiB array inside the library image, which every GPU that loads the
- * library holds until the process exits; shapes whose partial sums need more
- * (mhc_scratch_bytes(MHC_OP_ADD_RESIDUAL_BWD, ...) > mhc_add_residual_bwd_noalloc_max_bytes())
- * are rejected with MHC_ERR_SCRATCH_TOO_SMALL.  The call allocates and frees nothing.  The first
+ * library holds until the process exits; shapes whose partial sums need more than
+ * mhc_add_residual_bwd_noalloc_max_bytes() (16 bytes per 4 tokens per group of 256 16-byte packs
+ * along D, per batch element: 256 KiB for bf16 B=8, S=4096, D=4096) are rejected with
+ * MHC_ERR_SCRATCH_TOO_SMALL.  The call allocates and frees nothing.  The first
  * call on each device looks up the array's device address (with that device current) and should
  * therefore come before any stream capture.  All calls on a device share the one array: two calls
  * that may overlap on the GPU (different streams) race and must be ordered by the caller.

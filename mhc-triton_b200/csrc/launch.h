@@ -21,8 +21,10 @@ inline bool is_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p)
 
 // Geometry of a streaming kernel over [B, S, 4, D].
 //   vec   : elements per pack (1 = scalar path for odd D or unaligned pointers)
-//   pool  : the mean-pool kernel (long chunks, sub-groups inside the CTA)
-Geo make_geo(int64_t S, int64_t D, int vec, bool pool);
+//   kind  : Stream = no partial sums (short chunks), Reduce = leaves per-CTA partial sums,
+//           Pool = the mean-pool kernel (long chunks, sub-groups inside the CTA)
+enum class GeoKind { Stream, Reduce, Pool };
+Geo make_geo(int64_t S, int64_t D, int vec, GeoKind kind, int tpc);
 inline int geo_block(const Geo& g) { return g.cols * g.sub; }
 inline int64_t geo_slots(const Geo& g) { return (int64_t)g.nchunk * g.CG; }  // partial rows per batch element
 
@@ -71,6 +73,8 @@ int meanpool_partial_impl(const void* H, float* part, int64_t B, int64_t S, int6
 int mix_bwd_partials_impl(int mode, const void* dbi, const void* dHr, const void* H, const float* H_pre,
                           const float* H_res, void* dH, float* part, int64_t B, int64_t S, int64_t D, int dtype,
                           cudaStream_t st, int64_t* slots);
+int64_t add_residual_bwd_need_bytes(const void* dH_new, const void* bo, const void* dbo, int64_t B, int64_t S,
+                                    int64_t D, int dtype);
 int check_bsd_pub(const char* what, int64_t B, int64_t S, int64_t D, int dtype);
 int mix_bwd_apply_impl(const void* dbi, const void* dHr, const float* H_pre, const float* H_res, const float* gx,
                        float inv_S, void* dH, int64_t B, int64_t S, int64_t D, int dtype, cudaStream_t st);

@@ -55,8 +55,8 @@ extern "C" int64_t mhc_add_residual_bwd_noalloc_max_bytes(void) { return kStatic
 extern "C" int mhc_add_residual_bwd_noalloc(const void* dH_new, const void* branch_output, const float* H_post,
                                             void* d_branch_output, float* dH_post, int64_t B, int64_t S, int64_t D,
                                             int dtype, mhc_stream_t stream) {
-  const int64_t need = mhc_scratch_bytes(MHC_OP_ADD_RESIDUAL_BWD, B, S, D, dtype);
-  if (need < 0) return fail(MHC_ERR_BAD_SHAPE, "add_residual_bwd_noalloc: negative size");
+  if (int e = check_bsd_pub("add_residual_bwd_noalloc", B, S, D, dtype)) return e;
+  const int64_t need = add_residual_bwd_need_bytes(dH_new, branch_output, d_branch_output, B, S, D, dtype);
   if (need > mhc_add_residual_bwd_noalloc_max_bytes())
     return fail(MHC_ERR_SCRATCH_TOO_SMALL,
                 "add_residual_bwd_noalloc: B=%lld S=%lld D=%lld needs %lld bytes of partial sums, the built-in area "

@@ -12,10 +12,10 @@ namespace mhc {
 
 // Tuning knobs (compile-time): software pipelining and minimum resident CTAs per kernel.
 #ifndef MHC_MIXFWD_PIPE
-#define MHC_MIXFWD_PIPE 1
+#define MHC_MIXFWD_PIPE 0
 #endif
 #ifndef MHC_MIXFWD_MINB
-#define MHC_MIXFWD_MINB 3
+#define MHC_MIXFWD_MINB 4
 #endif
 #ifndef MHC_ADDFWD_PIPE
 #define MHC_ADDFWD_PIPE 1
@@ -42,8 +42,24 @@ namespace mhc {
 #ifndef MHC_REV_MASK
 #define MHC_REV_MASK 18
 #endif
-#ifndef MHC_TPC_MAX
-#define MHC_TPC_MAX 32
+#ifndef MHC_MAX_COLS
+#define MHC_MAX_COLS 256
+#endif
+// Tokens per CTA, per kernel.
+#ifndef MHC_TPC_MIXFWD
+#define MHC_TPC_MIXFWD 1
+#endif
+#ifndef MHC_TPC_ADDFWD
+#define MHC_TPC_ADDFWD 1
+#endif
+#ifndef MHC_TPC_APPLY
+#define MHC_TPC_APPLY 8
+#endif
+#ifndef MHC_TPC_ADDBWD
+#define MHC_TPC_ADDBWD 4
+#endif
+#ifndef MHC_TPC_MIXBWD
+#define MHC_TPC_MIXBWD 8
 #endif
 
 template <typename T, int V, int N> struct Bundle { RawPack<T, V> p[N]; };
@@ -56,7 +72,7 @@ __device__ __forceinline__ void unpack(const RawPack<T, V>& r, float (&o)[V]) {
 
 // ------------------------------------------------------------------------------- stream mix
 template <typename T, int V>
-__global__ void __launch_bounds__(256, MHC_MIXFWD_MINB)
+__global__ void __launch_bounds__(MHC_MAX_COLS, MHC_MIXFWD_MINB)
 k_stream_mix_fwd(const T* __restrict__ H, const float* __restrict__ Hpre, const float* __restrict__ Hres,
                  T* __restrict__ bi, T* __restrict__ Hr, Geo g) {
   pdl_prologue();
@@ -96,7 +112,7 @@ k_stream_mix_fwd(const T* __restrict__ H, const float* __restrict__ Hpre, const 
 
 // ------------------------------------------------------------------------------ add residual
 template <typename T, int V>
-__global__ void __launch_bounds__(256, MHC_ADDFWD_MINB)
+__global__ void __launch_bounds__(MHC_MAX_COLS, MHC_ADDFWD_MINB)
 k_add_residual_fwd(const T* __restrict__ Hr, const T* __restrict__ bo, const float* __restrict__ Hpost,
                    T* __restrict__ Hn, Geo g) {
   pdl_prologue();
@@ -132,7 +148,7 @@ k_add_residual_fwd(const T* __restrict__ Hr, const T* __restrict__ bo, const flo
 // d_branch_output[s,d] = sum_n H_post[n] g[s,n,d];  partial dH_post[n] = sum_{s,d} g[s,n,d] bo[s,d].
 // part: [B, slots, 4].
 template <typename T, int V>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(MHC_MAX_COLS)
 k_add_residual_bwd(const T* __restrict__ G, const T* __restrict__ bo, const float* __restrict__ Hpost,
                    T* __restrict__ dbo, float* __restrict__ part, Geo g) {
   pdl_prologue();
@@ -177,7 +193,7 @@ k_add_residual_bwd(const T* __restrict__ G, const T* __restrict__ bo, const floa
 // MODE 0: dH and partials.  MODE 1: partials only (the apply pass writes dH later).
 // part: [B, slots, 20] = dH_pre[4] then dH_res[4][4] row-major.
 template <typename T, int V, int MODE>
-__global__ void __launch_bounds__(256, 2)
+__global__ void __launch_bounds__(MHC_MAX_COLS, 512 / MHC_MAX_COLS)
 k_stream_mix_bwd(const T* __restrict__ dbi, const T* __restrict__ dHr, const T* __restrict__ H,
                  const float* __restrict__ Hpre, const float* __restrict__ Hres, T* __restrict__ dH,
                  float* __restrict__ part, Geo g) {
@@ -239,7 +255,7 @@ k_stream_mix_bwd(const T* __restrict__ dbi, const T* __restrict__ dHr, const T* 
 
 // dH[s,m,d] = H_pre[m] d_bi[s,d] + sum_n H_res[n,m] dH_residual[s,n,d] + inv_S * gx[m*D + d].
 template <typename T, int V>
-__global__ void __launch_bounds__(256, MHC_APPLY_MINB)
+__global__ void __launch_bounds__(MHC_MAX_COLS, MHC_APPLY_MINB)
 k_stream_mix_bwd_apply(const T* __restrict__ dbi, const T* __restrict__ dHr, const float* __restrict__ Hpre,
                        const float* __restrict__ Hres, const float* __restrict__ gx, float inv_S,
                        T* __restrict__ dH, Geo g) {
@@ -252,10 +268,23 @@ k_stream_mix_bwd_apply(const T* __restrict__ dbi, const T* __restrict__ dHr, con
 #pragma unroll
   for (int k = 0; k < 16; ++k) R[k] = __ldg(Hres + it.b * 16 + k);
   const int64_t D = g.D, c0 = (int64_t)it.col * V, tok = it.b * g.S;
+  // this thread's columns of grad_x / S (fp32), 16-byte loads when the pack is a full vector
 #pragma unroll
   for (int m = 0; m < 4; ++m) {
+    const float* gp = gx + it.b * 4 * D + m * D + c0;
+    if (!gx) {
 #pragma unroll
-    for (int e = 0; e < V; ++e) c[m][e] = gx ? inv_S * __ldg(gx + it.b * 4 * D + m * D + c0 + e) : 0.f;
+      for (int e = 0; e < V; ++e) c[m][e] = 0.f;
+    } else if constexpr (V % 4 == 0) {
+#pragma unroll
+      for (int e = 0; e < V; e += 4) {
+        const float4 t = __ldg(reinterpret_cast<const float4*>(gp + e));
+        c[m][e] = inv_S * t.x; c[m][e + 1] = inv_S * t.y; c[m][e + 2] = inv_S * t.z; c[m][e + 3] = inv_S * t.w;
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < V; ++e) c[m][e] = inv_S * __ldg(gp + e);
+    }
   }
   using B5 = Bundle<T, V, 5>;
   for_tokens<MHC_APPLY_PIPE != 0, B5>(
@@ -390,13 +419,14 @@ k_reduce_partials(const float* __restrict__ part, int64_t slots, int W, int W0, 
 }
 
 // -------------------------------------------------------------------------------- host side
-Geo make_geo(int64_t S, int64_t D, int vec, bool pool) {
+Geo make_geo(int64_t S, int64_t D, int vec, GeoKind kind, int tpc) {
   Geo g;
   g.reverse = 0;
   g.S = S;
   g.D = D;
   g.DV = (int32_t)(D / vec);
-  const int max_cols = pool ? MHC_POOL_COLS : 256;
+  const bool pool = kind == GeoKind::Pool;
+  const int max_cols = pool ? MHC_POOL_COLS : MHC_MAX_COLS;
   int cols = 32;
   while (cols < max_cols && cols < g.DV) cols <<= 1;
   g.cols = cols;
@@ -405,10 +435,12 @@ Geo make_geo(int64_t S, int64_t D, int vec, bool pool) {
     g.sub = 256 / cols;
     g.tpc = MHC_POOL_TPC;
   } else {
+    // Tokens per CTA: a per-kernel constant, so the chunking (and with it the layout of the per-CTA
+    // partial sums) depends on S only, never on the batch size.
     g.sub = 1;
-    int64_t t = S / 256;
-    g.tpc = (int32_t)(t < 4 ? 4 : (t > MHC_TPC_MAX ? MHC_TPC_MAX : t));
+    g.tpc = tpc;
   }
+  if (g.tpc > S) g.tpc = (int32_t)(S > 0 ? S : 1);
   g.nchunk = (int32_t)((S + g.tpc - 1) / g.tpc);
   return g;
 }
@@ -452,7 +484,7 @@ static int check_grid(const char* what, int64_t items) {
 int stream_mix_fwd_impl(const void* H, const float* H_pre, const float* H_res, void* bi, void* Hr, int64_t B, int64_t S,
                         int64_t D, int dtype, cudaStream_t st) {
   const int vec = pick_vec(dtype, D, {H, bi, Hr});
-  Geo g = make_geo(S, D, vec, false);
+  Geo g = make_geo(S, D, vec, GeoKind::Stream, MHC_TPC_MIXFWD);
   g.reverse = (MHC_REV_MASK >> 1) & 1;
   const int64_t items = B * geo_slots(g);
   if (int e = check_grid("stream_mix_fwd", items)) return e;
@@ -464,13 +496,13 @@ int stream_mix_fwd_impl(const void* H, const float* H_pre, const float* H_res, v
   return check_launch("stream_mix_fwd");
 }
 
-int64_t meanpool_scratch_floats(int64_t B, int64_t S, int64_t D) { return B * make_geo(S, D, 1, true).nchunk * 4 * D; }
-int64_t mix_bwd_scratch_floats(int64_t B, int64_t S, int64_t D) { return B * geo_slots(make_geo(S, D, 1, false)) * 20; }
+int64_t meanpool_scratch_floats(int64_t B, int64_t S, int64_t D) { return B * make_geo(S, D, 1, GeoKind::Pool, MHC_POOL_TPC).nchunk * 4 * D; }
+int64_t mix_bwd_scratch_floats(int64_t B, int64_t S, int64_t D) { return B * geo_slots(make_geo(S, D, 1, GeoKind::Reduce, MHC_TPC_MIXBWD)) * 20; }
 
 int meanpool_partial_impl(const void* H, float* part, int64_t B, int64_t S, int64_t D, int dtype, cudaStream_t st,
                           int* nchunk) {
   const int vec = pick_vec(dtype, D, {H});
-  Geo g = make_geo(S, D, vec, true);
+  Geo g = make_geo(S, D, vec, GeoKind::Pool, MHC_POOL_TPC);
   g.reverse = MHC_REV_MASK & 1;
   const int64_t items = B * geo_slots(g);
   if (int e = check_grid("meanpool_fwd", items)) return e;
@@ -488,7 +520,7 @@ int mix_bwd_partials_impl(int mode, const void* dbi, const void* dHr, const void
                           const float* H_res, void* dH, float* part, int64_t B, int64_t S, int64_t D, int dtype,
                           cudaStream_t st, int64_t* slots) {
   const int vec = pick_vec(dtype, D, {dbi, dHr, H, dH});
-  Geo g = make_geo(S, D, vec, false);
+  Geo g = make_geo(S, D, vec, GeoKind::Reduce, MHC_TPC_MIXBWD);
   g.reverse = (MHC_REV_MASK >> 4) & 1;
   *slots = geo_slots(g);
   const int64_t items = B * *slots;
@@ -508,7 +540,7 @@ int mix_bwd_partials_impl(int mode, const void* dbi, const void* dHr, const void
 int mix_bwd_apply_impl(const void* dbi, const void* dHr, const float* H_pre, const float* H_res, const float* gx,
                        float inv_S, void* dH, int64_t B, int64_t S, int64_t D, int dtype, cudaStream_t st) {
   const int vec = pick_vec(dtype, D, {dbi, dHr, dH});
-  Geo g = make_geo(S, D, vec, false);
+  Geo g = make_geo(S, D, vec, GeoKind::Stream, MHC_TPC_APPLY);
   g.reverse = (MHC_REV_MASK >> 5) & 1;
   const int64_t items = B * geo_slots(g);
   if (int e = check_grid("stream_mix_bwd_apply", items)) return e;
@@ -518,6 +550,15 @@ int mix_bwd_apply_impl(const void* dbi, const void* dHr, const float* H_pre, con
                                  (const T*)dbi, (const T*)dHr, H_pre, H_res, gx, inv_S, (T*)dH, g)));
   }
   return check_launch("stream_mix_bwd_apply");
+}
+
+// Exact scratch requirement of mhc_add_residual_bwd for these arguments (the pack width, and with it
+// the number of per-CTA partial sums, depends on D and on the alignment of the three tensors).
+int64_t add_residual_bwd_need_bytes(const void* dH_new, const void* bo, const void* dbo, int64_t B, int64_t S,
+                                    int64_t D, int dtype) {
+  if (B <= 0 || S <= 0 || D <= 0) return 0;
+  const int vec = pick_vec(dtype, D, {dH_new, bo, dbo});
+  return B * geo_slots(make_geo(S, D, vec, GeoKind::Reduce, MHC_TPC_ADDBWD)) * 4 * (int64_t)sizeof(float);
 }
 
 int check_bsd_pub(const char* what, int64_t B, int64_t S, int64_t D, int dtype) { return check_bsd(what, B, S, D, dtype); }
@@ -541,7 +582,7 @@ extern "C" int64_t mhc_scratch_bytes(int op, int64_t B, int64_t S, int64_t D, in
   const int64_t f = (int64_t)sizeof(float);
   // Sized for the scalar path (pack width 1), which has the most column groups.
   switch (op) {
-    case MHC_OP_ADD_RESIDUAL_BWD: return B * geo_slots(make_geo(S, D, 1, false)) * 4 * f;
+    case MHC_OP_ADD_RESIDUAL_BWD: return B * geo_slots(make_geo(S, D, 1, GeoKind::Reduce, MHC_TPC_ADDBWD)) * 4 * f;
     case MHC_OP_STREAM_MIX_BWD: return mix_bwd_scratch_floats(B, S, D) * f;
     case MHC_OP_MEANPOOL_FWD: return meanpool_scratch_floats(B, S, D) * f;
     case MHC_OP_DYNAMIC_WEIGHTS_FWD: return weights_fwd_scratch_bytes(B, 4 * D);
@@ -567,7 +608,7 @@ extern "C" int mhc_add_residual_fwd(const void* H_residual, const void* branch_o
   if (B == 0 || S == 0 || D == 0) return MHC_OK;
   if (!H_residual || !branch_output || !H_post || !H_new) return fail(MHC_ERR_NULL_POINTER, "add_residual_fwd: null pointer");
   const int vec = pick_vec(dtype, D, {H_residual, branch_output, H_new});
-  Geo g = make_geo(S, D, vec, false);
+  Geo g = make_geo(S, D, vec, GeoKind::Stream, MHC_TPC_ADDFWD);
   g.reverse = (MHC_REV_MASK >> 2) & 1;
   const int64_t items = B * geo_slots(g);
   if (int e = check_grid("add_residual_fwd", items)) return e;
@@ -594,7 +635,7 @@ extern "C" int mhc_add_residual_bwd(const void* dH_new, const void* branch_outpu
   if (!dH_new || !branch_output || !H_post || !d_branch_output || !scratch)
     return fail(MHC_ERR_NULL_POINTER, "add_residual_bwd: null pointer");
   const int vec = pick_vec(dtype, D, {dH_new, branch_output, d_branch_output});
-  Geo g = make_geo(S, D, vec, false);
+  Geo g = make_geo(S, D, vec, GeoKind::Reduce, MHC_TPC_ADDBWD);
   g.reverse = (MHC_REV_MASK >> 3) & 1;
   const int64_t slots = geo_slots(g), items = B * slots;
   if (int e = check_grid("add_residual_bwd", items)) return e;

@@ -8,6 +8,8 @@ from .module import HyperConnection
 from .ops import (fused_add_residual, fused_dynamic_weights, fused_stream_mix, hyper_connection_mix,
                   sequence_mean_pool, sinkhorn_knopp)
 from ._backward import get_abs_grad_at_zero, set_abs_grad_at_zero
+from .host import HostStreamedStep
+from .parallel import GradSync, shard_batch
 
 __version__ = "0.1.0"
 __all__ = [
@@ -18,6 +20,9 @@ __all__ = [
     "fused_dynamic_weights",
     "hyper_connection_mix",
     "sequence_mean_pool",
+    "HostStreamedStep",
+    "GradSync",
+    "shard_batch",
     "set_abs_grad_at_zero",
     "get_abs_grad_at_zero",
 ]

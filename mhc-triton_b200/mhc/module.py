@@ -51,6 +51,7 @@ class HyperConnection(nn.Module):
         # into it back to back (see mhc.parallel).
         self.grad_sink = None
         self.grads_ready_hook = None
+        self.grad_accumulate = False   # add to grad_sink instead of overwriting it
 
         n = num_streams
         in_dim = n * dim
@@ -108,7 +109,8 @@ class HyperConnection(nn.Module):
         if self.use_fused_weights:
             branch_input, H_residual, H_post, _, _ = hyper_connection_mix(
                 H, self.H_pre_base, self.H_post_base, self.H_res_base, self.phi, self.alpha_pre, self.alpha_post,
-                self.alpha_res, self.sinkhorn_iters, self.eps, self.grad_sink, self.grads_ready_hook)
+                self.alpha_res, self.sinkhorn_iters, self.eps, self.grad_sink, self.grads_ready_hook,
+                self.grad_accumulate)
         else:
             H_post, H_pre, H_res = self._compute_weights(H)
             branch_input, H_residual = fused_stream_mix(H, H_pre, H_res)

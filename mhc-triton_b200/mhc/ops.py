@@ -116,12 +116,13 @@ class _HyperConnectionMix(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, H, H_pre_base, H_post_base, H_res_base, phi, alpha_pre, alpha_post, alpha_res,
-                sinkhorn_iters, eps, grad_sink, ready_hook):
+                sinkhorn_iters, eps, grad_sink, ready_hook, accumulate):
         branch_input, H_residual, H_post, H_pre, H_res, x, saved = hc_mix_forward(
             H, H_pre_base, H_post_base, H_res_base, phi, alpha_pre, alpha_post, alpha_res, sinkhorn_iters, eps)
         ctx.save_for_backward(H, x, phi, H_pre_base, H_post_base, H_res_base, alpha_pre, alpha_post, alpha_res,
                               saved, H_pre, H_res)
         ctx.sinkhorn_iters, ctx.eps, ctx.grad_sink, ctx.ready_hook = sinkhorn_iters, eps, grad_sink, ready_hook
+        ctx.accumulate = bool(accumulate) and grad_sink is not None
         ctx.mark_non_differentiable(H_pre, H_res)
         return branch_input, H_residual, H_post, H_pre, H_res
 
@@ -130,16 +131,16 @@ class _HyperConnectionMix(torch.autograd.Function):
         (H, x, phi, pre_b, post_b, res_b, alpha_pre, alpha_post, alpha_res, saved, H_pre, H_res) = ctx.saved_tensors
         dH, gphi, gbias, galpha = hc_mix_backward(
             d_branch_input, dH_residual, dH_post, H, x, phi, pre_b, post_b, res_b, alpha_pre, alpha_post, alpha_res,
-            saved, H_pre, H_res, ctx.sinkhorn_iters, ctx.eps, param_grads=ctx.grad_sink)
+            saved, H_pre, H_res, ctx.sinkhorn_iters, ctx.eps, param_grads=ctx.grad_sink, accumulate=ctx.accumulate)
         if ctx.ready_hook is not None:
             ctx.ready_hook(ctx.grad_sink)
         if ctx.grad_sink is not None:  # the parameters' .grad tensors are views of the sink already
-            return (dH,) + (None,) * 11
+            return (dH,) + (None,) * 12
         return (dH, gbias[0:4].reshape(pre_b.shape).to(pre_b.dtype), gbias[4:8].reshape(post_b.shape).to(post_b.dtype),
                 gbias[8:24].reshape(res_b.shape).to(res_b.dtype), gphi.to(phi.dtype),
                 galpha[0:1].reshape_as(alpha_pre).to(alpha_pre.dtype),
                 galpha[1:2].reshape_as(alpha_post).to(alpha_post.dtype),
-                galpha[2:3].reshape_as(alpha_res).to(alpha_res.dtype), None, None, None, None)
+                galpha[2:3].reshape_as(alpha_res).to(alpha_res.dtype), None, None, None, None, None)
 
 
 def sinkhorn_knopp(M: torch.Tensor, num_iters: int = 20, eps: float = 1e-8) -> torch.Tensor:
@@ -173,11 +174,13 @@ def sequence_mean_pool(H: torch.Tensor) -> torch.Tensor:
 
 
 def hyper_connection_mix(H, H_pre_base, H_post_base, H_res_base, phi, alpha_pre, alpha_post, alpha_res,
-                         sinkhorn_iters: int = 20, eps: float = 1e-6, grad_sink=None, ready_hook=None):
+                         sinkhorn_iters: int = 20, eps: float = 1e-6, grad_sink=None, ready_hook=None,
+                         accumulate: bool = False):
     """Fused pooled-weights + stream-mix node; returns
     (branch_input, H_residual, H_post, H_pre, H_res); the last two carry no gradient.
     With `grad_sink` the parameter gradients are written into that flat buffer and no
     gradient is returned for the parameters; `ready_hook(grad_sink)` is called as soon as
-    the kernels that fill it have been launched."""
+    the kernels that fill it have been launched; `accumulate` adds to the buffer instead of
+    overwriting it."""
     return _HyperConnectionMix.apply(H, H_pre_base, H_post_base, H_res_base, phi, alpha_pre, alpha_post, alpha_res,
-                                     sinkhorn_iters, eps, grad_sink, ready_hook)
+                                     sinkhorn_iters, eps, grad_sink, ready_hook, accumulate)

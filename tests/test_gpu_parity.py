@@ -377,3 +377,30 @@ def test_unfused_ops_match_fused_node():
     assert_close(Hd.grad, fused["dH"], RT, 2 * AT, "dH")
     for n, q in hc.named_parameters():
         assert_close_norm(q.grad, fused["d" + n], RT, AT, n)
+
+
+def test_host_streamed_step_matches_direct_run():
+    """The host-buffer pipeline (groups of batch elements on three streams, parameter gradients
+    accumulated across groups) reproduces the direct on-device step."""
+    import mhc
+    torch.manual_seed(5)
+    B, S, D = 5, 130, 64
+    H = torch.randn(B, S, 4, D).bfloat16()
+    up = torch.randn(B, S, 4, D).bfloat16()
+    p = cases.perturb_params_(O.default_params(D, 0, 0.1), 12)
+    hc = to_module(mhc.HyperConnection(dim=D), p).to(DEV)
+    direct = _run_module(hc, H, up, lambda t: t)
+    direct = {k: v.clone() for k, v in direct.items()}
+    for q in hc.parameters():
+        q.grad = None
+    step = mhc.HostStreamedStep(hc, group=2)
+    Hh, gh = H.pin_memory(), up.pin_memory()
+    out_new, out_dH = torch.empty_like(Hh).pin_memory(), torch.empty_like(Hh).pin_memory()
+    flat = torch.empty(step.sync.flat.numel()).pin_memory()
+    for _ in range(2):      # the second call must not accumulate on top of the first
+        step(Hh, gh, out_new, out_dH, flat)
+    torch.cuda.synchronize()
+    assert torch.equal(out_new, direct["H_new"].cpu()) and torch.equal(out_dH, direct["dH"].cpu())
+    for n, q in hc.named_parameters():
+        assert_close_norm(q.grad, direct["d" + n], RT, AT, n)
+    assert torch.equal(flat[:4 * D * 24].view(4 * D, 24), hc.phi.grad.cpu())

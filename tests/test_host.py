@@ -53,7 +53,7 @@ def test_scratch_sizes():
     B, S, D = 8, 4096, 4096
     n = lib.mhc_scratch_bytes(_lib.OP_STREAM_MIX_BWD, B, S, D, _lib.MHC_BF16)
     assert 0 < n < 64 << 20
-    assert lib.mhc_scratch_bytes(_lib.OP_ADD_RESIDUAL_BWD, B, S, D, _lib.MHC_BF16) * 5 == n
+    assert 0 < lib.mhc_scratch_bytes(_lib.OP_ADD_RESIDUAL_BWD, B, S, D, _lib.MHC_BF16) <= 4 << 20
     # per-batch-element layout: scratch is linear in B
     assert lib.mhc_scratch_bytes(_lib.OP_MEANPOOL_FWD, 2 * B, S, D, 1) == 2 * lib.mhc_scratch_bytes(_lib.OP_MEANPOOL_FWD, B, S, D, 1)
     assert lib.mhc_scratch_bytes(99, B, S, D, 1) < 0 and lib.mhc_scratch_bytes(0, -1, S, D, 1) < 0

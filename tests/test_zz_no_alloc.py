@@ -58,7 +58,6 @@ def test_noalloc_rejects_oversized_shapes():
     cap = lib.mhc_add_residual_bwd_noalloc_max_bytes()
     assert cap == 1 << 20
     B, S, D = 64, 65536, 8192          # partial sums far beyond the built-in area; no kernel is launched
-    assert lib.mhc_scratch_bytes(L.OP_ADD_RESIDUAL_BWD, B, S, D, L.MHC_BF16) > cap
     t = torch.zeros(16, device="cuda")
     rc = lib.mhc_add_residual_bwd_noalloc(t.data_ptr(), t.data_ptr(), t.data_ptr(), t.data_ptr(), t.data_ptr(),
                                           B, S, D, L.MHC_BF16, None)
