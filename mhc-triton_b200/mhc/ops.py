@@ -39,11 +39,18 @@ class _FusedStreamMix(torch.autograd.Function):
     def forward(ctx, H, H_pre, H_res):
         branch_input, H_residual = stream_mix_forward(H, H_pre, H_res)
         ctx.save_for_backward(H, H_pre, H_res)
+        ctx.set_materialize_grads(False)
         return branch_input, H_residual
 
     @staticmethod
     def backward(ctx, grad_branch_input, grad_H_residual):
         H, H_pre, H_res = ctx.saved_tensors
+        if grad_branch_input is None and grad_H_residual is None:
+            return None, None, None
+        if grad_branch_input is None:
+            grad_branch_input = torch.zeros(H.shape[0], H.shape[1], H.shape[3], device=H.device, dtype=H.dtype)
+        if grad_H_residual is None:
+            grad_H_residual = torch.zeros_like(H)
         dH, dH_pre, dH_res = stream_mix_backward(grad_branch_input, grad_H_residual, H, H_pre, H_res)
         return dH, dH_pre.to(H_pre.dtype), dH_res.to(H_res.dtype)
 
@@ -74,11 +81,19 @@ class _FusedDynamicWeights(torch.autograd.Function):
             x, phi, bias, alpha_pre, alpha_post, alpha_res, sinkhorn_iters, eps, return_saved=True)
         ctx.save_for_backward(x, phi, bias, alpha_pre, alpha_post, alpha_res, saved)
         ctx.sinkhorn_iters, ctx.eps = sinkhorn_iters, eps
+        ctx.set_materialize_grads(False)
         return H_pre, H_post, H_res
 
     @staticmethod
     def backward(ctx, grad_H_pre, grad_H_post, grad_H_res):
         x, phi, bias, alpha_pre, alpha_post, alpha_res, saved = ctx.saved_tensors
+        B = x.shape[0]
+        if grad_H_pre is None:
+            grad_H_pre = torch.zeros(B, 4, device=x.device)
+        if grad_H_post is None:
+            grad_H_post = torch.zeros(B, 4, device=x.device)
+        if grad_H_res is None:
+            grad_H_res = torch.zeros(B, 4, 4, device=x.device)
         gx, gphi, gbias, galpha = fused_dynamic_weights_backward(
             x, phi, bias, alpha_pre, alpha_post, alpha_res, saved, grad_H_pre, grad_H_post, grad_H_res,
             ctx.sinkhorn_iters, ctx.eps)
@@ -124,11 +139,19 @@ class _HyperConnectionMix(torch.autograd.Function):
         ctx.sinkhorn_iters, ctx.eps, ctx.grad_sink, ctx.ready_hook = sinkhorn_iters, eps, grad_sink, ready_hook
         ctx.accumulate = bool(accumulate) and grad_sink is not None
         ctx.mark_non_differentiable(H_pre, H_res)
+        ctx.set_materialize_grads(False)   # no zero-filled gradients for outputs nobody used
         return branch_input, H_residual, H_post, H_pre, H_res
 
     @staticmethod
     def backward(ctx, d_branch_input, dH_residual, dH_post, _unused_pre, _unused_res):
         (H, x, phi, pre_b, post_b, res_b, alpha_pre, alpha_post, alpha_res, saved, H_pre, H_res) = ctx.saved_tensors
+        B, S, _, D = H.shape
+        if d_branch_input is None:
+            d_branch_input = torch.zeros(B, S, D, device=H.device, dtype=H.dtype)
+        if dH_residual is None:
+            dH_residual = torch.zeros_like(H)
+        if dH_post is None:
+            dH_post = torch.zeros(B, 4, device=H.device, dtype=torch.float32)
         dH, gphi, gbias, galpha = hc_mix_backward(
             d_branch_input, dH_residual, dH_post, H, x, phi, pre_b, post_b, res_b, alpha_pre, alpha_post, alpha_res,
             saved, H_pre, H_res, ctx.sinkhorn_iters, ctx.eps, param_grads=ctx.grad_sink, accumulate=ctx.accumulate)

@@ -404,3 +404,75 @@ def test_host_streamed_step_matches_direct_run():
     for n, q in hc.named_parameters():
         assert_close_norm(q.grad, direct["d" + n], RT, AT, n)
     assert torch.equal(flat[:4 * D * 24].view(4 * D, 24), hc.phi.grad.cpu())
+
+
+def test_layer_stack_with_mlp_branches():
+    """Reduced form of the 16-layer configuration: a stack of dynamic layers, each wrapping a
+    2-layer SiLU MLP branch, fp32, against the oracle chained the same way."""
+    import mhc
+    torch.manual_seed(11)
+    B, S, D, Lyr = 2, 48, 64, 3
+    H = torch.randn(B, S, 4, D)
+    up = torch.randn(B, S, 4, D)
+    params = [cases.perturb_params_(O.default_params(D, i, 0.1), 30 + i) for i in range(Lyr)]
+    W1 = [torch.randn(D, 4 * D) / D ** 0.5 for _ in range(Lyr)]
+    W2 = [torch.randn(4 * D, D) / (4 * D) ** 0.5 for _ in range(Lyr)]
+
+    def run(make_layer, mm, Hin, g):
+        Hin = Hin.requires_grad_(True)
+        layers = [make_layer(i) for i in range(Lyr)]
+        h = Hin
+        for i, lay in enumerate(layers):
+            bi, add = lay(h)
+            h = add(torch.nn.functional.silu(bi @ mm(W1[i])) @ mm(W2[i]))
+        h.backward(g)
+        return h, Hin.grad, layers
+
+    # oracle chain in fp64
+    leaves = [{k: v.double().requires_grad_(True) for k, v in p.tensors().items()} for p in params]
+
+    def oracle_layer(i):
+        lp = O.LayerParams(**leaves[i])
+
+        def fwd(h):
+            H_pre, H_post, H_res = O.layer_weights(lp, h, "fused", 20, 1e-6)
+            bi, Hr = O.stream_mix(h, H_pre, H_res)
+            return bi, lambda bo: O.add_residual(Hr, bo, H_post)
+        return fwd
+
+    out_ref, dH_ref, _ = run(oracle_layer, lambda w: w.double(), H.double(), up.double())
+    out, dH, layers = run(lambda i: to_module(mhc.HyperConnection(dim=D, layer_idx=i), params[i]).to(DEV),
+                          lambda w: w.to(DEV), dev(H), dev(up))
+    assert_close_norm(out, out_ref, RT, AT, "H_out"); assert_close_norm(dH, dH_ref, 1e-4, AT, "dH")
+    for i, lay in enumerate(layers):
+        for n, q in lay.named_parameters():
+            assert_close_norm(q.grad, leaves[i][n].grad, 1e-4, AT, f"layer{i}.{n}")
+
+
+def test_unused_outputs_get_no_gradient_buffers():
+    """Only one of an op's outputs feeds the loss: the missing upstream gradients count as zero."""
+    import mhc
+    torch.manual_seed(2)
+    B, S, D = 2, 20, 32
+    H = torch.randn(B, S, 4, D)
+    H_pre = torch.softmax(torch.randn(B, 4), -1)
+    H_res = O.sinkhorn(torch.randn(B, 4, 4))
+    g = torch.randn(B, S, D)
+    ref = [t.clone().double().requires_grad_(True) for t in (H, H_pre, H_res)]
+    (O.stream_mix(*ref)[0] * g.double()).sum().backward()
+    lv = [dev(t).requires_grad_(True) for t in (H, H_pre, H_res)]
+    (mhc.fused_stream_mix(*lv)[0] * dev(g)).sum().backward()
+    assert_close(lv[0].grad, ref[0].grad, RT, 2 * AT); assert_close_norm(lv[1].grad, ref[1].grad, RT, AT)
+    assert float(lv[2].grad.abs().max()) == 0.0
+    # module: loss on branch_input only (add_residual never called)
+    p = cases.perturb_params_(O.default_params(D, 0, 0.1), 9)
+    hc = to_module(mhc.HyperConnection(dim=D), p).to(DEV)
+    Hd = dev(H).requires_grad_(True)
+    bi, _ = hc(Hd)
+    (bi * dev(g)).sum().backward()
+    leaves = {k: v.double().requires_grad_(True) for k, v in p.tensors().items()}
+    Hl = H.double().requires_grad_(True)
+    a, b_, c = O.layer_weights(O.LayerParams(**leaves), Hl, "fused", 20, 1e-6)
+    (O.stream_mix(Hl, a, c)[0] * g.double()).sum().backward()
+    assert_close(Hd.grad, Hl.grad, RT, 2 * AT, "dH")
+    assert_close_norm(hc.phi.grad, leaves["phi"].grad, 1e-4, AT, "dphi")
