@@ -86,7 +86,7 @@ k_stream_mix_fwd(const T* __restrict__ H, const float* __restrict__ Hpre, const 
   const int64_t D = g.D, c0 = (int64_t)it.col * V, tok = it.b * g.S;
   using B4 = Bundle<T, V, 4>;
   for_tokens<MHC_MIXFWD_PIPE != 0, B4>(
-      it.s0, it.s1, 1,
+      it.s0 + it.sub, it.s1, g.sub,
       [&](B4& u, int64_t s) {
         const T* h = H + (tok + s) * 4 * D + c0;
 #pragma unroll
@@ -124,7 +124,7 @@ k_add_residual_fwd(const T* __restrict__ Hr, const T* __restrict__ bo, const flo
   const int64_t D = g.D, c0 = (int64_t)it.col * V, tok = it.b * g.S;
   using B5 = Bundle<T, V, 5>;
   for_tokens<MHC_ADDFWD_PIPE != 0, B5>(
-      it.s0, it.s1, 1,
+      it.s0 + it.sub, it.s1, g.sub,
       [&](B5& u, int64_t s) {
         const T* r = Hr + (tok + s) * 4 * D + c0;
         u.p[4] = ld_raw<T, V>(bo + (tok + s) * D + c0);
@@ -162,7 +162,7 @@ k_add_residual_bwd(const T* __restrict__ G, const T* __restrict__ bo, const floa
     const int64_t D = g.D, c0 = (int64_t)it.col * V, tok = it.b * g.S;
     using B5 = Bundle<T, V, 5>;
     for_tokens_pipelined<B5>(
-        it.s0, it.s1, 1,
+        it.s0 + it.sub, it.s1, g.sub,
         [&](B5& u, int64_t s) {
           const T* gp = G + (tok + s) * 4 * D + c0;
           u.p[4] = ld_raw<T, V>(bo + (tok + s) * D + c0);
@@ -214,7 +214,7 @@ k_stream_mix_bwd(const T* __restrict__ dbi, const T* __restrict__ dHr, const T* 
     const int64_t D = g.D, c0 = (int64_t)it.col * V, tok = it.b * g.S;
     using B9 = Bundle<T, V, 9>;  // 0..3 H rows, 4..7 dH_residual rows, 8 d_branch_input
     for_tokens_pipelined<B9>(
-        it.s0, it.s1, 1,
+        it.s0 + it.sub, it.s1, g.sub,
         [&](B9& u, int64_t s) {
           const int64_t o4 = (tok + s) * 4 * D + c0;
           u.p[8] = ld_raw<T, V>(dbi + (tok + s) * D + c0);
@@ -288,7 +288,7 @@ k_stream_mix_bwd_apply(const T* __restrict__ dbi, const T* __restrict__ dHr, con
   }
   using B5 = Bundle<T, V, 5>;
   for_tokens<MHC_APPLY_PIPE != 0, B5>(
-      it.s0, it.s1, 1,
+      it.s0 + it.sub, it.s1, g.sub,
       [&](B5& u, int64_t s) {
         const T* rp = dHr + (tok + s) * 4 * D + c0;
         u.p[4] = ld_raw<T, V>(dbi + (tok + s) * D + c0);
@@ -437,8 +437,9 @@ Geo make_geo(int64_t S, int64_t D, int vec, GeoKind kind, int tpc) {
   } else {
     // Tokens per CTA: a per-kernel constant, so the chunking (and with it the layout of the per-CTA
     // partial sums) depends on S only, never on the batch size.
-    g.sub = 1;
-    g.tpc = tpc;
+    // Narrow rows (fewer than 256 packs): the CTA keeps 256 threads by walking 256/cols tokens abreast.
+    g.sub = MHC_MAX_COLS / cols;
+    g.tpc = tpc * g.sub;
   }
   if (g.tpc > S) g.tpc = (int32_t)(S > 0 ? S : 1);
   g.nchunk = (int32_t)((S + g.tpc - 1) / g.tpc);
