@@ -1,10 +1,21 @@
 // Sinkhorn-Knopp projection of batches of 4x4 matrices: one thread owns one matrix, which
 // never leaves its registers.  Forward = `iters` row/column normalisations of |M| + eps;
 // backward = reverse sweep that re-derives each iteration's state from M (no saved state).
+#include <cstdlib>
+
 #include "common.cuh"
 #include "launch.h"
 
 namespace mhc {
+
+// MHC_SINKHORN_PLAIN=1 in the environment selects the plain O(iters^2) sweep (for cross-checks).
+static bool sinkhorn_plain_sweep() {
+  static const bool on = [] {
+    const char* e = std::getenv("MHC_SINKHORN_PLAIN");
+    return e && e[0] == '1';
+  }();
+  return on;
+}
 
 template <typename T>
 __device__ __forceinline__ void load_matrix(const T* __restrict__ p, float (&m)[16], bool aligned) {
@@ -83,6 +94,55 @@ __global__ void __launch_bounds__(128) k_sinkhorn_bwd(const T* __restrict__ M, c
   store_matrix(dM + i * 16, d, aligned);
 }
 
+// Same reverse sweep with kCk register-resident checkpoints: the iterations are cut into kCk + 1
+// segments of L = ceil(iters / (kCk + 1)); one forward sweep stores the state entering each
+// segment, and the state entering iteration t is then recomputed from its segment's checkpoint
+// (at most L - 1 steps) instead of from M (t steps).  The recomputation runs the same step
+// function from the same values, so the result is bit-identical to k_sinkhorn_bwd, for about
+// iters * (L + 3) / 2 steps instead of iters * (iters + 1) / 2.  Still nothing but M and dP is read.
+constexpr int kCk = 4;
+template <typename T>
+__global__ void __launch_bounds__(128) k_sinkhorn_bwd_ck(const T* __restrict__ M, const T* __restrict__ dP,
+                                                         T* __restrict__ dM, int64_t batch, int iters, int L,
+                                                         float eps, float sign_at_zero, bool aligned) {
+  pdl_prologue();
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= batch) return;
+  float m0[16], d[16], ck[kCk][16];
+  load_matrix(M + i * 16, m0, aligned);
+  load_matrix(dP + i * 16, d, aligned);
+  {
+    float m[16];
+#pragma unroll
+    for (int k = 0; k < 16; ++k) m[k] = fabsf(m0[k]) + eps;
+#pragma unroll
+    for (int k = 0; k < kCk; ++k) {
+      const int t1 = min((k + 1) * L, iters);
+      for (int t = k * L; t < t1; ++t) sinkhorn_step(m, eps);
+#pragma unroll
+      for (int e = 0; e < 16; ++e) ck[k][e] = m[e];  // state entering iteration (k + 1) * L
+    }
+  }
+#pragma unroll
+  for (int k = kCk; k >= 0; --k) {
+    const int t0 = k * L, t1 = min((k + 1) * L, iters);
+    for (int t = t1 - 1; t >= t0; --t) {
+      float m[16], r[4], c[4], mr[16];
+#pragma unroll
+      for (int e = 0; e < 16; ++e) m[e] = k == 0 ? fabsf(m0[e]) + eps : ck[k == 0 ? 0 : k - 1][e];
+      for (int f = t0; f < t; ++f) sinkhorn_step(m, eps);
+      sinkhorn_step(m, eps, r, mr, c);
+      sinkhorn_step_bwd(d, m, r, mr, c);
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < 16; ++k) {
+    const float sg = m0[k] > 0.f ? 1.f : (m0[k] < 0.f ? -1.f : sign_at_zero);
+    d[k] *= sg;
+  }
+  store_matrix(dM + i * 16, d, aligned);
+}
+
 template <typename T>
 static int launch_fwd(const void* M, void* P, int64_t batch, int iters, float eps, cudaStream_t st) {
   const bool aligned = is_aligned16(M) && is_aligned16(P);
@@ -101,10 +161,15 @@ static int launch_bwd(const void* M, const void* dP, void* dM, int64_t batch, in
   const bool aligned = is_aligned16(M) && is_aligned16(dP) && is_aligned16(dM);
   const int block = 128;
   const int64_t grid = (batch + block - 1) / block;
-  {
+  if (sinkhorn_plain_sweep()) {
     ProfScope ps("k_sinkhorn_bwd", st);
     launch_k(k_sinkhorn_bwd<T>, (unsigned)grid, block, 0, st, (const T*)M, (const T*)dP, (T*)dM, batch, iters, eps, sz,
-                                                         aligned);
+             aligned);
+  } else {
+    ProfScope ps("k_sinkhorn_bwd_ck", st);
+    const int L = (iters + kCk) / (kCk + 1);
+    launch_k(k_sinkhorn_bwd_ck<T>, (unsigned)grid, block, 0, st, (const T*)M, (const T*)dP, (T*)dM, batch, iters, L, eps,
+             sz, aligned);
   }
   return check_launch("sinkhorn_bwd");
 }

@@ -476,3 +476,33 @@ def test_unused_outputs_get_no_gradient_buffers():
     (O.stream_mix(Hl, a, c)[0] * g.double()).sum().backward()
     assert_close(Hd.grad, Hl.grad, RT, 2 * AT, "dH")
     assert_close_norm(hc.phi.grad, leaves["phi"].grad, 1e-4, AT, "dphi")
+
+
+def test_sinkhorn_backward_checkpointed_equals_plain_sweep(tmp_path):
+    """The default backward (register checkpoints) is bit-identical to the plain O(T^2) sweep,
+    which a child process selects through the environment."""
+    import os
+    import subprocess
+    import sys
+    from mhc import sinkhorn_knopp
+    from tests.conftest import PKG_DIR, ROOT
+    out = tmp_path / "plain.pt"
+    code = (
+        "import sys, torch\n"
+        f"sys.path.insert(0, {PKG_DIR!r})\n"
+        "from mhc._backward import sinkhorn_backward\n"
+        "torch.manual_seed(3)\n"
+        "res = {}\n"
+        "for T in (1, 3, 4, 5, 20, 23):\n"
+        "    M = torch.randn(1000, 4, 4); dP = torch.randn(1000, 4, 4)\n"
+        "    res[T] = sinkhorn_backward(M.cuda(), dP.cuda(), T, 1e-6).cpu()\n"
+        f"torch.save(res, {str(out)!r})\n")
+    env = dict(os.environ, MHC_SINKHORN_PLAIN="1")
+    subprocess.run([sys.executable, "-c", code], check=True, env=env, cwd=ROOT)
+    plain = torch.load(out)
+    from mhc._backward import sinkhorn_backward
+    torch.manual_seed(3)
+    for T in (1, 3, 4, 5, 20, 23):
+        M = torch.randn(1000, 4, 4); dP = torch.randn(1000, 4, 4)
+        got = sinkhorn_backward(M.cuda(), dP.cuda(), T, 1e-6).cpu()
+        assert torch.equal(got, plain[T]), T
