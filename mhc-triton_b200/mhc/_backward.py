@@ -103,9 +103,10 @@ def stream_mix_backward_reduce(d_branch_input, dH_residual, H) -> Tuple[torch.Te
 
 
 def stream_mix_backward_apply(d_branch_input, dH_residual, H_pre, H_res, grad_x: Optional[torch.Tensor],
-                              like: torch.Tensor) -> torch.Tensor:
-    """dH = mix-transpose of the upstream gradients + grad_x / S broadcast over the sequence
-    (second pass; grad_x is the fp32 [B, 4*D] gradient of the pooled state, or None)."""
+                              like: torch.Tensor, inv_S: Optional[float] = None) -> torch.Tensor:
+    """dH = mix-transpose of the upstream gradients + grad_x * inv_S broadcast over the sequence
+    (second pass; grad_x is the fp32 [B, 4*D] gradient of the pooled state, or None; inv_S
+    defaults to 1 / S of `like` and is 1 / (global sequence length) under sequence sharding)."""
     B, S, _, D = like.shape
     d_bi = d_branch_input.to(like.dtype).contiguous()
     dHr = dH_residual.to(like.dtype).contiguous()
@@ -116,7 +117,7 @@ def stream_mix_backward_apply(d_branch_input, dH_residual, H_pre, H_res, grad_x:
     dH = torch.empty_like(like, memory_format=torch.contiguous_format)
     with torch.cuda.device(like.device):
         L.call("mhc_stream_mix_bwd_apply", L.stream_of(like), L.ptr(d_bi), L.ptr(dHr), L.ptr(H_pre), L.ptr(H_res), L.ptr(grad_x),
-                                                  1.0 / S, L.ptr(dH), B, S, D, L.dtype_code(like))
+                                                  (1.0 / S) if inv_S is None else float(inv_S), L.ptr(dH), B, S, D, L.dtype_code(like))
     return dH
 
 

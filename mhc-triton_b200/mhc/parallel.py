@@ -45,7 +45,8 @@ class GradSync:
         sync.finish()                      # before the optimizer reads .grad
     """
 
-    def __init__(self, layers: Iterable[torch.nn.Module], process_group=None, overlap: bool = True):
+    def __init__(self, layers: Iterable[torch.nn.Module], process_group=None, overlap: bool = True,
+                 check_ranks: bool = True):
         self.layers: List[torch.nn.Module] = list(layers)
         if not self.layers:
             raise ValueError("GradSync needs at least one layer")
@@ -77,6 +78,8 @@ class GradSync:
             l.alpha_post.grad = rec[K24 + 25:K24 + 26]
             l.alpha_res.grad = rec[K24 + 26:K24 + 27]
             self.records.append(rec)
+        if check_ranks and self._distributed():
+            self._check_same_layout(sizes)
         self.overlap = overlap and dev.type == "cuda"
         self.side = torch.cuda.Stream(device=dev) if self.overlap else None
         self._pending = []
@@ -97,6 +100,16 @@ class GradSync:
         else:
             dist.all_reduce(rec, op=dist.ReduceOp.SUM, group=self.group)
 
+    def _check_same_layout(self, sizes) -> None:
+        """Every rank must reduce records of the same sizes in the same order; a mismatch (different
+        layer count or width on some rank) would otherwise corrupt gradients or hang the collective.
+        All ranks learn of it here, on the host, and all raise."""
+        world = dist.get_world_size(self.group)
+        seen = [None] * world
+        dist.all_gather_object(seen, list(sizes), group=self.group)
+        if any(s != seen[0] for s in seen):
+            raise ValueError(f"GradSync: ranks disagree on the gradient record layout: {seen}")
+
     def _distributed(self) -> bool:
         return dist.is_available() and dist.is_initialized() and dist.get_world_size(self.group) > 1
 
@@ -113,3 +126,90 @@ class GradSync:
 
     def zero(self) -> None:
         self.flat.zero_()
+
+
+# ---------------------------------------------------------------------------------------------
+# Sequence sharding: every rank holds a slice [B, S_local, 4, D] of every sequence.  The mixing
+# weights depend on the mean over the WHOLE sequence, so the forward needs one small all-reduce
+# (the pooled state, [B, 4*D] fp32) and the backward one more (the 24 weight gradients per batch
+# element, [B, 24] fp32).  Activations never move.  Parameter gradients come out complete and
+# identical on every rank of the sequence group: do not sum them over that group again.
+# ---------------------------------------------------------------------------------------------
+class _SequenceShardedMix(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, H, H_pre_base, H_post_base, H_res_base, phi, alpha_pre, alpha_post, alpha_res, sinkhorn_iters,
+                eps, group, total_len):
+        from ._kernels import fused_dynamic_weights_forward, meanpool_forward, stream_mix_forward
+        S_local = H.shape[1]
+        x = meanpool_forward(H) * (S_local / total_len)
+        if _group_size(group) > 1:
+            dist.all_reduce(x, op=dist.ReduceOp.SUM, group=group)
+        bias = torch.cat([H_pre_base.reshape(-1), H_post_base.reshape(-1), H_res_base.reshape(-1)]).float()
+        H_pre, H_post, H_res, saved = fused_dynamic_weights_forward(
+            x, phi, bias, alpha_pre, alpha_post, alpha_res, sinkhorn_iters, eps, return_saved=True)
+        branch_input, H_residual = stream_mix_forward(H, H_pre, H_res)
+        ctx.save_for_backward(H, x, phi, bias, alpha_pre, alpha_post, alpha_res, saved, H_pre, H_res)
+        ctx.meta = (sinkhorn_iters, eps, group, total_len, H_pre_base.shape, H_post_base.shape, H_res_base.shape)
+        ctx.mark_non_differentiable(H_pre, H_res)
+        ctx.set_materialize_grads(False)
+        return branch_input, H_residual, H_post, H_pre, H_res
+
+    @staticmethod
+    def backward(ctx, d_bi, dHr, dH_post, _a, _b):
+        from ._backward import (fused_dynamic_weights_backward, stream_mix_backward_apply,
+                                stream_mix_backward_reduce)
+        H, x, phi, bias, alpha_pre, alpha_post, alpha_res, saved, H_pre, H_res = ctx.saved_tensors
+        iters, eps, group, total_len, s_pre, s_post, s_res = ctx.meta
+        B, S, _, D = H.shape
+        if d_bi is None:
+            d_bi = torch.zeros(B, S, D, device=H.device, dtype=H.dtype)
+        if dHr is None:
+            dHr = torch.zeros_like(H)
+        if dH_post is None:
+            dH_post = torch.zeros(B, 4, device=H.device)
+        dH_pre, dH_res = stream_mix_backward_reduce(d_bi, dHr, H)
+        packed = torch.cat([dH_pre, dH_post.float(), dH_res.reshape(B, 16)], dim=1).contiguous()
+        if _group_size(group) > 1:
+            dist.all_reduce(packed, op=dist.ReduceOp.SUM, group=group)
+        gx, gphi, gbias, galpha = fused_dynamic_weights_backward(
+            x, phi, bias, alpha_pre, alpha_post, alpha_res, saved, packed[:, 0:4], packed[:, 4:8],
+            packed[:, 8:24].reshape(B, 4, 4), iters, eps)
+        dH = stream_mix_backward_apply(d_bi, dHr, H_pre, H_res, gx, H, inv_S=1.0 / total_len)
+        return (dH, gbias[0:4].reshape(s_pre), gbias[4:8].reshape(s_post), gbias[8:24].reshape(s_res),
+                gphi.to(phi.dtype), galpha[0:1].reshape_as(alpha_pre), galpha[1:2].reshape_as(alpha_post),
+                galpha[2:3].reshape_as(alpha_res), None, None, None, None)
+
+
+def _group_size(group) -> int:
+    if not (dist.is_available() and dist.is_initialized()):
+        return 1
+    return dist.get_world_size(group)
+
+
+class SequenceShardedHyperConnection(torch.nn.Module):
+    """Wraps a fused dynamic HyperConnection for inputs sharded along the sequence axis.
+
+    forward(H_local) takes this rank's [B, S_local, 4, D] slice and returns
+    (branch_input_local, add_residual) exactly like the wrapped layer; `total_len` is the global
+    sequence length (default: S_local times the group size).  Use it when the batch is smaller
+    than the number of GPUs or one sequence does not fit one GPU.
+    """
+
+    def __init__(self, layer: torch.nn.Module, process_group=None, total_len: Optional[int] = None):
+        super().__init__()
+        if not getattr(layer, "use_fused_weights", False):
+            raise ValueError("sequence sharding supports fused dynamic HyperConnection layers only")
+        self.layer, self.group, self.total_len = layer, process_group, total_len
+
+    def forward(self, H: torch.Tensor):
+        from .ops import fused_add_residual
+        l = self.layer
+        total = self.total_len if self.total_len is not None else H.shape[1] * _group_size(self.group)
+        branch_input, H_residual, H_post, _, _ = _SequenceShardedMix.apply(
+            H, l.H_pre_base, l.H_post_base, l.H_res_base, l.phi, l.alpha_pre, l.alpha_post, l.alpha_res,
+            l.sinkhorn_iters, l.eps, self.group, total)
+
+        def add_residual(branch_output: torch.Tensor) -> torch.Tensor:
+            return fused_add_residual(H_residual, branch_output, H_post)
+
+        return branch_input, add_residual

@@ -62,6 +62,61 @@ def _worker(rank, world, port, q):
         dist.destroy_process_group()
 
 
+def _seq_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        import mhc
+        from mhc.parallel import SequenceShardedHyperConnection
+        torch.manual_seed(1)
+        B, S, D = 3, 192, 64                     # fewer sequences than would keep 8 GPUs busy: shard the sequence
+        H = torch.randn(B, S, 4, D)
+        g = torch.randn(B, S, 4, D)
+        p = cases.perturb_params_(O.default_params(D, 0, 0.1), 4)
+        full = O.layer_fwd_bwd(p, H, g, None, "fused", dtype=torch.float64)
+        hc = to_module(mhc.HyperConnection(dim=D), p).to(dev)
+        sp = SequenceShardedHyperConnection(hc)
+        Sl = S // world
+        sl = slice(rank * Sl, (rank + 1) * Sl)
+        Hs = H[:, sl].contiguous().to(dev).requires_grad_(True)
+        bi, add = sp(Hs)
+        H_new = add(bi)
+        H_new.backward(g[:, sl].contiguous().to(dev))
+        torch.cuda.synchronize()
+        for k, v in (("branch_input", bi), ("H_new", H_new), ("dH", Hs.grad)):
+            ref = full[k][:, sl]
+            assert (v.double().cpu() - ref).abs().max() <= 2e-6 + 1e-5 * ref.abs().max(), k
+        for name, q_ in hc.named_parameters():     # complete on every rank, no further reduction
+            ref = full["d" + name]
+            assert (q_.grad.double().cpu() - ref).abs().max() <= 1e-6 + 1e-5 * ref.abs().max(), name
+        q.put((rank, "ok"))
+    except Exception as e:
+        q.put((rank, f"{type(e).__name__}: {e}"))
+    finally:
+        dist.destroy_process_group()
+
+
+def _spawn2(worker):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=worker, args=(r, 2, port, q)) for r in range(2)]
+    for pr in procs:
+        pr.start()
+    results = [q.get(timeout=300) for _ in procs]
+    for pr in procs:
+        pr.join(timeout=60)
+    assert sorted(results) == [(0, "ok"), (1, "ok")], results
+
+
+def test_two_gpu_sequence_sharded_layer_matches_oracle():
+    _spawn2(_seq_worker)
+
+
 def test_two_gpu_sharded_layer_matches_oracle():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")

@@ -506,3 +506,22 @@ def test_sinkhorn_backward_checkpointed_equals_plain_sweep(tmp_path):
         M = torch.randn(1000, 4, 4); dP = torch.randn(1000, 4, 4)
         got = sinkhorn_backward(M.cuda(), dP.cuda(), T, 1e-6).cpu()
         assert torch.equal(got, plain[T]), T
+
+
+def test_sequence_sharded_wrapper_single_rank_equals_layer():
+    """With one rank the sequence-sharded wrapper is the layer itself (same kernels, unfused chain)."""
+    import mhc
+    from mhc.parallel import SequenceShardedHyperConnection
+    torch.manual_seed(6)
+    B, S, D = 2, 90, 64
+    H = torch.randn(B, S, 4, D)
+    up = torch.randn(B, S, 4, D)
+    p = cases.perturb_params_(O.default_params(D, 0, 0.1), 14)
+    hc = to_module(mhc.HyperConnection(dim=D), p).to(DEV)
+    a = {k: v.clone() for k, v in _run_module(hc, H, up, lambda t: t).items()}
+    b = _run_module(SequenceShardedHyperConnection(hc), H, up, lambda t: t)
+    for k in ("branch_input", "H_new"):
+        assert torch.equal(a[k], b[k]), k
+    assert_close(b["dH"], a["dH"], RT, 2 * AT, "dH")
+    for n, _ in hc.named_parameters():
+        assert_close_norm(b["dlayer." + n], a["d" + n], RT, AT, n)

@@ -107,3 +107,37 @@ def test_gradsync_rejects_unsupported_layers():
         GradSync([mhc.HyperConnection(dim=8, dynamic=False)])
     with pytest.raises(ValueError):
         GradSync([mhc.HyperConnection(dim=8).half()])
+
+
+def _mismatch_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    import datetime
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+    try:
+        import mhc
+        from mhc.parallel import GradSync
+        layers = [mhc.HyperConnection(dim=16 if rank == 0 else 32)]     # rank 1 was built with another width
+        try:
+            GradSync(layers)
+            q.put((rank, "no error"))
+        except ValueError as e:
+            q.put((rank, "ValueError" if "disagree" in str(e) else str(e)))
+    except Exception as e:
+        q.put((rank, f"{type(e).__name__}: {e}"))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_mismatched_layers_are_reported_on_every_rank():
+    """A configuration fault injected on the host: ranks built with different layer widths.  The
+    check runs before any collective on gradients, so nothing hangs and every rank raises."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_mismatch_worker, args=(r, 2, port, q)) for r in range(2)]
+    for pr in procs:
+        pr.start()
+    results = [q.get(timeout=120) for _ in procs]
+    for pr in procs:
+        pr.join(timeout=60)
+    assert sorted(results) == [(0, "ValueError"), (1, "ValueError")], results
