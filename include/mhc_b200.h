@@ -137,6 +137,16 @@ int mhc_add_residual_fwd(const void* H_residual, const void* branch_output, cons
                          void* H_new, int64_t B, int64_t S, int64_t D, int dtype,
                          mhc_stream_t stream);
 
+/* Add residual that also leaves, for the next layer, the token sums of the H_new it writes:
+ * pool_partials [B, mhc_add_residual_pool_chunks(S, D), 4*D] fp32, to be handed to that layer's
+ * mhc_hc_mix_fwd as pooled_partials.  The next layer then reads H once instead of twice
+ * (the reference reads it twice: H.mean(dim=1), src/mhc/module.py:123, then the stream-mix
+ * kernel, src/mhc/_kernels.py:137-236).  H_new is identical to mhc_add_residual_fwd's. */
+int mhc_add_residual_pool_fwd(const void* H_residual, const void* branch_output, const float* H_post,
+                              void* H_new, float* pool_partials, int64_t B, int64_t S, int64_t D,
+                              int dtype, mhc_stream_t stream);
+int64_t mhc_add_residual_pool_chunks(int64_t S, int64_t D);
+
 /* d_branch_output and dH_post [B,4] (fp32).  dH_residual equals dH_new and is not written:
  * the caller aliases it.  Replaces add_residual_backward, src/mhc/_backward.py:533-575
  * (kernel :269-351) including its torch.sum (:573). */
@@ -197,12 +207,15 @@ int mhc_dynamic_weights_bwd(const float* x, const float* phi, const float* bias,
 /* ---- Fused layer entry points ------------------------------------------------------
  * Forward of the module's fused dynamic path in one call: x = mean_s H (fp32 [B,4D], output),
  * the dynamic weights from x (bias given as the three base parameters, pre [4], post [4],
- * res [16]), then the stream mix.  Replaces the chain HyperConnection._compute_weights (fused
+ * res [16]), then the stream mix.  If pooled_partials is not NULL it holds the token sums of H
+ * as left by mhc_add_residual_pool_fwd of the previous layer ([B, pooled_chunks, 4*D] fp32) and
+ * the pass over H for pooling is skipped.  Replaces the chain HyperConnection._compute_weights (fused
  * branch, src/mhc/module.py:119-139) + fused_stream_mix (src/mhc/module.py:177). */
 int mhc_hc_mix_fwd(const void* H, const float* phi, const float* H_pre_base, const float* H_post_base,
                    const float* H_res_base, const float* alpha_pre, const float* alpha_post,
                    const float* alpha_res, float* x, float* H_pre, float* H_post, float* H_res,
-                   float* saved, void* branch_input, void* H_residual, void* scratch,
+                   float* saved, void* branch_input, void* H_residual,
+                   const float* pooled_partials, int64_t pooled_chunks, void* scratch,
                    int64_t scratch_bytes, int64_t B, int64_t S, int64_t D, int dtype, int iters,
                    float eps, mhc_stream_t stream);
 

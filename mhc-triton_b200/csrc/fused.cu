@@ -11,9 +11,9 @@ using namespace mhc;
 extern "C" int mhc_hc_mix_fwd(const void* H, const float* phi, const float* H_pre_base, const float* H_post_base,
                               const float* H_res_base, const float* alpha_pre, const float* alpha_post,
                               const float* alpha_res, float* x, float* H_pre, float* H_post, float* H_res,
-                              float* saved, void* branch_input, void* H_residual, void* scratch,
-                              int64_t scratch_bytes, int64_t B, int64_t S, int64_t D, int dtype, int iters, float eps,
-                              mhc_stream_t stream) {
+                              float* saved, void* branch_input, void* H_residual, const float* pooled_partials,
+                              int64_t pooled_chunks, void* scratch, int64_t scratch_bytes, int64_t B, int64_t S,
+                              int64_t D, int dtype, int iters, float eps, mhc_stream_t stream) {
   if (int e = check_bsd_pub("hc_mix_fwd", B, S, D, dtype)) return e;
   if (iters < 0) return fail(MHC_ERR_BAD_ARGUMENT, "hc_mix_fwd: iters < 0");
   if (B == 0) return MHC_OK;
@@ -29,8 +29,15 @@ extern "C" int mhc_hc_mix_fwd(const void* H, const float* phi, const float* H_pr
   float* pool_part = (float*)scratch;
   float* proj_part = pool_part + pool_floats;
   int nchunk = 0;
-  if (int e = meanpool_partial_impl(H, pool_part, B, S, D, dtype, st, &nchunk)) return e;
-  if (int e = weights_fwd_impl(pool_part, nchunk, 1.0 / (double)S, x, phi, BiasPtrs{H_pre_base, H_post_base, H_res_base},
+  const float* pool_src = pool_part;
+  if (pooled_partials) {  // token sums of H left by the previous layer's add residual: no pass over H here
+    if (pooled_chunks <= 0 || pooled_chunks > (1 << 20)) return fail(MHC_ERR_BAD_ARGUMENT, "hc_mix_fwd: bad pooled_chunks");
+    pool_src = pooled_partials;
+    nchunk = (int)pooled_chunks;
+  } else if (int e = meanpool_partial_impl(H, pool_part, B, S, D, dtype, st, &nchunk)) {
+    return e;
+  }
+  if (int e = weights_fwd_impl(pool_src, nchunk, 1.0 / (double)S, x, phi, BiasPtrs{H_pre_base, H_post_base, H_res_base},
                                alpha_pre, alpha_post, alpha_res, H_pre, H_post, H_res, saved, proj_part, B, 4 * D,
                                iters, eps, st))
     return e;

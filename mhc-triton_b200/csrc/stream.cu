@@ -145,6 +145,83 @@ k_add_residual_fwd(const T* __restrict__ Hr, const T* __restrict__ bo, const flo
       });
 }
 
+// Add residual that also leaves the token sums of its own output for the NEXT layer's mean-pool:
+// pool[b, chunk, n*D + d] = sum over the chunk's tokens of H_new[b,s,n,d] (the values as stored,
+// i.e. after rounding to T).  Same layout as k_meanpool_partial's output, so the next layer's
+// projection kernel consumes it directly and that layer's pass over H for pooling disappears.
+#ifndef MHC_TPC_ADDPOOL
+#define MHC_TPC_ADDPOOL 64
+#endif
+template <typename T, int V>
+__global__ void __launch_bounds__(MHC_MAX_COLS, 2)
+k_add_residual_pool_fwd(const T* __restrict__ Hr, const T* __restrict__ bo, const float* __restrict__ Hpost,
+                        T* __restrict__ Hn, float* __restrict__ pool, Geo g) {
+  extern __shared__ float sm[];  // [4*V][sub][cols], used when several tokens are walked abreast
+  pdl_prologue();
+  const Item it = decode_item(g);
+  const int64_t D = g.D, c0 = (int64_t)it.col * V, tok = it.b * g.S;
+  float acc[4][V];
+#pragma unroll
+  for (int n = 0; n < 4; ++n)
+#pragma unroll
+    for (int e = 0; e < V; ++e) acc[n][e] = 0.f;
+  const bool live = it.col < g.DV;
+  if (live) {
+    float p[4];
+#pragma unroll
+    for (int n = 0; n < 4; ++n) p[n] = __ldg(Hpost + it.b * 4 + n);
+    using B5 = Bundle<T, V, 5>;
+    for_tokens_pipelined<B5>(
+        it.s0 + it.sub, it.s1, g.sub,
+        [&](B5& u, int64_t s) {
+          const T* r = Hr + (tok + s) * 4 * D + c0;
+          u.p[4] = ld_raw<T, V>(bo + (tok + s) * D + c0);
+#pragma unroll
+          for (int n = 0; n < 4; ++n) u.p[n] = ld_raw<T, V>(r + n * D);
+        },
+        [&](const B5& u, int64_t s) {
+          float y[V], x[V];
+          unpack<T, V>(u.p[4], y);
+          T* o = Hn + (tok + s) * 4 * D + c0;
+#pragma unroll
+          for (int n = 0; n < 4; ++n) {
+            unpack<T, V>(u.p[n], x);
+#pragma unroll
+            for (int e = 0; e < V; ++e) {
+              x[e] = x[e] + p[n] * y[e];
+              acc[n][e] += to_f32(from_f32<T>(x[e]));   // what a later read of H_new would see
+            }
+            PackIO<T, V>::store(o + n * D, x);
+          }
+        });
+  }
+  const int c = threadIdx.x % g.cols;
+  if (g.sub > 1) {
+#pragma unroll
+    for (int n = 0; n < 4; ++n)
+#pragma unroll
+      for (int e = 0; e < V; ++e) sm[((n * V + e) * g.sub + it.sub) * g.cols + c] = acc[n][e];
+    __syncthreads();
+    if (it.sub == 0) {
+#pragma unroll
+      for (int n = 0; n < 4; ++n)
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+          float t = acc[n][e];
+          for (int j = 1; j < g.sub; ++j) t += sm[((n * V + e) * g.sub + j) * g.cols + c];
+          acc[n][e] = t;
+        }
+    }
+  }
+  if (live && it.sub == 0) {
+    float* o = pool + (it.b * g.nchunk + it.chunk) * 4 * D + c0;
+#pragma unroll
+    for (int n = 0; n < 4; ++n)
+#pragma unroll
+      for (int e = 0; e < V; ++e) o[n * D + e] = acc[n][e];
+  }
+}
+
 // d_branch_output[s,d] = sum_n H_post[n] g[s,n,d];  partial dH_post[n] = sum_{s,d} g[s,n,d] bo[s,d].
 // part: [B, slots, 4].
 template <typename T, int V>
@@ -620,6 +697,38 @@ extern "C" int mhc_add_residual_fwd(const void* H_residual, const void* branch_o
                                  (const T*)H_residual, (const T*)branch_output, H_post, (T*)H_new, g)));
   }
   return check_launch("add_residual_fwd");
+}
+
+extern "C" int64_t mhc_add_residual_pool_chunks(int64_t S, int64_t D) {
+  (void)D;
+  if (S <= 0) return 0;
+  return (S + MHC_TPC_ADDPOOL - 1) / MHC_TPC_ADDPOOL;  // a function of S only
+}
+
+extern "C" int mhc_add_residual_pool_fwd(const void* H_residual, const void* branch_output, const float* H_post,
+                                         void* H_new, float* pool_partials, int64_t B, int64_t S, int64_t D, int dtype,
+                                         mhc_stream_t stream) {
+  if (int e = check_bsd("add_residual_pool_fwd", B, S, D, dtype)) return e;
+  if (B == 0 || S == 0 || D == 0) return MHC_OK;
+  if (!H_residual || !branch_output || !H_post || !H_new || !pool_partials)
+    return fail(MHC_ERR_NULL_POINTER, "add_residual_pool_fwd: null pointer");
+  const int vec = pick_vec(dtype, D, {H_residual, branch_output, H_new});
+  Geo g = make_geo(S, D, vec, GeoKind::Reduce, MHC_TPC_ADDPOOL);
+  // Chunks are MHC_TPC_ADDPOOL tokens whatever the row width (token sub-groups share a chunk), so the
+  // number of partial rows is a function of S only.
+  g.tpc = (int32_t)(S < MHC_TPC_ADDPOOL ? S : MHC_TPC_ADDPOOL);
+  g.nchunk = (int32_t)mhc_add_residual_pool_chunks(S, D);
+  g.reverse = (MHC_REV_MASK >> 2) & 1;
+  const int64_t items = B * geo_slots(g);
+  if (int e = check_grid("add_residual_pool_fwd", items)) return e;
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t smem = g.sub > 1 ? (size_t)4 * vec * geo_block(g) * sizeof(float) : 0;
+  {
+    ProfScope ps("k_add_residual_pool_fwd", st);
+    MHC_DISPATCH(dtype, vec, (launch_k(k_add_residual_pool_fwd<T, V>, (unsigned)items, geo_block(g), smem, st,
+                                       (const T*)H_residual, (const T*)branch_output, H_post, (T*)H_new, pool_partials, g)));
+  }
+  return check_launch("add_residual_pool_fwd");
 }
 
 extern "C" int mhc_add_residual_bwd(const void* dH_new, const void* branch_output, const float* H_post,

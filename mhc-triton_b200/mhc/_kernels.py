@@ -49,8 +49,10 @@ def stream_mix_forward(H: torch.Tensor, H_pre: torch.Tensor, H_res: torch.Tensor
 
 
 def add_residual_forward(H_residual: torch.Tensor, branch_output: torch.Tensor, H_post: torch.Tensor,
-                         block_dim: int = 128) -> torch.Tensor:
-    """H_new = H_residual + H_post[:, None, :, None] * branch_output[:, :, None, :]."""
+                         block_dim: int = 128, pool: bool = False):
+    """H_new = H_residual + H_post[:, None, :, None] * branch_output[:, :, None, :].
+    With pool=True returns (H_new, partials): partials [B, chunks, 4*D] fp32 are the token sums of
+    H_new per chunk, which the next layer's fused forward accepts in place of its own pooling pass."""
     _check(H_residual.dim() == 4, "H_residual must be [batch, seq, 4, dim]")
     B, S, n, D = H_residual.shape
     _check(n == 4, "num_streams must be 4")
@@ -61,6 +63,13 @@ def add_residual_forward(H_residual: torch.Tensor, branch_output: torch.Tensor, 
     branch_output = branch_output.to(H_residual.dtype).contiguous()
     H_post = L.f32c(H_post)
     H_new = torch.empty_like(H_residual)
+    if pool:
+        chunks = L.load().mhc_add_residual_pool_chunks(S, D)
+        partials = torch.empty(B, chunks, 4 * D, device=H_residual.device, dtype=torch.float32)
+        with torch.cuda.device(H_residual.device):
+            L.call("mhc_add_residual_pool_fwd", L.stream_of(H_residual), L.ptr(H_residual), L.ptr(branch_output),
+                   L.ptr(H_post), L.ptr(H_new), L.ptr(partials), B, S, D, L.dtype_code(H_residual))
+        return H_new, partials
     with torch.cuda.device(H_residual.device):
         L.call("mhc_add_residual_fwd", L.stream_of(H_residual), L.ptr(H_residual), L.ptr(branch_output), L.ptr(H_post), L.ptr(H_new),
                                               B, S, D, L.dtype_code(H_residual))
@@ -121,11 +130,12 @@ def fused_dynamic_weights_forward(x: torch.Tensor, phi: torch.Tensor, bias: torc
 
 
 def hc_mix_forward(H, H_pre_base, H_post_base, H_res_base, phi, alpha_pre, alpha_post, alpha_res,
-                   sinkhorn_iters: int = 20, eps: float = 1e-6):
+                   sinkhorn_iters: int = 20, eps: float = 1e-6, pooled=None):
     """Fused forward of the module's dynamic path in ONE library call: sequence mean-pool,
     dynamic weights, stream mix.  Returns
     (branch_input, H_residual, H_post, H_pre, H_res, x, saved); x [B,4D] and saved [B,32]
-    are what the fused backward needs."""
+    are what the fused backward needs.  `pooled` ([B, chunks, 4D] fp32 token sums of H from the
+    previous layer's add_residual_forward(pool=True)) replaces the pooling pass over H."""
     _check(H.dim() == 4 and H.shape[2] == 4, "H must be [batch, seq, 4, dim]")
     B, S, _, D = H.shape
     _check(S > 0 and D > 0, "empty sequence or width")
@@ -143,8 +153,14 @@ def hc_mix_forward(H, H_pre_base, H_post_base, H_res_base, phi, alpha_pre, alpha
     bi = torch.empty(B, S, D, device=dev, dtype=H.dtype)
     Hr = torch.empty_like(H)
     buf, nbytes = L.scratch(L.OP_HC_MIX_FWD, B, S, D, H)
+    chunks = 0
+    if pooled is not None:
+        _check(pooled.dim() == 3 and pooled.shape[0] == B and pooled.shape[2] == 4 * D and pooled.dtype == torch.float32
+               and pooled.is_contiguous() and pooled.device == dev, "pooled must be contiguous fp32 [B, chunks, 4*D]")
+        chunks = pooled.shape[1]
     with torch.cuda.device(dev):
         L.call("mhc_hc_mix_fwd", L.stream_of(H), L.ptr(H), L.ptr(phi), L.ptr(pre_b), L.ptr(post_b), L.ptr(res_b),
                L.ptr(a[0]), L.ptr(a[1]), L.ptr(a[2]), L.ptr(x), L.ptr(H_pre), L.ptr(H_post), L.ptr(H_res), L.ptr(saved),
-               L.ptr(bi), L.ptr(Hr), L.ptr(buf), nbytes, B, S, D, L.dtype_code(H), int(sinkhorn_iters), float(eps))
+               L.ptr(bi), L.ptr(Hr), L.ptr(pooled), chunks, L.ptr(buf), nbytes, B, S, D, L.dtype_code(H),
+               int(sinkhorn_iters), float(eps))
     return bi, Hr, H_post, H_pre, H_res, x, saved

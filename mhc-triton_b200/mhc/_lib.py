@@ -38,14 +38,15 @@ _PROTOTYPES = {
     "mhc_dynamic_weights_fwd": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _I, _F, _P],
     "mhc_dynamic_weights_bwd": [_P] * 15 + [_L, _L, _L, _I, _F, _I, _I, _P],
     "mhc_add_residual_bwd_noalloc": [_P, _P, _P, _P, _P, _L, _L, _L, _I, _P],
-    "mhc_hc_mix_fwd": [_P] * 16 + [_L, _L, _L, _L, _I, _I, _F, _P],
+    "mhc_hc_mix_fwd": [_P] * 16 + [_L, _P, _L, _L, _L, _L, _I, _I, _F, _P],
+    "mhc_add_residual_pool_fwd": [_P, _P, _P, _P, _P, _L, _L, _L, _I, _P],
     "mhc_hc_mix_bwd": [_P] * 23 + [_L, _L, _L, _L, _I, _I, _F, _I, _I, _P],
 }
 
 EXPORTS = sorted(list(_PROTOTYPES) + ["mhc_version", "mhc_last_error_string", "mhc_status_name", "mhc_scratch_bytes",
                                           "mhc_launch_count", "mhc_profile_enable", "mhc_profile_count",
                                           "mhc_profile_get", "mhc_profile_select",
-                                          "mhc_add_residual_bwd_noalloc_max_bytes"])
+                                          "mhc_add_residual_bwd_noalloc_max_bytes", "mhc_add_residual_pool_chunks"])
 
 _lib = None
 
@@ -78,6 +79,8 @@ def load():
     lib.mhc_profile_enable.restype = c_int
     lib.mhc_add_residual_bwd_noalloc_max_bytes.argtypes = []
     lib.mhc_add_residual_bwd_noalloc_max_bytes.restype = c_int64
+    lib.mhc_add_residual_pool_chunks.argtypes = [c_int64, c_int64]
+    lib.mhc_add_residual_pool_chunks.restype = c_int64
     lib.mhc_profile_select.argtypes = [c_char_p]
     lib.mhc_profile_select.restype = c_int
     lib.mhc_profile_count.argtypes = []

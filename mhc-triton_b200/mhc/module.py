@@ -10,7 +10,7 @@ from typing import Callable, Tuple
 import torch
 import torch.nn as nn
 
-from .ops import (fused_add_residual, fused_dynamic_weights, fused_stream_mix, hyper_connection_mix,
+from .ops import (fused_add_residual, fused_dynamic_weights, fused_stream_mix, hyper_connection_mix, pooled_sums_of,
                   sequence_mean_pool, sinkhorn_knopp)
 
 
@@ -110,13 +110,15 @@ class HyperConnection(nn.Module):
             branch_input, H_residual, H_post, _, _ = hyper_connection_mix(
                 H, self.H_pre_base, self.H_post_base, self.H_res_base, self.phi, self.alpha_pre, self.alpha_post,
                 self.alpha_res, self.sinkhorn_iters, self.eps, self.grad_sink, self.grads_ready_hook,
-                self.grad_accumulate)
+                self.grad_accumulate, pooled_sums_of(H))
         else:
             H_post, H_pre, H_res = self._compute_weights(H)
             branch_input, H_residual = fused_stream_mix(H, H_pre, H_res)
 
-        def add_residual(branch_output: torch.Tensor) -> torch.Tensor:
-            return fused_add_residual(H_residual, branch_output, H_post)
+        def add_residual(branch_output: torch.Tensor, pool_for_next: bool = False) -> torch.Tensor:
+            """pool_for_next=True: also accumulate the token sums the NEXT HyperConnection needs for its
+            mean-pool, so that layer reads H once instead of twice (pass the returned tensor to it as is)."""
+            return fused_add_residual(H_residual, branch_output, H_post, pool_for_next)
 
         return branch_input, add_residual
 

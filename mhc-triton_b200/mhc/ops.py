@@ -60,16 +60,22 @@ class _FusedAddResidual(torch.autograd.Function):
     itself and is returned without a copy."""
 
     @staticmethod
-    def forward(ctx, H_residual, branch_output, H_post):
-        H_new = add_residual_forward(H_residual, branch_output, H_post)
+    def forward(ctx, H_residual, branch_output, H_post, pool):
         ctx.save_for_backward(branch_output, H_post)
-        return H_new
+        ctx.set_materialize_grads(False)
+        if pool:
+            H_new, partials = add_residual_forward(H_residual, branch_output, H_post, pool=True)
+            ctx.mark_non_differentiable(partials)
+            return H_new, partials
+        return add_residual_forward(H_residual, branch_output, H_post)
 
     @staticmethod
-    def backward(ctx, grad_H_new):
+    def backward(ctx, grad_H_new, _unused=None):
+        if grad_H_new is None:
+            return None, None, None, None
         branch_output, H_post = ctx.saved_tensors
         dH_residual, d_bo, dH_post = add_residual_backward(grad_H_new, branch_output, H_post)
-        return dH_residual, d_bo.to(branch_output.dtype), dH_post.to(H_post.dtype)
+        return dH_residual, d_bo.to(branch_output.dtype), dH_post.to(H_post.dtype), None
 
 
 class _FusedDynamicWeights(torch.autograd.Function):
@@ -131,9 +137,10 @@ class _HyperConnectionMix(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, H, H_pre_base, H_post_base, H_res_base, phi, alpha_pre, alpha_post, alpha_res,
-                sinkhorn_iters, eps, grad_sink, ready_hook, accumulate):
+                sinkhorn_iters, eps, grad_sink, ready_hook, accumulate, pooled):
         branch_input, H_residual, H_post, H_pre, H_res, x, saved = hc_mix_forward(
-            H, H_pre_base, H_post_base, H_res_base, phi, alpha_pre, alpha_post, alpha_res, sinkhorn_iters, eps)
+            H, H_pre_base, H_post_base, H_res_base, phi, alpha_pre, alpha_post, alpha_res, sinkhorn_iters, eps,
+            pooled=pooled)
         ctx.save_for_backward(H, x, phi, H_pre_base, H_post_base, H_res_base, alpha_pre, alpha_post, alpha_res,
                               saved, H_pre, H_res)
         ctx.sinkhorn_iters, ctx.eps, ctx.grad_sink, ctx.ready_hook = sinkhorn_iters, eps, grad_sink, ready_hook
@@ -158,12 +165,12 @@ class _HyperConnectionMix(torch.autograd.Function):
         if ctx.ready_hook is not None:
             ctx.ready_hook(ctx.grad_sink)
         if ctx.grad_sink is not None:  # the parameters' .grad tensors are views of the sink already
-            return (dH,) + (None,) * 12
+            return (dH,) + (None,) * 13
         return (dH, gbias[0:4].reshape(pre_b.shape).to(pre_b.dtype), gbias[4:8].reshape(post_b.shape).to(post_b.dtype),
                 gbias[8:24].reshape(res_b.shape).to(res_b.dtype), gphi.to(phi.dtype),
                 galpha[0:1].reshape_as(alpha_pre).to(alpha_pre.dtype),
                 galpha[1:2].reshape_as(alpha_post).to(alpha_post.dtype),
-                galpha[2:3].reshape_as(alpha_res).to(alpha_res.dtype), None, None, None, None, None)
+                galpha[2:3].reshape_as(alpha_res).to(alpha_res.dtype), None, None, None, None, None, None)
 
 
 def sinkhorn_knopp(M: torch.Tensor, num_iters: int = 20, eps: float = 1e-8) -> torch.Tensor:
@@ -178,9 +185,31 @@ def fused_stream_mix(H: torch.Tensor, H_pre: torch.Tensor, H_res: torch.Tensor) 
     return _FusedStreamMix.apply(H, H_pre, H_res)
 
 
-def fused_add_residual(H_residual: torch.Tensor, branch_output: torch.Tensor, H_post: torch.Tensor) -> torch.Tensor:
-    """H_new[n] = H_residual[n] + H_post[n] * branch_output, per batch element."""
-    return _FusedAddResidual.apply(H_residual, branch_output, H_post)
+def fused_add_residual(H_residual: torch.Tensor, branch_output: torch.Tensor, H_post: torch.Tensor,
+                       pool_for_next: bool = False) -> torch.Tensor:
+    """H_new[n] = H_residual[n] + H_post[n] * branch_output, per batch element.
+
+    With pool_for_next=True the same kernel also accumulates the per-chunk token sums of H_new and
+    the returned tensor carries them (attribute `_mhc_pooled`); a HyperConnection that receives
+    this very tensor as its input uses them instead of reading H once more for its mean-pool."""
+    if not pool_for_next:
+        return _FusedAddResidual.apply(H_residual, branch_output, H_post, False)
+    H_new, partials = _FusedAddResidual.apply(H_residual, branch_output, H_post, True)
+    H_new._mhc_pooled = (partials, H_new._version)
+    return H_new
+
+
+def pooled_sums_of(H: torch.Tensor):
+    """Token sums attached to H by fused_add_residual(pool_for_next=True), or None if absent, of the
+    wrong shape, or if H was modified in place since."""
+    tag = getattr(H, "_mhc_pooled", None)
+    if tag is None:
+        return None
+    partials, version = tag
+    if H._version != version or H.dim() != 4 or partials.shape[0] != H.shape[0] or \
+            partials.shape[2] != 4 * H.shape[3] or partials.device != H.device:
+        return None
+    return partials
 
 
 def fused_dynamic_weights(x, phi, bias, alpha_pre, alpha_post, alpha_res, sinkhorn_iters: int = 20,
@@ -198,12 +227,12 @@ def sequence_mean_pool(H: torch.Tensor) -> torch.Tensor:
 
 def hyper_connection_mix(H, H_pre_base, H_post_base, H_res_base, phi, alpha_pre, alpha_post, alpha_res,
                          sinkhorn_iters: int = 20, eps: float = 1e-6, grad_sink=None, ready_hook=None,
-                         accumulate: bool = False):
+                         accumulate: bool = False, pooled=None):
     """Fused pooled-weights + stream-mix node; returns
     (branch_input, H_residual, H_post, H_pre, H_res); the last two carry no gradient.
     With `grad_sink` the parameter gradients are written into that flat buffer and no
     gradient is returned for the parameters; `ready_hook(grad_sink)` is called as soon as
     the kernels that fill it have been launched; `accumulate` adds to the buffer instead of
-    overwriting it."""
+    overwriting it; `pooled` are token sums of H from the previous layer (see fused_add_residual)."""
     return _HyperConnectionMix.apply(H, H_pre_base, H_post_base, H_res_base, phi, alpha_pre, alpha_post, alpha_res,
-                                     sinkhorn_iters, eps, grad_sink, ready_hook, accumulate)
+                                     sinkhorn_iters, eps, grad_sink, ready_hook, accumulate, pooled)

@@ -525,3 +525,44 @@ def test_sequence_sharded_wrapper_single_rank_equals_layer():
     assert_close(b["dH"], a["dH"], RT, 2 * AT, "dH")
     for n, _ in hc.named_parameters():
         assert_close_norm(b["dlayer." + n], a["d" + n], RT, AT, n)
+
+
+@pytest.mark.parametrize("dtype,B,S,D", [(torch.float32, 2, 150, 96), (torch.bfloat16, 2, 300, 512), (torch.float32, 1, 70, 20)])
+def test_cross_layer_pooling_matches_separate_pooling(dtype, B, S, D):
+    """add_residual(pool_for_next=True) hands the next layer the token sums of H_new: that layer
+    launches no mean-pool kernel and gives the same results (the pooled state only differs in
+    summation order)."""
+    import mhc
+    from mhc import _lib
+    torch.manual_seed(8)
+    H = torch.randn(B, S, 4, D).to(dtype)
+    up = torch.randn(B, S, 4, D).to(dtype)
+    ps = [cases.perturb_params_(O.default_params(D, i, 0.1), 40 + i) for i in range(2)]
+    layers = [to_module(mhc.HyperConnection(dim=D, layer_idx=i), ps[i]).to(DEV) for i in range(2)]
+
+    def run(pool):
+        for l in layers:
+            for q in l.parameters():
+                q.grad = None
+        Hd = dev(H).requires_grad_(True)
+        bi, add = layers[0](Hd)
+        H1 = add(torch.tanh(bi), pool_for_next=pool)
+        assert (mhc.ops.pooled_sums_of(H1) is not None) == pool
+        _lib.profile_start()
+        bi2, add2 = layers[1](H1)
+        names = set(_lib.profile_stop())
+        H2 = add2(bi2 * 0.5)
+        H2.backward(dev(up))
+        return H1, H2, Hd.grad, [q.grad.clone() for l in layers for q in l.parameters()], names
+
+    H1a, H2a, dHa, ga, na = run(False)
+    H1b, H2b, dHb, gb, nb = run(True)
+    assert "k_meanpool_partial" in na and "k_meanpool_partial" not in nb
+    assert torch.equal(H1a, H1b)
+    rt, at = (RT, 4 * AT) if dtype == torch.float32 else (2e-2, 2e-2)
+    assert_close_norm(H2b, H2a, rt, at, "H2"); assert_close_norm(dHb, dHa, rt, at, "dH")
+    for x, y in zip(gb, ga):
+        assert_close_norm(x, y, 1e-4 if dtype == torch.float32 else 2e-2, AT)
+    # a tensor modified in place no longer carries valid sums
+    H1b.detach().add_(1.0)
+    assert mhc.ops.pooled_sums_of(H1b) is None
