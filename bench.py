@@ -39,13 +39,16 @@ WORKLOADS = {
     "c4": (8, 4096, 4096, torch.bfloat16),
     "c3": (8, 4096, 2048, torch.bfloat16),
     "c1": (2, 128, 512, torch.float32),
+    "c5": (2, 4096, 7168, torch.bfloat16),   # the 16-layer stack, hyper-connection kernels only (identity branches)
 }
+LAYERS = {"c5": 16}
 METRIC = "hc_fwd_bwd_tokens_per_s"
 # Algorithmic HBM bytes per token, in units of D * element size: each logical tensor is read once
 # per consuming op and written once (mean-pool 4, stream mix 9, add residual 9, add-residual
 # backward 6, stream-mix backward: reduction pass 9 + apply pass 9).
 OP_UNITS = {
-    "k_meanpool_partial": 4, "k_stream_mix_fwd": 9, "k_add_residual_fwd": 9, "k_add_residual_bwd": 6,
+    "k_meanpool_partial": 4, "k_stream_mix_fwd": 9, "k_add_residual_fwd": 9, "k_add_residual_pool_fwd": 9,
+    "k_add_residual_bwd": 6,
     "k_stream_mix_bwd_reduce": 9, "k_stream_mix_bwd_apply": 9,
 }
 TOTAL_UNITS = 46
@@ -172,7 +175,9 @@ def run_reference(args):
 
 def describe(name):
     B, S, D, dtype = WORKLOADS[name]
-    return (f"{name}: dynamic HyperConnection fwd+bwd, {str(dtype).split('.')[-1]} H({B},{S},4,{D}) per GPU, "
+    nl = LAYERS.get(name, 1)
+    stack = f"stack of {nl} layers, " if nl > 1 else ""
+    return (f"{name}: {stack}dynamic HyperConnection fwd+bwd, {str(dtype).split('.')[-1]} H({B},{S},4,{D}) per GPU, "
             f"fp32 phi[{4 * D},24], 20 Sinkhorn iters, identity branch")
 
 
@@ -191,6 +196,9 @@ def main():
     ap.add_argument("--no-overlap", action="store_true", help="all-reduce on the compute stream")
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
                     help="weak: every rank runs the workload's batch; strong: the workload's batch is split over the ranks")
+    ap.add_argument("--layers", type=int, default=None, help="override the number of stacked layers")
+    ap.add_argument("--no-cross-layer", action="store_true",
+                    help="stacks: let every layer pool its own input instead of taking the sums from the layer before")
     ap.add_argument("--graph", action="store_true",
                     help="replay the step from a CUDA graph (for small per-GPU batches, where the host would be the limit)")
     args = ap.parse_args()
@@ -225,17 +233,21 @@ def main():
         torch.cat([torch.randn(1, S, 4, D, device=dev, dtype=torch.float32, generator=gen).to(dtype) for _ in range(B)])
     g = torch.cat([torch.randn(1, S, 4, D, device=dev, dtype=torch.float32, generator=gen).to(dtype) for _ in range(B)])
     H.requires_grad_(True)
-    hc = make_layer(D, dev)
-    sync = GradSync([hc], overlap=not args.no_overlap)
+    n_layers = args.layers or LAYERS.get(args.workload, 1)
+    layers = [make_layer(D, dev) for _ in range(n_layers)]
+    hc = layers[0]
+    sync = GradSync(layers, overlap=not args.no_overlap)
     lib = _lib.load()
 
     def step():
         H.grad = None
-        bi, add = hc(H)
-        H_new = add(bi)            # identity branch
-        H_new.backward(g)
+        h = H
+        for i, layer in enumerate(layers):
+            bi, add = layer(h)
+            h = add(bi, pool_for_next=(i + 1 < n_layers and not args.no_cross_layer))   # identity branch
+        h.backward(g)
         sync.finish()
-        return H_new
+        return h
 
     def barrier():
         if world > 1:
@@ -306,7 +318,7 @@ def main():
         per_op[name] = ent
     dom_bytes = OP_UNITS[dom] * D * esz * B * S
     dom_avg_ms = dom_ms / dom_calls
-    step_bytes = TOTAL_UNITS * D * esz * B * S
+    step_bytes = TOTAL_UNITS * D * esz * B * S * n_layers
     roofline = {
         "bound": "hbm", "kernel": dom, "achieved": dom_bytes / (dom_avg_ms * 1e-3) / 1e9, "peak": peak,
         "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": dom_bytes / (dom_avg_ms * 1e-3) / 1e9 / peak,
@@ -318,7 +330,7 @@ def main():
 
     # ---- end to end: same step from pinned host buffers, results read back to the host ----
     e2e = None
-    if not args.no_e2e:
+    if not args.no_e2e and n_layers == 1:   # the host-streamed step drives one layer
         H_host = H.detach().cpu().pin_memory()
         g_host = g.cpu().pin_memory()
         out_new = torch.empty_like(H_host).pin_memory()
@@ -351,7 +363,7 @@ def main():
                        "H_new + dH + parameter grads -> pinned host, copies overlapped with kernels on three streams"}
 
     cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and n_layers == 1:
         tps, cores, sec = cpu_oracle_sample(D, S, dtype, args.cpu_steps, 1)
         cpu = {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port",
                "sample": f"1 of {B} batch elements ({S} tokens, D={D}), fp32 math, fwd+bwd, {args.cpu_steps} timed runs "
@@ -363,7 +375,8 @@ def main():
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": args.scaling,
             "vs_baseline": None, "dtype": "bf16" if dtype == torch.bfloat16 else "f32", "data": "synthetic",
             "config": {"workload": describe(args.workload) + (f" [batch overridden to {B}]" if args.batch else ""),
-                       "global_tokens": tokens, "sharding": f"batch x{world}", "per_gpu_batch": B, "cuda_graph": bool(args.graph),
+                       "global_tokens": tokens, "sharding": f"batch x{world}", "per_gpu_batch": B, "layers": n_layers,
+                       "cross_layer_pooling": n_layers > 1 and not args.no_cross_layer, "cuda_graph": bool(args.graph),
                        "l2": "inputs larger than L2 (H alone is %.0f MiB per GPU)" % (B * S * 4 * D * esz / 2 ** 20),
                        "collective": "NCCL SUM all-reduce of phi/bias/alpha grads" if world > 1 else "none"},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches) * world,

@@ -53,7 +53,7 @@ namespace mhc {
 #define MHC_TPC_ADDFWD 1
 #endif
 #ifndef MHC_TPC_APPLY
-#define MHC_TPC_APPLY 8
+#define MHC_TPC_APPLY 4
 #endif
 #ifndef MHC_TPC_ADDBWD
 #define MHC_TPC_ADDBWD 4
