@@ -256,21 +256,36 @@ def main():
 
     eager_step = step
     if args.graph:
-        # warm up on a side stream, then capture one step (all-reduce included) and replay it
+        # Warm up on a side stream, then capture one step and replay it.  Collectives stay OUT of the
+        # graph: the captured step leaves this rank's gradients in the flat record and the all-reduce
+        # is issued eagerly after every replay.
+        hooks = [l.grads_ready_hook for l in layers]
+        for l in layers:
+            l.grads_ready_hook = None
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
-        sync.overlap = False
         with torch.cuda.stream(side):
             for _ in range(3):
                 eager_step()
         torch.cuda.current_stream().wait_stream(side)
-        barrier()
+        torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             eager_step()
+        torch.cuda.synchronize()
 
         def step():  # noqa: F811
             graph.replay()
+            sync.all_reduce_now()
+
+        def eager_step_with_hooks():
+            for l, h in zip(layers, hooks):
+                l.grads_ready_hook = h
+            try:
+                return eager_step()
+            finally:
+                for l in layers:
+                    l.grads_ready_hook = None
 
     for _ in range(args.warmup):
         step()
@@ -278,7 +293,7 @@ def main():
     # ---- survey pass (untimed): every kernel bracketed by events, to find the dominant one ----
     _lib.profile_start()
     for _ in range(3):
-        eager_step()
+        (eager_step_with_hooks if args.graph else eager_step)()
     survey = _lib.profile_stop()
     dom = max((n for n in survey if n in OP_UNITS), key=lambda n: survey[n][1])
     barrier()
