@@ -66,6 +66,12 @@ template <typename T, int V> struct PackIO;
 template <typename T> struct PackIO<T, 1> {
   static __device__ __forceinline__ void load(const T* __restrict__ p, float (&o)[1]) { o[0] = to_f32(__ldg(p)); }
   static __device__ __forceinline__ void store(T* __restrict__ p, const float (&v)[1]) { *p = from_f32<T>(v[0]); }
+  // store, and leave in v the values as a later load would return them (rounded to T)
+  static __device__ __forceinline__ void store_round(T* __restrict__ p, float (&v)[1]) {
+    const T t = from_f32<T>(v[0]);
+    *p = t;
+    v[0] = to_f32(t);
+  }
 };
 
 template <> struct PackIO<float, 4> {
@@ -78,6 +84,7 @@ template <> struct PackIO<float, 4> {
     st_stream16(p, make_uint4(__float_as_uint(v[0]), __float_as_uint(v[1]), __float_as_uint(v[2]),
                               __float_as_uint(v[3])));
   }
+  static __device__ __forceinline__ void store_round(float* __restrict__ p, float (&v)[4]) { store(p, v); }
 };
 
 template <> struct PackIO<__nv_bfloat16, 8> {
@@ -96,6 +103,17 @@ template <> struct PackIO<__nv_bfloat16, 8> {
     for (int i = 0; i < 4; ++i) {
       __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
       w[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    st_stream16(p, make_uint4(w[0], w[1], w[2], w[3]));
+  }
+  static __device__ __forceinline__ void store_round(__nv_bfloat16* __restrict__ p, float (&v)[8]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+      w[i] = *reinterpret_cast<uint32_t*>(&h);
+      v[2 * i] = __uint_as_float(w[i] << 16);
+      v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
     }
     st_stream16(p, make_uint4(w[0], w[1], w[2], w[3]));
   }
@@ -118,6 +136,18 @@ template <> struct PackIO<__half, 8> {
     for (int i = 0; i < 4; ++i) {
       __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
       w[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    st_stream16(p, make_uint4(w[0], w[1], w[2], w[3]));
+  }
+  static __device__ __forceinline__ void store_round(__half* __restrict__ p, float (&v)[8]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+      w[i] = *reinterpret_cast<uint32_t*>(&h);
+      const float2 f = __half22float2(h);
+      v[2 * i] = f.x;
+      v[2 * i + 1] = f.y;
     }
     st_stream16(p, make_uint4(w[0], w[1], w[2], w[3]));
   }

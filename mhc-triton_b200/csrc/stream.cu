@@ -152,6 +152,9 @@ k_add_residual_fwd(const T* __restrict__ Hr, const T* __restrict__ bo, const flo
 #ifndef MHC_TPC_ADDPOOL
 #define MHC_TPC_ADDPOOL 64
 #endif
+#ifndef MHC_ADDPOOL_PIPE
+#define MHC_ADDPOOL_PIPE 1
+#endif
 template <typename T, int V>
 __global__ void __launch_bounds__(MHC_MAX_COLS, 2)
 k_add_residual_pool_fwd(const T* __restrict__ Hr, const T* __restrict__ bo, const float* __restrict__ Hpost,
@@ -171,7 +174,7 @@ k_add_residual_pool_fwd(const T* __restrict__ Hr, const T* __restrict__ bo, cons
 #pragma unroll
     for (int n = 0; n < 4; ++n) p[n] = __ldg(Hpost + it.b * 4 + n);
     using B5 = Bundle<T, V, 5>;
-    for_tokens_pipelined<B5>(
+    for_tokens<MHC_ADDPOOL_PIPE != 0, B5>(
         it.s0 + it.sub, it.s1, g.sub,
         [&](B5& u, int64_t s) {
           const T* r = Hr + (tok + s) * 4 * D + c0;
@@ -187,11 +190,10 @@ k_add_residual_pool_fwd(const T* __restrict__ Hr, const T* __restrict__ bo, cons
           for (int n = 0; n < 4; ++n) {
             unpack<T, V>(u.p[n], x);
 #pragma unroll
-            for (int e = 0; e < V; ++e) {
-              x[e] = x[e] + p[n] * y[e];
-              acc[n][e] += to_f32(from_f32<T>(x[e]));   // what a later read of H_new would see
-            }
-            PackIO<T, V>::store(o + n * D, x);
+            for (int e = 0; e < V; ++e) x[e] = x[e] + p[n] * y[e];
+            PackIO<T, V>::store_round(o + n * D, x);   // x now holds what a later read of H_new returns
+#pragma unroll
+            for (int e = 0; e < V; ++e) acc[n][e] += x[e];
           }
         });
   }
@@ -270,7 +272,7 @@ k_add_residual_bwd(const T* __restrict__ G, const T* __restrict__ bo, const floa
 // MODE 0: dH and partials.  MODE 1: partials only (the apply pass writes dH later).
 // part: [B, slots, 20] = dH_pre[4] then dH_res[4][4] row-major.
 template <typename T, int V, int MODE>
-__global__ void __launch_bounds__(MHC_MAX_COLS, 512 / MHC_MAX_COLS)
+__global__ void __launch_bounds__(MHC_MAX_COLS, MODE == 0 ? 1 : 512 / MHC_MAX_COLS)
 k_stream_mix_bwd(const T* __restrict__ dbi, const T* __restrict__ dHr, const T* __restrict__ H,
                  const float* __restrict__ Hpre, const float* __restrict__ Hres, T* __restrict__ dH,
                  float* __restrict__ part, Geo g) {
