@@ -153,7 +153,7 @@ k_add_residual_fwd(const T* __restrict__ Hr, const T* __restrict__ bo, const flo
 #define MHC_TPC_ADDPOOL 64
 #endif
 #ifndef MHC_ADDPOOL_PIPE
-#define MHC_ADDPOOL_PIPE 1
+#define MHC_ADDPOOL_PIPE 0
 #endif
 template <typename T, int V>
 __global__ void __launch_bounds__(MHC_MAX_COLS, 2)

@@ -566,3 +566,47 @@ def test_cross_layer_pooling_matches_separate_pooling(dtype, B, S, D):
     # a tensor modified in place no longer carries valid sums
     H1b.detach().add_(1.0)
     assert mhc.ops.pooled_sums_of(H1b) is None
+
+
+def test_step_replayed_from_cuda_graph_equals_eager():
+    """Forward + backward captured in a CUDA graph (kernels chained by programmatic dependent
+    launch, no host synchronisation anywhere in the step) replays to the eager results, also
+    after the static input buffers are refilled."""
+    import mhc
+    torch.manual_seed(13)
+    B, S, D = 2, 160, 128
+    p = cases.perturb_params_(O.default_params(D, 0, 0.1), 17)
+    hc = to_module(mhc.HyperConnection(dim=D), p).to(DEV)
+    sync = mhc.GradSync([hc])
+    H = torch.randn(B, S, 4, D, device=DEV).bfloat16().requires_grad_(True)
+    g = torch.randn(B, S, 4, D, device=DEV).bfloat16()
+    out = {}
+
+    def step():
+        H.grad = None
+        bi, add = hc(H)
+        H_new = add(torch.tanh(bi))
+        H_new.backward(g)
+        out["H_new"], out["dH"] = H_new, H.grad
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            step()
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step()
+    static_new, static_dH = out["H_new"], out["dH"]
+    for seed in (1, 2):
+        torch.manual_seed(seed)
+        with torch.no_grad():
+            H.copy_(torch.randn(B, S, 4, D, device=DEV).bfloat16())
+            g.copy_(torch.randn(B, S, 4, D, device=DEV).bfloat16())
+        graph.replay()
+        torch.cuda.synchronize()
+        got = (static_new.clone(), static_dH.clone(), sync.flat.clone())
+        step()
+        torch.cuda.synchronize()
+        assert torch.equal(got[0], out["H_new"]) and torch.equal(got[1], out["dH"]) and torch.equal(got[2], sync.flat)
