@@ -290,12 +290,12 @@ def main():
     for _ in range(args.warmup):
         step()
     barrier()
-    # ---- survey pass (untimed): every kernel bracketed by events, to find the dominant one ----
+    # ---- breakdown pass (untimed): every kernel bracketed by events, to find the dominant one ----
     _lib.profile_start()
     for _ in range(3):
         (eager_step_with_hooks if args.graph else eager_step)()
-    survey = _lib.profile_stop()
-    dom = max((n for n in survey if n in OP_UNITS), key=lambda n: survey[n][1])
+    breakdown = _lib.profile_stop()
+    dom = max((n for n in breakdown if n in OP_UNITS), key=lambda n: breakdown[n][1])
     barrier()
     # ---- timed region: K steps, device-timed; only the dominant kernel's launches carry events ----
     _lib.profile_start(only=dom)
@@ -310,7 +310,7 @@ def main():
     ms = ev0.elapsed_time(ev1)
     launches = lib.mhc_launch_count() - n0
     timed_prof = _lib.profile_stop()
-    dom_calls, dom_ms = timed_prof.get(dom) or survey[dom]   # a replayed graph carries no events: use the survey pass
+    dom_calls, dom_ms = timed_prof.get(dom) or breakdown[dom]   # a replayed graph carries no events: use the breakdown pass
     t = torch.tensor([ms], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -322,10 +322,10 @@ def main():
     # ---- roofline of the dominant kernel (largest share of device time), timed inside the timed region ----
     peak, peak_kind = hbm_peak()
     per_op = {}
-    for name, (calls, total_ms) in survey.items():
+    for name, (calls, total_ms) in breakdown.items():
         units = OP_UNITS.get(name)
         avg_ms = total_ms / calls
-        ent = {"launches_per_step": calls / 3, "avg_ms": avg_ms, "share_of_kernel_time": total_ms / sum(v[1] for v in survey.values())}
+        ent = {"launches_per_step": calls / 3, "avg_ms": avg_ms, "share_of_kernel_time": total_ms / sum(v[1] for v in breakdown.values())}
         if units:
             ent["algorithmic_bytes"] = units * D * esz * B * S
             ent["gbs"] = ent["algorithmic_bytes"] / (avg_ms * 1e-3) / 1e9
@@ -395,7 +395,7 @@ def main():
                        "l2": "inputs larger than L2 (H alone is %.0f MiB per GPU)" % (B * S * 4 * D * esz / 2 ** 20),
                        "collective": "NCCL SUM all-reduce of phi/bias/alpha grads" if world > 1 else "none"},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches) * world,
-            "clocks": clocks.summary(), "kernels_survey_pass": per_op,
+            "clocks": clocks.summary(), "kernels_breakdown_pass": per_op,
         }
         print(json.dumps(line))
     if world > 1:

@@ -36,7 +36,9 @@ SAMPLE_STRIDE = 97
 
 
 def load_reference():
-    src = os.environ.get("MHC_REFERENCE_SRC", "/root/reference/src")
+    src = os.environ.get("MHC_REFERENCE_SRC")
+    if not src:
+        raise SystemExit("set MHC_REFERENCE_SRC to the src/ directory of a checkout of the reference project")
     path = os.path.join(src, "mhc", "_torch_baseline.py")
     sys.dont_write_bytecode = True
     spec = importlib.util.spec_from_file_location("mhc_reference_torch_baseline", path)
