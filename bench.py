@@ -56,12 +56,12 @@ TOTAL_UNITS = 46
 # summarised under profiles/, keyed by (workload, kernel); None = not captured.
 NCU_TRAFFIC = {
     # batch-2 capture x4 (traffic is proportional to the batch); writes still dirty in L2 at kernel end are not counted
-    ("c4", "k_stream_mix_bwd_apply"): 4 * (335.694080e6 + 212.609024e6),
-    ("c4", "k_stream_mix_fwd"): 4 * (268.447232e6 + 280.043776e6),
-    ("c4", "k_add_residual_fwd"): 4 * (335.556608e6 + 214.134272e6),
-    ("c4", "k_add_residual_bwd"): 4 * (335.559168e6 + 13.965568e6),
-    ("c4", "k_stream_mix_bwd_reduce"): 4 * (604.000512e6 + 3.906304e6),
-    ("c4", "k_meanpool_partial"): 4 * (268.491520e6 + 4.674048e6),
+    ("c4", "k_stream_mix_bwd_apply"): 4 * (335.689472e6 + 212.243712e6),
+    ("c4", "k_stream_mix_fwd"): 4 * (268.464896e6 + 278.717952e6),
+    ("c4", "k_add_residual_fwd"): 4 * (335.556864e6 + 217.698048e6),
+    ("c4", "k_add_residual_bwd"): 4 * (335.558400e6 + 13.125632e6),
+    ("c4", "k_stream_mix_bwd_reduce"): 4 * (604.000000e6 + 3.297792e6),
+    ("c4", "k_meanpool_partial"): 4 * (268.491776e6 + 3.950336e6),
 }
 
 

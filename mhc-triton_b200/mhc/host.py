@@ -59,9 +59,11 @@ class HostStreamedStep:
                 if free_ev[i % self.nslots] is not None:
                     self.s_in.wait_event(free_ev[i % self.nslots])
                 Hd[:n].copy_(H_host[lo:hi], non_blocking=True)
-                gd[:n].copy_(g_host[lo:hi], non_blocking=True)
                 ev_in = torch.cuda.Event()
-                ev_in.record(self.s_in)
+                ev_in.record(self.s_in)          # the forward needs only H ...
+                gd[:n].copy_(g_host[lo:hi], non_blocking=True)
+                ev_in_g = torch.cuda.Event()
+                ev_in_g.record(self.s_in)        # ... the upstream gradient arrives while it runs
             comp.wait_event(ev_in)
             Hin = Hd[:n].detach().requires_grad_(True)
             layer.grad_accumulate = i > 0
@@ -70,6 +72,7 @@ class HostStreamedStep:
             H_new = add(bi if self.branch is None else self.branch(bi))
             ev_fwd = torch.cuda.Event()
             ev_fwd.record(comp)
+            comp.wait_event(ev_in_g)
             H_new.backward(gd[:n])
             ev_bwd = torch.cuda.Event()
             ev_bwd.record(comp)
