@@ -150,7 +150,7 @@ k_add_residual_fwd(const T* __restrict__ Hr, const T* __restrict__ bo, const flo
 // i.e. after rounding to T).  Same layout as k_meanpool_partial's output, so the next layer's
 // projection kernel consumes it directly and that layer's pass over H for pooling disappears.
 #ifndef MHC_TPC_ADDPOOL
-#define MHC_TPC_ADDPOOL 64
+#define MHC_TPC_ADDPOOL 32
 #endif
 #ifndef MHC_ADDPOOL_PIPE
 #define MHC_ADDPOOL_PIPE 0

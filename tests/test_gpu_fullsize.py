@@ -99,3 +99,32 @@ def test_config4_layer_against_oracle_on_one_batch_element():
         if n.startswith("alpha"):
             continue   # three scalars with heavy cancellation; covered at reduced size against the storage-rounded oracle
         assert_close_norm(q.grad, ref["d" + n], 2e-2, 1e-6, n)
+
+
+def test_config3_layer_with_linear_branch_on_one_batch_element():
+    """config 3: bf16 H(8, 4096, 4, 2048), branch = bf16 Linear(2048 -> 2048), fwd + bwd; one batch
+    element against the fp64 oracle on the up-cast values (rtol 2e-2, norm-wise)."""
+    from mhc import HyperConnection
+    B, S, D = 8, 4096, 2048
+    H, g = _c4_inputs(B, S, D)
+    p = O.default_params(D, 0, 0.1)
+    gen = torch.Generator().manual_seed(0)
+    p.phi.copy_((torch.randn(24, 4 * D, generator=gen) * 0.02).T)
+    hc = to_module(HyperConnection(dim=D), p).to(DEV)
+    torch.manual_seed(0)
+    lin = torch.nn.Linear(D, D).bfloat16()
+    lin_d = torch.nn.Linear(D, D).bfloat16()
+    lin_d.load_state_dict(lin.state_dict())
+    lin_d = lin_d.to(DEV)
+    Hd = H.requires_grad_(True)
+    bi, add = hc(Hd)
+    H_new = add(lin_d(bi))
+    H_new.backward(g)
+    torch.cuda.synchronize()
+    b = 2
+    W, bias = lin.weight.detach().double(), lin.bias.detach().double()
+    ref = O.layer_fwd_bwd(p, H[b:b + 1].detach().float().cpu(), g[b:b + 1].float().cpu(),
+                          lambda t: t @ W.T + bias, "fused", dtype=torch.float64)
+    assert_close_norm(bi[b:b + 1], ref["branch_input"], 2e-2, 0, "branch_input")
+    assert_close_norm(H_new[b:b + 1], ref["H_new"], 2e-2, 0, "H_new")
+    assert_close_norm(Hd.grad[b:b + 1], ref["dH"], 2e-2, 0, "dH")
