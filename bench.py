@@ -40,9 +40,14 @@ WORKLOADS = {
     "c3": (8, 4096, 2048, torch.bfloat16),
     "c1": (2, 128, 512, torch.float32),
     "c5": (2, 4096, 7168, torch.bfloat16),   # the 16-layer stack, hyper-connection kernels only (identity branches)
+    # the reference README's own protocol: fp16 module and tensors, batch 16 x seq 2048, branch = 0.5 * branch_input,
+    # loss = H_new.sum() (so the upstream gradient arrives as an expanded scalar)
+    "readme": (16, 2048, 4096, torch.float16),
 }
 LAYERS = {"c5": 16}
 METRIC = "hc_fwd_bwd_tokens_per_s"
+# Published by the reference for the "readme" workload only: 13.66 ms per fwd+bwd of 32 768 tokens on one H100.
+README_PUBLISHED_TOKENS_PER_S = 32768 / 13.66e-3
 # Algorithmic HBM bytes per token, in units of D * element size: each logical tensor is read once
 # per consuming op and written once (mean-pool 4, stream mix 9, add residual 9, add-residual
 # backward 6, stream-mix backward: reduction pass 9 + apply pass 9).
@@ -236,16 +241,38 @@ def main():
     n_layers = args.layers or LAYERS.get(args.workload, 1)
     layers = [make_layer(D, dev) for _ in range(n_layers)]
     hc = layers[0]
-    sync = GradSync(layers, overlap=not args.no_overlap)
     lib = _lib.load()
+
+    readme = args.workload == "readme"
+    if readme:
+        for layer in layers:
+            layer.half()
+        args.no_e2e = True
+
+    class _NoSync:      # half-precision parameters: gradients flow through autograd, nothing to all-reduce at N=1
+        flat = torch.zeros(1)
+
+        def finish(self):
+            pass
+
+        def all_reduce_now(self):
+            pass
+
+    if readme and world > 1:
+        raise SystemExit("the readme workload is a single-GPU protocol")
+    sync = _NoSync() if readme else GradSync(layers, overlap=not args.no_overlap)
 
     def step():
         H.grad = None
         h = H
         for i, layer in enumerate(layers):
             bi, add = layer(h)
-            h = add(bi, pool_for_next=(i + 1 < n_layers and not args.no_cross_layer))   # identity branch
-        h.backward(g)
+            bo = bi * 0.5 if readme else bi                                    # identity branch unless "readme"
+            h = add(bo, pool_for_next=(i + 1 < n_layers and not args.no_cross_layer))
+        if readme:
+            h.sum().backward()
+        else:
+            h.backward(g)
         sync.finish()
         return h
 
@@ -388,7 +415,8 @@ def main():
         line = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": args.scaling,
-            "vs_baseline": None, "dtype": "bf16" if dtype == torch.bfloat16 else "f32", "data": "synthetic",
+            "vs_baseline": (value / README_PUBLISHED_TOKENS_PER_S) if readme else None,
+            "dtype": {torch.bfloat16: "bf16", torch.float16: "f16"}.get(dtype, "f32"), "data": "synthetic",
             "config": {"workload": describe(args.workload) + (f" [batch overridden to {B}]" if args.batch else ""),
                        "global_tokens": tokens, "sharding": f"batch x{world}", "per_gpu_batch": B, "layers": n_layers,
                        "cross_layer_pooling": n_layers > 1 and not args.no_cross_layer, "cuda_graph": bool(args.graph),

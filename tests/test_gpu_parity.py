@@ -610,3 +610,21 @@ def test_step_replayed_from_cuda_graph_equals_eager():
         step()
         torch.cuda.synchronize()
         assert torch.equal(got[0], out["H_new"]) and torch.equal(got[1], out["dH"]) and torch.equal(got[2], sync.flat)
+
+
+def test_whole_module_in_half_precision():
+    """The reference's benchmark casts the whole module to fp16 (parameters too): parameters are
+    up-cast per call, gradients come back in the parameters' dtype."""
+    import mhc
+    torch.manual_seed(3)
+    B, S, D = 2, 256, 256
+    H = torch.randn(B, S, 4, D).half()
+    up = torch.randn(B, S, 4, D).half()
+    p = cases.perturb_params_(O.default_params(D, 0, 0.1), 23)
+    hc = to_module(mhc.HyperConnection(dim=D), p).to(DEV).half()
+    p16 = O.LayerParams(**{k: v.half().float() for k, v in p.tensors().items()})   # what the module holds after .half()
+    out = _run_module(hc, H, up, lambda t: t * 0.5)
+    ref = O.layer_fwd_bwd(p16, H.float(), up.float(), lambda t: t * 0.5, "fused", dtype=torch.float64)
+    for k, v in out.items():
+        assert v.dtype == torch.float16, k
+        assert_close_norm(v, ref[k], 2e-2, 2e-3 if k.startswith("dalpha") else 1e-4, k)
