@@ -262,8 +262,13 @@ def main():
         raise SystemExit("the readme workload is a single-GPU protocol")
     sync = _NoSync() if readme else GradSync(layers, overlap=not args.no_overlap)
 
+    params = [q for layer in layers for q in layer.parameters()]
+
     def step():
         H.grad = None
+        if readme:
+            for q in params:
+                q.grad = None
         h = H
         for i, layer in enumerate(layers):
             bi, add = layer(h)
