@@ -313,6 +313,19 @@ __device__ __forceinline__ double warp_sum_f64(double v) {
   return v;
 }
 
+// sum_{c < n} p[c * stride] in fp64: four interleaved chains (c = 0,4,8,.. / 1,5,.. / ...) so that the
+// loads overlap, joined in a fixed order.  Used wherever the mean-pool's per-chunk sums are added.
+__device__ __forceinline__ double sum_strided_f64(const float* __restrict__ p, int64_t stride, int n) {
+  double t[4] = {0.0, 0.0, 0.0, 0.0};
+  int c = 0;
+  for (; c + 4 <= n; c += 4) {
+#pragma unroll
+    for (int u = 0; u < 4; ++u) t[u] += (double)__ldg(p + (int64_t)(c + u) * stride);
+  }
+  for (; c < n; ++c) t[0] += (double)__ldg(p + (int64_t)c * stride);
+  return (t[0] + t[1]) + (t[2] + t[3]);
+}
+
 // Column sums of a [slots, W] fp32 array (W <= 20) by a CTA of 256 threads: thread t adds rows
 // t, t+256, ... (all loads issued before any use), a xor-shuffle tree adds the lanes of each warp,
 // and after the barrier sm[w][j] holds warp w's sum of column j; callers add the 8 warps in index

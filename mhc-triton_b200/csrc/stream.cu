@@ -462,7 +462,7 @@ k_meanpool_partial(const T* __restrict__ H, float* __restrict__ part, Geo g) {
   }
 }
 
-// x[b,k] = scale * sum_chunk part[b, chunk, k], chunks added in index order in fp64.
+// x[b,k] = scale * sum_chunk part[b, chunk, k], chunks added in a fixed order in fp64.
 __global__ void __launch_bounds__(256)
 k_meanpool_finish(const float* __restrict__ part, float* __restrict__ x, int64_t K, int nchunk, double scale,
                   int64_t total) {
@@ -471,9 +471,7 @@ k_meanpool_finish(const float* __restrict__ part, float* __restrict__ x, int64_t
   if (i >= total) return;
   const int64_t b = i / K, k = i - b * K;
   const float* p = part + b * nchunk * K + k;
-  double s = 0.0;
-  for (int c = 0; c < nchunk; ++c) s += (double)__ldg(p + (int64_t)c * K);
-  x[i] = (float)(s * scale);
+  x[i] = (float)(sum_strided_f64(p, K, nchunk) * scale);
 }
 
 // out[b, j] = sum_p part[b, p, j] for j < W (W <= 20).  One CTA of 256 threads per batch element:

@@ -13,7 +13,7 @@ constexpr int kBwdStride = 56;   // per-row buffer of the backward: ds[24] d_raw
 constexpr int kMaxStoredIters = 64;
 
 static inline int k_slices(int64_t K) {
-  int64_t ks = (K + 511) / 512;
+  int64_t ks = (K + 255) / 256;
   if (ks > 128) ks = 128;
   if (ks < 1) ks = 1;
   return (int)ks;
@@ -63,9 +63,7 @@ k_dw_project(const float* __restrict__ xsrc, int nsrc, double scale, float* __re
     if (nsrc == 1) {
       xv = scale == 1.0 ? __ldg(xr + k) : (float)((double)__ldg(xr + k) * scale);
     } else {
-      double t = 0.0;
-      for (int c = 0; c < nsrc; ++c) t += (double)__ldg(xr + (int64_t)c * K + k);
-      xv = (float)(t * scale);
+      xv = (float)(sum_strided_f64(xr + k, K, nsrc) * scale);
     }
     if (x_out) x_out[row * K + k] = xv;
     float p[24];
