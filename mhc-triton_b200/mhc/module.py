@@ -105,6 +105,9 @@ class HyperConnection(nn.Module):
         return H_post.contiguous(), H_pre.contiguous(), H_res.contiguous()
 
     # -- forward ------------------------------------------------------------------------
+    # The kernels are reached through ctypes, which a tracing compiler cannot see into: under
+    # torch.compile the layer runs as an opaque eager call and the model around it is compiled.
+    @torch.compiler.disable
     def forward(self, H: torch.Tensor) -> Tuple[torch.Tensor, Callable[[torch.Tensor], torch.Tensor]]:
         if self.use_fused_weights:
             branch_input, H_residual, H_post, _, _ = hyper_connection_mix(

@@ -628,3 +628,31 @@ def test_whole_module_in_half_precision():
     for k, v in out.items():
         assert v.dtype == torch.float16, k
         assert_close_norm(v, ref[k], 2e-2, 2e-3 if k.startswith("dalpha") else 1e-4, k)
+
+
+def test_layer_inside_a_compiled_model():
+    """torch.compile of a model that contains the layer: the layer itself runs eagerly (opaque
+    call), results equal the uncompiled model."""
+    import mhc
+
+    class Block(torch.nn.Module):
+        def __init__(self, D):
+            super().__init__()
+            self.hc = mhc.HyperConnection(dim=D)
+            self.lin = torch.nn.Linear(D, D)
+
+        def forward(self, H):
+            bi, add = self.hc(H)
+            return add(torch.nn.functional.gelu(self.lin(bi))) * 1.5
+
+    torch.manual_seed(21)
+    D = 64
+    blk = Block(D).to(DEV)
+    with torch.no_grad():
+        blk.hc.phi.copy_(torch.randn(4 * D, 24, device=DEV) * 0.02)
+    H = torch.randn(2, 40, 4, D, device=DEV)
+    want = blk(H.clone().requires_grad_(True))
+    got = torch.compile(blk, backend="eager")(H.clone().requires_grad_(True))
+    assert torch.equal(got, want)
+    got.sum().backward()
+    assert blk.hc.phi.grad is not None and torch.isfinite(blk.hc.phi.grad).all()
