@@ -656,3 +656,21 @@ def test_layer_inside_a_compiled_model():
     assert torch.equal(got, want)
     got.sum().backward()
     assert blk.hc.phi.grad is not None and torch.isfinite(blk.hc.phi.grad).all()
+
+
+def test_per_token_weights_through_reshape():
+    """The paper's per-token formulation (weights from every token's own 4*D state, not from the
+    sequence mean) is the same layer applied to H viewed as [B*S, 1, 4, D]: every entry point
+    takes any number of rows, so it runs correctly today (slowly: the projection is not tiled
+    over rows yet)."""
+    import mhc
+    torch.manual_seed(31)
+    B, S, D = 2, 37, 48
+    H = torch.randn(B * S, 1, 4, D)
+    up = torch.randn(B * S, 1, 4, D)
+    p = cases.perturb_params_(O.default_params(D, 0, 0.1), 19)
+    hc = to_module(mhc.HyperConnection(dim=D), p).to(DEV)
+    out = _run_module(hc, H, up, lambda t: torch.tanh(t))
+    ref = O.layer_fwd_bwd(p, H, up, torch.tanh, "fused", dtype=torch.float64)
+    for k, v in out.items():
+        assert_close_norm(v, ref[k], 1e-4 if k.startswith("d") else RT, 4 * AT, k)
