@@ -15,7 +15,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "mhc", "libmhc_b200.so")
-SOURCES = ["api.cu", "sinkhorn.cu", "stream.cu", "weights.cu", "fused.cu", "noalloc.cu"]
+SOURCES = ["api.cu", "sinkhorn.cu", "stream.cu", "weights.cu", "weights_rows.cu", "fused.cu", "noalloc.cu"]
 HEADERS = ["common.cuh", "launch.h", os.path.join("..", "..", "include", "mhc_b200.h")]
 
 

@@ -90,6 +90,14 @@ int weights_bwd_impl(const float* x, const float* phi, BiasPtrs bias, const floa
                      float* grad_alpha, float* buf, int64_t batch, int64_t K, int iters, float eps,
                      int abs_grad_at_zero, int accumulate_params, cudaStream_t st);
 
+// Many-rows variants (weights_rows.cu), used from kManyRows rows on.
+constexpr int64_t kManyRows = 64;
+int phi_row_tiles(int64_t batch);
+int project_rows_launch(const float* x, const float* phi, float* part, int64_t batch, int64_t K, int ks_max,
+                        cudaStream_t st, int* ks_used);
+int bwd_rows_launch(const float* x, const float* phi, const float* buf, float* phi_part, float* grad_x, float* grad_phi,
+                    float* grad_bias, float* grad_alpha, int64_t batch, int64_t K, int accumulate, cudaStream_t st);
+
 int64_t weights_fwd_scratch_bytes(int64_t batch, int64_t K);
 int64_t weights_bwd_scratch_bytes(int64_t batch, int64_t K);
 

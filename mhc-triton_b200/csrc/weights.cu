@@ -23,8 +23,9 @@ int64_t weights_fwd_scratch_bytes(int64_t batch, int64_t K) {
   return batch * k_slices(K) * kProjW * (int64_t)sizeof(float);
 }
 int64_t weights_bwd_scratch_bytes(int64_t batch, int64_t K) {
-  (void)K;
-  return batch * kBwdStride * (int64_t)sizeof(float);
+  int64_t n = batch * kBwdStride;                                   // per-row records
+  if (batch >= kManyRows) n += (int64_t)phi_row_tiles(batch) * K * 24;  // grad_phi partial sums per row tile
+  return n * (int64_t)sizeof(float);
 }
 
 __device__ __forceinline__ void load_phi_row(const float* __restrict__ phi, int64_t k, bool aligned, float (&p)[24]) {
@@ -335,13 +336,16 @@ int weights_fwd_impl(const float* xsrc, int nsrc, double scale, float* x_out, co
                      const float* alpha_pre, const float* alpha_post, const float* alpha_res, float* H_pre,
                      float* H_post, float* H_res, float* saved, float* part, int64_t batch, int64_t K, int iters,
                      float eps, cudaStream_t st) {
-  const int ks = k_slices(K);
-  if (batch * ks > kMaxGridItems) return fail(MHC_ERR_BAD_SHAPE, "dynamic_weights_fwd: batch too large");
-  {
+  int ks = k_slices(K);
+  if (nsrc == 1 && scale == 1.0 && !x_out && batch >= kManyRows) {
+    if (int e = project_rows_launch(xsrc, phi, part, batch, K, ks, st, &ks)) return e;
+  } else {
+    if (batch * ks > kMaxGridItems) return fail(MHC_ERR_BAD_SHAPE, "dynamic_weights_fwd: batch too large");
     ProfScope ps("k_dw_project", st);
     launch_k(k_dw_project, (unsigned)(batch * ks), 256, 0, st, xsrc, nsrc, scale, x_out, phi, part, K, ks, is_aligned16(phi));
   }
-  if (int e = check_launch("dynamic_weights_fwd(project)")) return e;
+  if (!(nsrc == 1 && scale == 1.0 && !x_out && batch >= kManyRows))
+    if (int e = check_launch("dynamic_weights_fwd(project)")) return e;
   {
     ProfScope ps("k_dw_finish", st);
     launch_k(k_dw_finish, (unsigned)batch, 32, 0, st, part, bias, alpha_pre, alpha_post, alpha_res, H_pre, H_post, H_res,
@@ -359,12 +363,15 @@ int weights_bwd_impl(const float* x, const float* phi, BiasPtrs bias, const floa
   if (batch) {
     {
       ProfScope ps("k_dw_bwd_rows", st);
-      launch_k(k_dw_bwd_rows, (unsigned)batch, 256, 0, st, saved, bias, alpha_pre, alpha_post, alpha_res, part20, slots,
+      launch_k(k_dw_bwd_rows, (unsigned)batch, part20 ? 256 : 32, 0, st, saved, bias, alpha_pre, alpha_post, alpha_res, part20, slots,
                                                      dH_pre, dH_post, dH_res, buf, K, iters, eps,
                                                      abs_grad_at_zero == MHC_ABS0_PLUS_ONE ? 1.f : 0.f);
     }
     if (int e = check_launch("dynamic_weights_bwd(rows)")) return e;
   }
+  if (batch >= kManyRows)
+    return bwd_rows_launch(x, phi, buf, buf + batch * kBwdStride, grad_x, grad_phi, grad_bias, grad_alpha, batch, K,
+                           accumulate_params, st);
   const int64_t kblocks = (K + 255) / 256;
   {
     ProfScope ps("k_dw_bwd_main", st);

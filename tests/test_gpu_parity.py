@@ -674,3 +674,24 @@ def test_per_token_weights_through_reshape():
     ref = O.layer_fwd_bwd(p, H, up, torch.tanh, "fused", dtype=torch.float64)
     for k, v in out.items():
         assert_close_norm(v, ref[k], 1e-4 if k.startswith("d") else RT, 4 * AT, k)
+
+
+@pytest.mark.parametrize("B,K", [(64, 4 * 64), (200, 4 * 100 + 4), (1000, 4 * 256)])
+def test_dynamic_weights_many_rows(B, K):
+    """From 64 rows on the op switches to kernels tiled over rows (per-token use); same results."""
+    from mhc import fused_dynamic_weights
+    torch.manual_seed(B + K)
+    x = torch.randn(B, K)
+    phi = torch.randn(K, 24) * 0.05
+    bias = torch.randn(24)
+    al = [torch.tensor([0.3]), torch.tensor([-0.2]), torch.tensor([0.5])]
+    gp, gq, gr = torch.randn(B, 4), torch.randn(B, 4), torch.randn(B, 4, 4)
+    ref = [t.double().requires_grad_(True) for t in (x, phi, bias, *al)]
+    a, b, c = O.dynamic_weights(*ref, 20, 1e-6)
+    ((a * gp).sum() + (b * gq).sum() + (c * gr).sum()).backward()
+    lv = [dev(t).requires_grad_(True) for t in (x, phi, bias, *al)]
+    a2, b2, c2 = fused_dynamic_weights(*lv, 20, 1e-6)
+    assert_close(a2, a, RT, AT, "H_pre"); assert_close(b2, b, RT, AT, "H_post"); assert_close(c2, c, 2e-5, AT, "H_res")
+    ((a2 * dev(gp)).sum() + (b2 * dev(gq)).sum() + (c2 * dev(gr)).sum()).backward()
+    for r, l, n in zip(ref, lv, "x phi bias a_pre a_post a_res".split()):
+        assert_close_norm(l.grad, r.grad, 1e-4, 1e-6, "d" + n)
