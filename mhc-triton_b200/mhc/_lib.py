@@ -145,7 +145,9 @@ def ptr(t):
 
 
 def stream_of(t: torch.Tensor):
-    return torch.cuda.current_stream(t.device).cuda_stream
+    """Raw cudaStream_t of torch's current stream on t's device."""
+    return torch._C._cuda_getCurrentRawStream(t.device.index if t.device.index is not None
+                                              else torch.cuda.current_device())
 
 
 def scratch(op, B, S, D, like: torch.Tensor):

@@ -17,6 +17,10 @@ from ._kernels import (add_residual_forward, fused_dynamic_weights_forward, hc_m
                        sinkhorn_forward, stream_mix_forward)
 
 
+# The public functions below are opaque to torch.compile (the kernels are reached through ctypes):
+# a compiled model calls them eagerly and compiles what surrounds them.
+
+
 class _SinkhornKnopp(torch.autograd.Function):
     """Saves only M; the backward recomputes the iterations (reference: src/mhc/ops.py:15-29)."""
 
@@ -173,18 +177,21 @@ class _HyperConnectionMix(torch.autograd.Function):
                 galpha[2:3].reshape_as(alpha_res).to(alpha_res.dtype), None, None, None, None, None, None)
 
 
+@torch.compiler.disable
 def sinkhorn_knopp(M: torch.Tensor, num_iters: int = 20, eps: float = 1e-8) -> torch.Tensor:
     """Project (batch, 4, 4) matrices to (approximately) doubly stochastic ones by `num_iters`
     alternating row / column normalisations of |M| + eps."""
     return _SinkhornKnopp.apply(M, num_iters, eps)
 
 
+@torch.compiler.disable
 def fused_stream_mix(H: torch.Tensor, H_pre: torch.Tensor, H_res: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     """H (batch, seq, 4, dim), H_pre (batch, 4), H_res (batch, 4, 4) ->
     branch_input (batch, seq, dim), H_residual (batch, seq, 4, dim)."""
     return _FusedStreamMix.apply(H, H_pre, H_res)
 
 
+@torch.compiler.disable
 def fused_add_residual(H_residual: torch.Tensor, branch_output: torch.Tensor, H_post: torch.Tensor,
                        pool_for_next: bool = False) -> torch.Tensor:
     """H_new[n] = H_residual[n] + H_post[n] * branch_output, per batch element.
@@ -212,6 +219,7 @@ def pooled_sums_of(H: torch.Tensor):
     return partials
 
 
+@torch.compiler.disable
 def fused_dynamic_weights(x, phi, bias, alpha_pre, alpha_post, alpha_res, sinkhorn_iters: int = 20,
                           eps: float = 1e-6) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """x [batch, in_dim], phi [in_dim, 24], bias [24], three one-element scale tensors ->
@@ -220,11 +228,13 @@ def fused_dynamic_weights(x, phi, bias, alpha_pre, alpha_post, alpha_res, sinkho
     return _FusedDynamicWeights.apply(x, phi, bias, alpha_pre, alpha_post, alpha_res, sinkhorn_iters, eps)
 
 
+@torch.compiler.disable
 def sequence_mean_pool(H: torch.Tensor) -> torch.Tensor:
     """H (batch, seq, 4, dim) -> fp32 (batch, 4*dim) mean over the sequence axis."""
     return _SequenceMeanPool.apply(H)
 
 
+@torch.compiler.disable
 def hyper_connection_mix(H, H_pre_base, H_post_base, H_res_base, phi, alpha_pre, alpha_post, alpha_res,
                          sinkhorn_iters: int = 20, eps: float = 1e-6, grad_sink=None, ready_hook=None,
                          accumulate: bool = False, pooled=None):
