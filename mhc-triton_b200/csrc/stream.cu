@@ -10,7 +10,15 @@
 
 namespace mhc {
 
-// Tuning knobs (compile-time): software pipelining and minimum resident CTAs per kernel.
+// Tuning constants.  The defaults are the best configuration found by sweeps on a B200 with bf16
+// H(8, 4096, 4, 4096); `build.py -D NAME=value --out other.so` builds a variant and the environment
+// variable MHC_B200_LIB points the Python package at it.
+//   *_PIPE  1: prefetch the next token's packs while computing the current one (worth it when few
+//              CTAs fit an SM);  0: rely on more resident CTAs instead.
+//   *_MINB  minimum resident CTAs per SM asked of the compiler (caps the registers per thread).
+//   *_TPC   tokens walked by one CTA.  Short chunks make consecutive CTAs sweep memory almost
+//           linearly (faster), long chunks amortise per-CTA state (coefficients, grad_x columns,
+//           partial sums).
 #ifndef MHC_MIXFWD_PIPE
 #define MHC_MIXFWD_PIPE 0
 #endif
