@@ -43,6 +43,9 @@ namespace mhc {
 #ifndef MHC_POOL_COLS
 #define MHC_POOL_COLS 64
 #endif
+#ifndef MHC_POOL_THREADS
+#define MHC_POOL_THREADS 256
+#endif
 // Walking direction per kernel (bit set = from the end of the tensor to its start): bit 0 mean-pool,
 // 1 stream mix, 2 add residual, 3 add-residual backward, 4 stream-mix backward reduce / full,
 // 5 stream-mix backward apply.  Consecutive kernels of a layer step walk in opposite directions so
@@ -167,7 +170,7 @@ template <typename T, int V>
 __global__ void __launch_bounds__(MHC_MAX_COLS, 2)
 k_add_residual_pool_fwd(const T* __restrict__ Hr, const T* __restrict__ bo, const float* __restrict__ Hpost,
                         T* __restrict__ Hn, float* __restrict__ pool, Geo g) {
-  extern __shared__ float sm[];  // [4*V][sub][cols], used when several tokens are walked abreast
+  extern __shared__ float sm[];  // [2*V][sub][cols], used when several tokens are walked abreast
   pdl_prologue();
   const Item it = decode_item(g);
   const int64_t D = g.D, c0 = (int64_t)it.col * V, tok = it.b * g.S;
@@ -206,21 +209,25 @@ k_add_residual_pool_fwd(const T* __restrict__ Hr, const T* __restrict__ bo, cons
         });
   }
   const int c = threadIdx.x % g.cols;
-  if (g.sub > 1) {
+  if (g.sub > 1) {  // add the sub-groups in index order, two stream rows at a time (halves the shared memory)
 #pragma unroll
-    for (int n = 0; n < 4; ++n)
+    for (int half = 0; half < 2; ++half) {
+      if (half) __syncthreads();
 #pragma unroll
-      for (int e = 0; e < V; ++e) sm[((n * V + e) * g.sub + it.sub) * g.cols + c] = acc[n][e];
-    __syncthreads();
-    if (it.sub == 0) {
+      for (int n = 0; n < 2; ++n)
 #pragma unroll
-      for (int n = 0; n < 4; ++n)
+        for (int e = 0; e < V; ++e) sm[((n * V + e) * g.sub + it.sub) * g.cols + c] = acc[2 * half + n][e];
+      __syncthreads();
+      if (it.sub == 0) {
 #pragma unroll
-        for (int e = 0; e < V; ++e) {
-          float t = acc[n][e];
-          for (int j = 1; j < g.sub; ++j) t += sm[((n * V + e) * g.sub + j) * g.cols + c];
-          acc[n][e] = t;
-        }
+        for (int n = 0; n < 2; ++n)
+#pragma unroll
+          for (int e = 0; e < V; ++e) {
+            float t = acc[2 * half + n][e];
+            for (int j = 1; j < g.sub; ++j) t += sm[((n * V + e) * g.sub + j) * g.cols + c];
+            acc[2 * half + n][e] = t;
+          }
+      }
     }
   }
   if (live && it.sub == 0) {
@@ -404,10 +411,10 @@ k_stream_mix_bwd_apply(const T* __restrict__ dbi, const T* __restrict__ dHr, con
 // blockDim.x = cols * sub: thread (col, j) sums tokens j, j+sub, ... of the chunk (two tokens in
 // flight); the sub-groups are then added in index order through shared memory.
 template <typename T, int V>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(MHC_POOL_THREADS)
 k_meanpool_partial(const T* __restrict__ H, float* __restrict__ part, Geo g) {
   pdl_prologue();
-  extern __shared__ float sm[];  // [4*V][sub][cols]
+  extern __shared__ float sm[];  // [2*V][sub][cols]
   const Item it = decode_item(g);
   const int64_t D = g.D, c0 = (int64_t)it.col * V, tok = it.b * g.S;
   float acc[4][V];
@@ -444,21 +451,25 @@ k_meanpool_partial(const T* __restrict__ H, float* __restrict__ part, Geo g) {
         });
   }
   const int c = threadIdx.x % g.cols;
-  if (g.sub > 1) {
+  if (g.sub > 1) {  // add the sub-groups in index order, two stream rows at a time (halves the shared memory)
 #pragma unroll
-    for (int n = 0; n < 4; ++n)
+    for (int half = 0; half < 2; ++half) {
+      if (half) __syncthreads();
 #pragma unroll
-      for (int e = 0; e < V; ++e) sm[((n * V + e) * g.sub + it.sub) * g.cols + c] = acc[n][e];
-    __syncthreads();
-    if (it.sub == 0) {
+      for (int n = 0; n < 2; ++n)
 #pragma unroll
-      for (int n = 0; n < 4; ++n)
+        for (int e = 0; e < V; ++e) sm[((n * V + e) * g.sub + it.sub) * g.cols + c] = acc[2 * half + n][e];
+      __syncthreads();
+      if (it.sub == 0) {
 #pragma unroll
-        for (int e = 0; e < V; ++e) {
-          float t = acc[n][e];
-          for (int j = 1; j < g.sub; ++j) t += sm[((n * V + e) * g.sub + j) * g.cols + c];
-          acc[n][e] = t;
-        }
+        for (int n = 0; n < 2; ++n)
+#pragma unroll
+          for (int e = 0; e < V; ++e) {
+            float t = acc[2 * half + n][e];
+            for (int j = 1; j < g.sub; ++j) t += sm[((n * V + e) * g.sub + j) * g.cols + c];
+            acc[2 * half + n][e] = t;
+          }
+      }
     }
   }
   if (live && it.sub == 0) {
@@ -517,7 +528,7 @@ Geo make_geo(int64_t S, int64_t D, int vec, GeoKind kind, int tpc) {
   g.cols = cols;
   g.CG = (g.DV + cols - 1) / cols;
   if (pool) {
-    g.sub = 256 / cols;
+    g.sub = MHC_POOL_THREADS / cols;
     g.tpc = MHC_POOL_TPC;
   } else {
     // Tokens per CTA: a per-kernel constant, so the chunking (and with it the layout of the per-CTA
@@ -592,7 +603,7 @@ int meanpool_partial_impl(const void* H, float* part, int64_t B, int64_t S, int6
   g.reverse = MHC_REV_MASK & 1;
   const int64_t items = B * geo_slots(g);
   if (int e = check_grid("meanpool_fwd", items)) return e;
-  const size_t smem = (size_t)4 * vec * geo_block(g) * sizeof(float);
+  const size_t smem = (size_t)2 * vec * geo_block(g) * sizeof(float);
   {
     ProfScope ps("k_meanpool_partial", st);
     MHC_DISPATCH(dtype, vec, (launch_k(k_meanpool_partial<T, V>, (unsigned)items, geo_block(g), smem, st, (const T*)H, part, g)));
@@ -730,7 +741,7 @@ extern "C" int mhc_add_residual_pool_fwd(const void* H_residual, const void* bra
   const int64_t items = B * geo_slots(g);
   if (int e = check_grid("add_residual_pool_fwd", items)) return e;
   cudaStream_t st = (cudaStream_t)stream;
-  const size_t smem = g.sub > 1 ? (size_t)4 * vec * geo_block(g) * sizeof(float) : 0;
+  const size_t smem = g.sub > 1 ? (size_t)2 * vec * geo_block(g) * sizeof(float) : 0;
   {
     ProfScope ps("k_add_residual_pool_fwd", st);
     MHC_DISPATCH(dtype, vec, (launch_k(k_add_residual_pool_fwd<T, V>, (unsigned)items, geo_block(g), smem, st,
