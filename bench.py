@@ -52,7 +52,8 @@ README_PUBLISHED_TOKENS_PER_S = 32768 / 13.66e-3
 # per consuming op and written once (mean-pool 4, stream mix 9, add residual 9, add-residual
 # backward 6, stream-mix backward: reduction pass 9 + apply pass 9).
 OP_UNITS = {
-    "k_meanpool_partial": 4, "k_stream_mix_fwd": 9, "k_add_residual_fwd": 9, "k_add_residual_pool_fwd": 9,
+    "k_meanpool_partial": 4, "k_stream_mix_fwd": 9, "k_stream_premix_fwd": 5, "k_add_residual_mix_fwd": 9,
+    "k_add_residual_mix_pool_fwd": 9, "k_add_residual_fwd": 9, "k_add_residual_pool_fwd": 9,
     "k_add_residual_bwd": 6,
     "k_stream_mix_bwd_reduce": 9, "k_stream_mix_bwd_apply": 9,
 }

@@ -142,6 +142,17 @@ int mhc_add_residual_fwd(const void* H_residual, const void* branch_output, cons
  * mhc_hc_mix_fwd as pooled_partials.  The next layer then reads H once instead of twice
  * (the reference reads it twice: H.mean(dim=1), src/mhc/module.py:123, then the stream-mix
  * kernel, src/mhc/_kernels.py:137-236).  H_new is identical to mhc_add_residual_fwd's. */
+/* Add residual with the residual mix recomputed from H instead of read from a materialised
+ * H_residual: H_new[b,s,n,d] = (sum_m H_res[b,n,m] H[b,s,m,d]) + H_post[b,n] branch_output[b,s,d].
+ * Together with mhc_hc_mix_fwd called with H_residual == NULL (which then writes branch_input
+ * only) this removes the write and the read-back of H_residual from a layer step.  pool_partials
+ * may be NULL; if given it receives the token sums of H_new as in mhc_add_residual_pool_fwd.
+ * Fuses add_residual_forward (src/mhc/_kernels.py:655-687) with the residual half of
+ * stream_mix_forward (src/mhc/_kernels.py:617-652, kernel lines :227-230). */
+int mhc_add_residual_mix_fwd(const void* H, const float* H_res, const void* branch_output,
+                             const float* H_post, void* H_new, float* pool_partials, int64_t B,
+                             int64_t S, int64_t D, int dtype, mhc_stream_t stream);
+
 int mhc_add_residual_pool_fwd(const void* H_residual, const void* branch_output, const float* H_post,
                               void* H_new, float* pool_partials, int64_t B, int64_t S, int64_t D,
                               int dtype, mhc_stream_t stream);
@@ -209,7 +220,8 @@ int mhc_dynamic_weights_bwd(const float* x, const float* phi, const float* bias,
  * the dynamic weights from x (bias given as the three base parameters, pre [4], post [4],
  * res [16]), then the stream mix.  If pooled_partials is not NULL it holds the token sums of H
  * as left by mhc_add_residual_pool_fwd of the previous layer ([B, pooled_chunks, 4*D] fp32) and
- * the pass over H for pooling is skipped.  Replaces the chain HyperConnection._compute_weights (fused
+ * the pass over H for pooling is skipped.  H_residual may be NULL: only branch_input is then
+ * written and the caller uses mhc_add_residual_mix_fwd afterwards.  Replaces the chain HyperConnection._compute_weights (fused
  * branch, src/mhc/module.py:119-139) + fused_stream_mix (src/mhc/module.py:177). */
 int mhc_hc_mix_fwd(const void* H, const float* phi, const float* H_pre_base, const float* H_post_base,
                    const float* H_res_base, const float* alpha_pre, const float* alpha_post,

@@ -19,7 +19,7 @@ extern "C" int mhc_hc_mix_fwd(const void* H, const float* phi, const float* H_pr
   if (B == 0) return MHC_OK;
   if (S == 0 || D == 0) return fail(MHC_ERR_BAD_SHAPE, "hc_mix_fwd: empty sequence or width");
   if (!H || !phi || !H_pre_base || !H_post_base || !H_res_base || !alpha_pre || !alpha_post || !alpha_res || !x ||
-      !H_pre || !H_post || !H_res || !saved || !branch_input || !H_residual || !scratch)
+      !H_pre || !H_post || !H_res || !saved || !branch_input || !scratch)
     return fail(MHC_ERR_NULL_POINTER, "hc_mix_fwd: null pointer");
   const int64_t pool_floats = meanpool_scratch_floats(B, S, D);
   const int64_t need = pool_floats * (int64_t)sizeof(float) + weights_fwd_scratch_bytes(B, 4 * D);

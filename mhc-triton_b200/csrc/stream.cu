@@ -121,6 +121,39 @@ k_stream_mix_fwd(const T* __restrict__ H, const float* __restrict__ Hpre, const 
       });
 }
 
+// Pre-mix only: branch_input[s,d] = sum_n H_pre[n] H[s,n,d].  Used when the residual mix is not
+// materialised (it is then recomputed from H inside k_add_residual_mix_fwd).
+#ifndef MHC_TPC_PREMIX
+#define MHC_TPC_PREMIX 2
+#endif
+template <typename T, int V>
+__global__ void __launch_bounds__(MHC_MAX_COLS, 4)
+k_stream_premix_fwd(const T* __restrict__ H, const float* __restrict__ Hpre, T* __restrict__ bi, Geo g) {
+  pdl_prologue();
+  const Item it = decode_item(g);
+  if (it.col >= g.DV) return;
+  float w[4];
+#pragma unroll
+  for (int n = 0; n < 4; ++n) w[n] = __ldg(Hpre + it.b * 4 + n);
+  const int64_t D = g.D, c0 = (int64_t)it.col * V, tok = it.b * g.S;
+  using B4 = Bundle<T, V, 4>;
+  for_tokens_pipelined<B4>(
+      it.s0 + it.sub, it.s1, g.sub,
+      [&](B4& u, int64_t s) {
+        const T* h = H + (tok + s) * 4 * D + c0;
+#pragma unroll
+        for (int n = 0; n < 4; ++n) u.p[n] = ld_raw<T, V>(h + n * D);
+      },
+      [&](const B4& u, int64_t s) {
+        float y[V];
+#pragma unroll
+        for (int e = 0; e < V; ++e)
+          y[e] = ((w[0] * raw_get<V>(u.p[0], e) + w[1] * raw_get<V>(u.p[1], e)) + w[2] * raw_get<V>(u.p[2], e)) +
+                 w[3] * raw_get<V>(u.p[3], e);
+        PackIO<T, V>::store(bi + (tok + s) * D + c0, y);
+      });
+}
+
 // ------------------------------------------------------------------------------ add residual
 template <typename T, int V>
 __global__ void __launch_bounds__(MHC_MAX_COLS, MHC_ADDFWD_MINB)
@@ -236,6 +269,107 @@ k_add_residual_pool_fwd(const T* __restrict__ Hr, const T* __restrict__ bo, cons
     for (int n = 0; n < 4; ++n)
 #pragma unroll
       for (int e = 0; e < V; ++e) o[n * D + e] = acc[n][e];
+  }
+}
+
+// H_new[s,n,d] = (sum_m H_res[n,m] H[s,m,d]) + H_post[n] branch_output[s,d]: the residual mix is
+// recomputed from H here instead of being written by the stream-mix kernel and read back (saves
+// 8 of the 46 D*e bytes per token of a layer step).  The sum is formed first and the branch term
+// added last, the order the two separate kernels use.  POOL: also leave the per-chunk token sums
+// of H_new for the next layer (see k_add_residual_pool_fwd).
+#ifndef MHC_TPC_ADDMIX
+#define MHC_TPC_ADDMIX 1
+#endif
+#ifndef MHC_ADDMIX_PIPE
+#define MHC_ADDMIX_PIPE 0
+#endif
+#ifndef MHC_ADDMIX_MINB
+#define MHC_ADDMIX_MINB 3
+#endif
+template <typename T, int V, bool POOL>
+__global__ void __launch_bounds__(MHC_MAX_COLS, POOL ? 2 : MHC_ADDMIX_MINB)
+k_add_residual_mix_fwd(const T* __restrict__ H, const float* __restrict__ Hres, const T* __restrict__ bo,
+                       const float* __restrict__ Hpost, T* __restrict__ Hn, float* __restrict__ pool, Geo g) {
+  extern __shared__ float sm[];  // POOL: [2*V][sub][cols]
+  pdl_prologue();
+  const Item it = decode_item(g);
+  const int64_t D = g.D, c0 = (int64_t)it.col * V, tok = it.b * g.S;
+  float acc[POOL ? 4 : 1][V];
+  if (POOL) {
+#pragma unroll
+    for (int n = 0; n < 4; ++n)
+#pragma unroll
+      for (int e = 0; e < V; ++e) acc[POOL ? n : 0][e] = 0.f;
+  }
+  const bool live = it.col < g.DV;
+  if (!POOL && !live) return;
+  if (live) {
+    float p[4], R[16];
+#pragma unroll
+    for (int n = 0; n < 4; ++n) p[n] = __ldg(Hpost + it.b * 4 + n);
+#pragma unroll
+    for (int k = 0; k < 16; ++k) R[k] = __ldg(Hres + it.b * 16 + k);
+    using B5 = Bundle<T, V, 5>;
+    for_tokens<(!POOL && MHC_ADDMIX_PIPE != 0), B5>(
+        it.s0 + it.sub, it.s1, g.sub,
+        [&](B5& u, int64_t s) {
+          const T* h = H + (tok + s) * 4 * D + c0;
+          u.p[4] = ld_raw<T, V>(bo + (tok + s) * D + c0);
+#pragma unroll
+          for (int n = 0; n < 4; ++n) u.p[n] = ld_raw<T, V>(h + n * D);
+        },
+        [&](const B5& u, int64_t s) {
+          float x[4][V], y[V], o[V];
+          unpack<T, V>(u.p[4], y);
+#pragma unroll
+          for (int n = 0; n < 4; ++n) unpack<T, V>(u.p[n], x[n]);
+          T* op = Hn + (tok + s) * 4 * D + c0;
+#pragma unroll
+          for (int n = 0; n < 4; ++n) {
+#pragma unroll
+            for (int e = 0; e < V; ++e)
+              o[e] = (((R[4 * n] * x[0][e] + R[4 * n + 1] * x[1][e]) + R[4 * n + 2] * x[2][e]) + R[4 * n + 3] * x[3][e]) +
+                     p[n] * y[e];
+            if (POOL) {
+              PackIO<T, V>::store_round(op + n * D, o);
+#pragma unroll
+              for (int e = 0; e < V; ++e) acc[POOL ? n : 0][e] += o[e];
+            } else {
+              PackIO<T, V>::store(op + n * D, o);
+            }
+          }
+        });
+  }
+  if (POOL) {
+    const int c = threadIdx.x % g.cols;
+    if (g.sub > 1) {
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        if (half) __syncthreads();
+#pragma unroll
+        for (int n = 0; n < 2; ++n)
+#pragma unroll
+          for (int e = 0; e < V; ++e) sm[((n * V + e) * g.sub + it.sub) * g.cols + c] = acc[POOL ? 2 * half + n : 0][e];
+        __syncthreads();
+        if (it.sub == 0) {
+#pragma unroll
+          for (int n = 0; n < 2; ++n)
+#pragma unroll
+            for (int e = 0; e < V; ++e) {
+              float t = acc[POOL ? 2 * half + n : 0][e];
+              for (int j = 1; j < g.sub; ++j) t += sm[((n * V + e) * g.sub + j) * g.cols + c];
+              acc[POOL ? 2 * half + n : 0][e] = t;
+            }
+        }
+      }
+    }
+    if (live && it.sub == 0) {
+      float* o = pool + (it.b * g.nchunk + it.chunk) * 4 * D + c0;
+#pragma unroll
+      for (int n = 0; n < 4; ++n)
+#pragma unroll
+        for (int e = 0; e < V; ++e) o[n * D + e] = acc[POOL ? n : 0][e];
+    }
   }
 }
 
@@ -585,7 +719,15 @@ int stream_mix_fwd_impl(const void* H, const float* H_pre, const float* H_res, v
   g.reverse = (MHC_REV_MASK >> 1) & 1;
   const int64_t items = B * geo_slots(g);
   if (int e = check_grid("stream_mix_fwd", items)) return e;
-  {
+  if (!Hr) {  // branch_input only; the residual mix is recomputed by mhc_add_residual_mix_fwd
+    Geo gp = make_geo(S, D, vec, GeoKind::Stream, MHC_TPC_PREMIX);
+    gp.reverse = g.reverse;
+    const int64_t n = B * geo_slots(gp);
+    if (int e = check_grid("stream_mix_fwd", n)) return e;
+    ProfScope ps("k_stream_premix_fwd", st);
+    MHC_DISPATCH(dtype, vec, (launch_k(k_stream_premix_fwd<T, V>, (unsigned)n, geo_block(gp), 0, st, (const T*)H, H_pre,
+                                       (T*)bi, gp)));
+  } else {
     ProfScope ps("k_stream_mix_fwd", st);
     MHC_DISPATCH(dtype, vec, (launch_k(k_stream_mix_fwd<T, V>, (unsigned)items, geo_block(g), 0, st, 
                                  (const T*)H, H_pre, H_res, (T*)bi, (T*)Hr, g)));
@@ -716,6 +858,39 @@ extern "C" int mhc_add_residual_fwd(const void* H_residual, const void* branch_o
                                  (const T*)H_residual, (const T*)branch_output, H_post, (T*)H_new, g)));
   }
   return check_launch("add_residual_fwd");
+}
+
+extern "C" int mhc_add_residual_mix_fwd(const void* H, const float* H_res, const void* branch_output,
+                                        const float* H_post, void* H_new, float* pool_partials, int64_t B, int64_t S,
+                                        int64_t D, int dtype, mhc_stream_t stream) {
+  if (int e = check_bsd("add_residual_mix_fwd", B, S, D, dtype)) return e;
+  if (B == 0 || S == 0 || D == 0) return MHC_OK;
+  if (!H || !H_res || !branch_output || !H_post || !H_new)
+    return fail(MHC_ERR_NULL_POINTER, "add_residual_mix_fwd: null pointer");
+  const int vec = pick_vec(dtype, D, {H, branch_output, H_new});
+  cudaStream_t st = (cudaStream_t)stream;
+  if (pool_partials) {
+    Geo g = make_geo(S, D, vec, GeoKind::Reduce, MHC_TPC_ADDPOOL);
+    g.tpc = (int32_t)(S < MHC_TPC_ADDPOOL ? S : MHC_TPC_ADDPOOL);
+    g.nchunk = (int32_t)((S + MHC_TPC_ADDPOOL - 1) / MHC_TPC_ADDPOOL);
+    g.reverse = (MHC_REV_MASK >> 2) & 1;
+    const int64_t items = B * geo_slots(g);
+    if (int e = check_grid("add_residual_mix_fwd", items)) return e;
+    const size_t smem = g.sub > 1 ? (size_t)2 * vec * geo_block(g) * sizeof(float) : 0;
+    ProfScope ps("k_add_residual_mix_pool_fwd", st);
+    MHC_DISPATCH(dtype, vec, (launch_k(k_add_residual_mix_fwd<T, V, true>, (unsigned)items, geo_block(g), smem, st,
+                                       (const T*)H, H_res, (const T*)branch_output, H_post, (T*)H_new, pool_partials, g)));
+  } else {
+    Geo g = make_geo(S, D, vec, GeoKind::Stream, MHC_TPC_ADDMIX);
+    g.reverse = (MHC_REV_MASK >> 2) & 1;
+    const int64_t items = B * geo_slots(g);
+    if (int e = check_grid("add_residual_mix_fwd", items)) return e;
+    ProfScope ps("k_add_residual_mix_fwd", st);
+    MHC_DISPATCH(dtype, vec, (launch_k(k_add_residual_mix_fwd<T, V, false>, (unsigned)items, geo_block(g), 0, st,
+                                       (const T*)H, H_res, (const T*)branch_output, H_post, (T*)H_new, (float*)nullptr,
+                                       g)));
+  }
+  return check_launch("add_residual_mix_fwd");
 }
 
 extern "C" int64_t mhc_add_residual_pool_chunks(int64_t S, int64_t D) {

@@ -130,12 +130,14 @@ def fused_dynamic_weights_forward(x: torch.Tensor, phi: torch.Tensor, bias: torc
 
 
 def hc_mix_forward(H, H_pre_base, H_post_base, H_res_base, phi, alpha_pre, alpha_post, alpha_res,
-                   sinkhorn_iters: int = 20, eps: float = 1e-6, pooled=None):
+                   sinkhorn_iters: int = 20, eps: float = 1e-6, pooled=None, want_residual: bool = True):
     """Fused forward of the module's dynamic path in ONE library call: sequence mean-pool,
     dynamic weights, stream mix.  Returns
     (branch_input, H_residual, H_post, H_pre, H_res, x, saved); x [B,4D] and saved [B,32]
     are what the fused backward needs.  `pooled` ([B, chunks, 4D] fp32 token sums of H from the
-    previous layer's add_residual_forward(pool=True)) replaces the pooling pass over H."""
+    previous layer's add_residual_forward(pool=True)) replaces the pooling pass over H.  With
+    want_residual=False H_residual is not written (returned as None): the caller adds the residual
+    with add_residual_mix_forward, which recomputes the mix from H."""
     _check(H.dim() == 4 and H.shape[2] == 4, "H must be [batch, seq, 4, dim]")
     B, S, _, D = H.shape
     _check(S > 0 and D > 0, "empty sequence or width")
@@ -151,7 +153,7 @@ def hc_mix_forward(H, H_pre_base, H_post_base, H_res_base, phi, alpha_pre, alpha
     H_res, saved = small[8 * B:24 * B].view(B, 4, 4), small[24 * B:].view(B, 32)
     x = torch.empty(B, 4 * D, device=dev, dtype=torch.float32)
     bi = torch.empty(B, S, D, device=dev, dtype=H.dtype)
-    Hr = torch.empty_like(H)
+    Hr = torch.empty_like(H) if want_residual else None
     buf, nbytes = L.scratch(L.OP_HC_MIX_FWD, B, S, D, H)
     chunks = 0
     if pooled is not None:
@@ -164,3 +166,27 @@ def hc_mix_forward(H, H_pre_base, H_post_base, H_res_base, phi, alpha_pre, alpha
                L.ptr(bi), L.ptr(Hr), L.ptr(pooled), chunks, L.ptr(buf), nbytes, B, S, D, L.dtype_code(H),
                int(sinkhorn_iters), float(eps))
     return bi, Hr, H_post, H_pre, H_res, x, saved
+
+
+def add_residual_mix_forward(H: torch.Tensor, H_res: torch.Tensor, branch_output: torch.Tensor, H_post: torch.Tensor,
+                             pool: bool = False):
+    """H_new = H_res @ H (over the stream axis) + H_post * branch_output in one kernel: the residual
+    mix is recomputed from H instead of being read from a materialised H_residual.  With pool=True
+    returns (H_new, partials) as add_residual_forward does."""
+    _check(H.dim() == 4 and H.shape[2] == 4, "H must be [batch, seq, 4, dim]")
+    B, S, _, D = H.shape
+    _check(tuple(branch_output.shape) == (B, S, D), "branch_output shape mismatch")
+    _check(tuple(H_post.shape) == (B, 4) and tuple(H_res.shape) == (B, 4, 4), "weight shape mismatch")
+    L.require_cuda(H, H_res, branch_output, H_post)
+    H = H.contiguous()
+    branch_output = branch_output.to(H.dtype).contiguous()
+    H_post, H_res = L.f32c(H_post), L.f32c(H_res)
+    H_new = torch.empty_like(H)
+    partials = None
+    if pool:
+        chunks = L.load().mhc_add_residual_pool_chunks(S, D)
+        partials = torch.empty(B, chunks, 4 * D, device=H.device, dtype=torch.float32)
+    with torch.cuda.device(H.device):
+        L.call("mhc_add_residual_mix_fwd", L.stream_of(H), L.ptr(H), L.ptr(H_res), L.ptr(branch_output), L.ptr(H_post),
+               L.ptr(H_new), L.ptr(partials), B, S, D, L.dtype_code(H))
+    return (H_new, partials) if pool else H_new

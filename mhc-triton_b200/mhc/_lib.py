@@ -40,6 +40,7 @@ _PROTOTYPES = {
     "mhc_add_residual_bwd_noalloc": [_P, _P, _P, _P, _P, _L, _L, _L, _I, _P],
     "mhc_hc_mix_fwd": [_P] * 16 + [_L, _P, _L, _L, _L, _L, _I, _I, _F, _P],
     "mhc_add_residual_pool_fwd": [_P, _P, _P, _P, _P, _L, _L, _L, _I, _P],
+    "mhc_add_residual_mix_fwd": [_P, _P, _P, _P, _P, _P, _L, _L, _L, _I, _P],
     "mhc_hc_mix_bwd": [_P] * 23 + [_L, _L, _L, _L, _I, _I, _F, _I, _I, _P],
 }
 

@@ -10,7 +10,7 @@ from typing import Callable, Tuple
 import torch
 import torch.nn as nn
 
-from .ops import (fused_add_residual, fused_dynamic_weights, fused_stream_mix, hyper_connection_mix, pooled_sums_of,
+from .ops import (add_residual_from_state, fused_add_residual, fused_dynamic_weights, fused_stream_mix, hyper_connection_mix, pooled_sums_of,
                   sequence_mean_pool, sinkhorn_knopp)
 
 
@@ -52,6 +52,9 @@ class HyperConnection(nn.Module):
         self.grad_sink = None
         self.grads_ready_hook = None
         self.grad_accumulate = False   # add to grad_sink instead of overwriting it
+        # Fused dynamic path: do not write H_residual in forward(); add_residual() recomputes the residual
+        # mix from H in the same kernel that adds the branch output (8 of 46 bytes per element less).
+        self.materialize_residual = False
 
         n = num_streams
         in_dim = n * dim
@@ -110,10 +113,23 @@ class HyperConnection(nn.Module):
     @torch.compiler.disable
     def forward(self, H: torch.Tensor) -> Tuple[torch.Tensor, Callable[[torch.Tensor], torch.Tensor]]:
         if self.use_fused_weights:
-            branch_input, H_residual, H_post, _, _ = hyper_connection_mix(
+            lazy = not self.materialize_residual
+            branch_input, H_residual, H_post, _, H_res = hyper_connection_mix(
                 H, self.H_pre_base, self.H_post_base, self.H_res_base, self.phi, self.alpha_pre, self.alpha_post,
                 self.alpha_res, self.sinkhorn_iters, self.eps, self.grad_sink, self.grads_ready_hook,
-                self.grad_accumulate, pooled_sums_of(H))
+                self.grad_accumulate, pooled_sums_of(H), lazy)
+            if lazy:
+                version = H._version
+
+                def add_residual(branch_output: torch.Tensor, pool_for_next: bool = False) -> torch.Tensor:
+                    """pool_for_next=True: also accumulate the token sums the NEXT HyperConnection needs
+                    for its mean-pool (pass the returned tensor to it as is)."""
+                    if H._version != version:
+                        raise RuntimeError("H was modified in place between HyperConnection.forward and add_residual "
+                                           "(set layer.materialize_residual = True if that is intended)")
+                    return add_residual_from_state(H_residual, H, H_res, branch_output, H_post, pool_for_next)
+
+                return branch_input, add_residual
         else:
             H_post, H_pre, H_res = self._compute_weights(H)
             branch_input, H_residual = fused_stream_mix(H, H_pre, H_res)

@@ -13,8 +13,8 @@ import torch
 
 from ._backward import (add_residual_backward, fused_dynamic_weights_backward, hc_mix_backward, sinkhorn_backward,
                         stream_mix_backward)
-from ._kernels import (add_residual_forward, fused_dynamic_weights_forward, hc_mix_forward, meanpool_forward,
-                       sinkhorn_forward, stream_mix_forward)
+from ._kernels import (add_residual_forward, add_residual_mix_forward, fused_dynamic_weights_forward, hc_mix_forward,
+                       meanpool_forward, sinkhorn_forward, stream_mix_forward)
 
 
 # The public functions below are opaque to torch.compile (the kernels are reached through ctypes):
@@ -82,6 +82,33 @@ class _FusedAddResidual(torch.autograd.Function):
         return dH_residual, d_bo.to(branch_output.dtype), dH_post.to(H_post.dtype), None
 
 
+class _AddResidualFromState(torch.autograd.Function):
+    """H_new = H_res @ H + H_post * branch_output with the residual mix recomputed from H.
+
+    `stand_in` is the storage-less second output of the fused node run with lazy_residual=True;
+    the gradient with respect to the residual mix (which equals the upstream gradient) is returned
+    for it, and the fused node turns it into the gradients of H and H_res, exactly as it does for
+    a materialised H_residual.  That is why H and H_res receive no gradient from this node."""
+
+    @staticmethod
+    def forward(ctx, stand_in, H, H_res, branch_output, H_post, pool):
+        ctx.save_for_backward(branch_output, H_post)
+        ctx.set_materialize_grads(False)
+        if pool:
+            H_new, partials = add_residual_mix_forward(H, H_res, branch_output, H_post, pool=True)
+            ctx.mark_non_differentiable(partials)
+            return H_new, partials
+        return add_residual_mix_forward(H, H_res, branch_output, H_post)
+
+    @staticmethod
+    def backward(ctx, grad_H_new, _unused=None):
+        if grad_H_new is None:
+            return None, None, None, None, None, None
+        branch_output, H_post = ctx.saved_tensors
+        dH_residual, d_bo, dH_post = add_residual_backward(grad_H_new, branch_output, H_post)
+        return dH_residual, None, None, d_bo.to(branch_output.dtype), dH_post.to(H_post.dtype), None
+
+
 class _FusedDynamicWeights(torch.autograd.Function):
     """Reference: src/mhc/ops.py:72-228.  The scales are read on the device (no .item())."""
 
@@ -141,10 +168,14 @@ class _HyperConnectionMix(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, H, H_pre_base, H_post_base, H_res_base, phi, alpha_pre, alpha_post, alpha_res,
-                sinkhorn_iters, eps, grad_sink, ready_hook, accumulate, pooled):
+                sinkhorn_iters, eps, grad_sink, ready_hook, accumulate, pooled, lazy_residual):
         branch_input, H_residual, H_post, H_pre, H_res, x, saved = hc_mix_forward(
             H, H_pre_base, H_post_base, H_res_base, phi, alpha_pre, alpha_post, alpha_res, sinkhorn_iters, eps,
-            pooled=pooled)
+            pooled=pooled, want_residual=not lazy_residual)
+        if lazy_residual:
+            # A stand-in with H's shape and no storage of its own: it only carries the gradient of the
+            # (never materialised) residual mix back to this node.  Its values are meaningless.
+            H_residual = branch_input.new_empty(1).expand(H.shape)
         ctx.save_for_backward(H, x, phi, H_pre_base, H_post_base, H_res_base, alpha_pre, alpha_post, alpha_res,
                               saved, H_pre, H_res)
         ctx.sinkhorn_iters, ctx.eps, ctx.grad_sink, ctx.ready_hook = sinkhorn_iters, eps, grad_sink, ready_hook
@@ -169,12 +200,12 @@ class _HyperConnectionMix(torch.autograd.Function):
         if ctx.ready_hook is not None:
             ctx.ready_hook(ctx.grad_sink)
         if ctx.grad_sink is not None:  # the parameters' .grad tensors are views of the sink already
-            return (dH,) + (None,) * 13
+            return (dH,) + (None,) * 14
         return (dH, gbias[0:4].reshape(pre_b.shape).to(pre_b.dtype), gbias[4:8].reshape(post_b.shape).to(post_b.dtype),
                 gbias[8:24].reshape(res_b.shape).to(res_b.dtype), gphi.to(phi.dtype),
                 galpha[0:1].reshape_as(alpha_pre).to(alpha_pre.dtype),
                 galpha[1:2].reshape_as(alpha_post).to(alpha_post.dtype),
-                galpha[2:3].reshape_as(alpha_res).to(alpha_res.dtype), None, None, None, None, None, None)
+                galpha[2:3].reshape_as(alpha_res).to(alpha_res.dtype), None, None, None, None, None, None, None)
 
 
 @torch.compiler.disable
@@ -202,6 +233,17 @@ def fused_add_residual(H_residual: torch.Tensor, branch_output: torch.Tensor, H_
     if not pool_for_next:
         return _FusedAddResidual.apply(H_residual, branch_output, H_post, False)
     H_new, partials = _FusedAddResidual.apply(H_residual, branch_output, H_post, True)
+    H_new._mhc_pooled = (partials, H_new._version)
+    return H_new
+
+
+@torch.compiler.disable
+def add_residual_from_state(stand_in, H, H_res, branch_output, H_post, pool_for_next: bool = False) -> torch.Tensor:
+    """Second half of a layer whose fused node ran with lazy_residual=True (see hyper_connection_mix):
+    H_new = H_res @ H + H_post * branch_output, the residual mix recomputed from H."""
+    if not pool_for_next:
+        return _AddResidualFromState.apply(stand_in, H, H_res, branch_output, H_post, False)
+    H_new, partials = _AddResidualFromState.apply(stand_in, H, H_res, branch_output, H_post, True)
     H_new._mhc_pooled = (partials, H_new._version)
     return H_new
 
@@ -237,12 +279,14 @@ def sequence_mean_pool(H: torch.Tensor) -> torch.Tensor:
 @torch.compiler.disable
 def hyper_connection_mix(H, H_pre_base, H_post_base, H_res_base, phi, alpha_pre, alpha_post, alpha_res,
                          sinkhorn_iters: int = 20, eps: float = 1e-6, grad_sink=None, ready_hook=None,
-                         accumulate: bool = False, pooled=None):
+                         accumulate: bool = False, pooled=None, lazy_residual: bool = False):
     """Fused pooled-weights + stream-mix node; returns
     (branch_input, H_residual, H_post, H_pre, H_res); the last two carry no gradient.
     With `grad_sink` the parameter gradients are written into that flat buffer and no
     gradient is returned for the parameters; `ready_hook(grad_sink)` is called as soon as
     the kernels that fill it have been launched; `accumulate` adds to the buffer instead of
-    overwriting it; `pooled` are token sums of H from the previous layer (see fused_add_residual)."""
+    overwriting it; `pooled` are token sums of H from the previous layer (see fused_add_residual).
+    With lazy_residual=True the second output is a storage-less stand-in to be passed to
+    add_residual_from_state, which recomputes the residual mix from H."""
     return _HyperConnectionMix.apply(H, H_pre_base, H_post_base, H_res_base, phi, alpha_pre, alpha_post, alpha_res,
-                                     sinkhorn_iters, eps, grad_sink, ready_hook, accumulate, pooled)
+                                     sinkhorn_iters, eps, grad_sink, ready_hook, accumulate, pooled, lazy_residual)
