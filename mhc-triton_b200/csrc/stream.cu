@@ -284,7 +284,7 @@ k_add_residual_pool_fwd(const T* __restrict__ Hr, const T* __restrict__ bo, cons
 #define MHC_ADDMIX_PIPE 0
 #endif
 #ifndef MHC_ADDMIX_MINB
-#define MHC_ADDMIX_MINB 3
+#define MHC_ADDMIX_MINB 4
 #endif
 template <typename T, int V, bool POOL>
 __global__ void __launch_bounds__(MHC_MAX_COLS, POOL ? 2 : MHC_ADDMIX_MINB)
