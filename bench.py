@@ -66,12 +66,12 @@ MOVED_UNITS = 42
 # summarised under profiles/, keyed by (workload, kernel); None = not captured.
 NCU_TRAFFIC = {
     # batch-2 capture x4 (traffic is proportional to the batch); writes still dirty in L2 at kernel end are not counted
-    ("c4", "k_stream_mix_bwd_apply"): 4 * (335.689472e6 + 212.243712e6),
-    ("c4", "k_stream_mix_fwd"): 4 * (268.464896e6 + 278.717952e6),
-    ("c4", "k_add_residual_fwd"): 4 * (335.556864e6 + 217.698048e6),
-    ("c4", "k_add_residual_bwd"): 4 * (335.558400e6 + 13.125632e6),
-    ("c4", "k_stream_mix_bwd_reduce"): 4 * (604.000000e6 + 3.297792e6),
-    ("c4", "k_meanpool_partial"): 4 * (268.491776e6 + 3.950336e6),
+    ("c4", "k_stream_mix_bwd_apply"): 4 * (335.689216e6 + 212.662016e6),
+    ("c4", "k_add_residual_mix_fwd"): 4 * (335.556096e6 + 212.420864e6),
+    ("c4", "k_stream_mix_bwd_reduce"): 4 * (604.002304e6 + 3.213056e6),
+    ("c4", "k_add_residual_bwd"): 4 * (335.597568e6 + 13.030144e6),
+    ("c4", "k_stream_premix_fwd"): 4 * (268.445952e6 + 13.323520e6),
+    ("c4", "k_meanpool_partial"): 4 * (268.504064e6 + 4.123392e6),
 }
 
 

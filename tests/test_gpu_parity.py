@@ -695,3 +695,33 @@ def test_dynamic_weights_many_rows(B, K):
     ((a2 * dev(gp)).sum() + (b2 * dev(gq)).sum() + (c2 * dev(gr)).sum()).backward()
     for r, l, n in zip(ref, lv, "x phi bias a_pre a_post a_res".split()):
         assert_close_norm(l.grad, r.grad, 1e-4, 1e-6, "d" + n)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_lazy_residual_equals_materialised_residual(dtype):
+    """Default module path (H_residual never written, residual mix recomputed inside add residual)
+    against the two-kernel forward: bit-identical in fp32, one rounding apart in bf16; and the
+    closure refuses to run after an in-place change of H."""
+    import mhc
+    torch.manual_seed(41)
+    B, S, D = 2, 130, 72
+    H = torch.randn(B, S, 4, D).to(dtype)
+    up = torch.randn(B, S, 4, D).to(dtype)
+    p = cases.perturb_params_(O.default_params(D, 0, 0.1), 27)
+    hc = to_module(mhc.HyperConnection(dim=D), p).to(DEV)
+    lazy = {k: v.clone() for k, v in _run_module(hc, H, up, torch.tanh).items()}
+    hc.materialize_residual = True
+    full = _run_module(hc, H, up, torch.tanh)
+    hc.materialize_residual = False
+    for k in lazy:
+        if dtype == torch.float32:
+            assert torch.equal(lazy[k], full[k]), k
+        elif k in ("branch_input",):
+            assert torch.equal(lazy[k], full[k]), k
+        else:
+            assert_close_norm(lazy[k], full[k], 2e-2, 1e-6, k)
+    Hd = dev(H).requires_grad_(False)
+    bi, add = hc(Hd)
+    Hd.add_(1.0)
+    with pytest.raises(RuntimeError, match="modified in place"):
+        add(bi)
