@@ -286,8 +286,14 @@ k_add_residual_pool_fwd(const T* __restrict__ Hr, const T* __restrict__ bo, cons
 #ifndef MHC_ADDMIX_MINB
 #define MHC_ADDMIX_MINB 4
 #endif
+#ifndef MHC_ADDMIXPOOL_PIPE
+#define MHC_ADDMIXPOOL_PIPE 0
+#endif
+#ifndef MHC_ADDMIXPOOL_MINB
+#define MHC_ADDMIXPOOL_MINB 2
+#endif
 template <typename T, int V, bool POOL>
-__global__ void __launch_bounds__(MHC_MAX_COLS, POOL ? 2 : MHC_ADDMIX_MINB)
+__global__ void __launch_bounds__(MHC_MAX_COLS, POOL ? MHC_ADDMIXPOOL_MINB : MHC_ADDMIX_MINB)
 k_add_residual_mix_fwd(const T* __restrict__ H, const float* __restrict__ Hres, const T* __restrict__ bo,
                        const float* __restrict__ Hpost, T* __restrict__ Hn, float* __restrict__ pool, Geo g) {
   extern __shared__ float sm[];  // POOL: [2*V][sub][cols]
@@ -310,7 +316,7 @@ k_add_residual_mix_fwd(const T* __restrict__ H, const float* __restrict__ Hres, 
 #pragma unroll
     for (int k = 0; k < 16; ++k) R[k] = __ldg(Hres + it.b * 16 + k);
     using B5 = Bundle<T, V, 5>;
-    for_tokens<(!POOL && MHC_ADDMIX_PIPE != 0), B5>(
+    for_tokens<(POOL ? MHC_ADDMIXPOOL_PIPE != 0 : MHC_ADDMIX_PIPE != 0), B5>(
         it.s0 + it.sub, it.s1, g.sub,
         [&](B5& u, int64_t s) {
           const T* h = H + (tok + s) * 4 * D + c0;

@@ -10,7 +10,7 @@ from typing import Callable, Tuple
 import torch
 import torch.nn as nn
 
-from .ops import (add_residual_from_state, fused_add_residual, fused_dynamic_weights, fused_stream_mix, hyper_connection_mix, pooled_sums_of,
+from .ops import (add_residual_from_state, fused_add_residual, version_of, fused_dynamic_weights, fused_stream_mix, hyper_connection_mix, pooled_sums_of,
                   sequence_mean_pool, sinkhorn_knopp)
 
 
@@ -119,12 +119,12 @@ class HyperConnection(nn.Module):
                 self.alpha_res, self.sinkhorn_iters, self.eps, self.grad_sink, self.grads_ready_hook,
                 self.grad_accumulate, pooled_sums_of(H), lazy)
             if lazy:
-                version = H._version
+                version = version_of(H)
 
                 def add_residual(branch_output: torch.Tensor, pool_for_next: bool = False) -> torch.Tensor:
                     """pool_for_next=True: also accumulate the token sums the NEXT HyperConnection needs
                     for its mean-pool (pass the returned tensor to it as is)."""
-                    if H._version != version:
+                    if version_of(H) != version:
                         raise RuntimeError("H was modified in place between HyperConnection.forward and add_residual "
                                            "(set layer.materialize_residual = True if that is intended)")
                     return add_residual_from_state(H_residual, H, H_res, branch_output, H_post, pool_for_next)

@@ -233,7 +233,7 @@ def fused_add_residual(H_residual: torch.Tensor, branch_output: torch.Tensor, H_
     if not pool_for_next:
         return _FusedAddResidual.apply(H_residual, branch_output, H_post, False)
     H_new, partials = _FusedAddResidual.apply(H_residual, branch_output, H_post, True)
-    H_new._mhc_pooled = (partials, H_new._version)
+    H_new._mhc_pooled = (partials, version_of(H_new))
     return H_new
 
 
@@ -244,8 +244,13 @@ def add_residual_from_state(stand_in, H, H_res, branch_output, H_post, pool_for_
     if not pool_for_next:
         return _AddResidualFromState.apply(stand_in, H, H_res, branch_output, H_post, False)
     H_new, partials = _AddResidualFromState.apply(stand_in, H, H_res, branch_output, H_post, True)
-    H_new._mhc_pooled = (partials, H_new._version)
+    H_new._mhc_pooled = (partials, version_of(H_new))
     return H_new
+
+
+def version_of(t: torch.Tensor):
+    """In-place modification counter of t, or None for inference tensors (which keep none)."""
+    return None if t.is_inference() else t._version
 
 
 def pooled_sums_of(H: torch.Tensor):
@@ -255,7 +260,7 @@ def pooled_sums_of(H: torch.Tensor):
     if tag is None:
         return None
     partials, version = tag
-    if H._version != version or H.dim() != 4 or partials.shape[0] != H.shape[0] or \
+    if version_of(H) != version or H.dim() != 4 or partials.shape[0] != H.shape[0] or \
             partials.shape[2] != 4 * H.shape[3] or partials.device != H.device:
         return None
     return partials

@@ -725,3 +725,22 @@ def test_lazy_residual_equals_materialised_residual(dtype):
     Hd.add_(1.0)
     with pytest.raises(RuntimeError, match="modified in place"):
         add(bi)
+
+
+def test_inference_mode_and_no_grad():
+    """Forward under torch.inference_mode() / no_grad (tensors without version counters or graphs)."""
+    import mhc
+    torch.manual_seed(2)
+    B, S, D = 2, 50, 64
+    H = torch.randn(B, S, 4, D)
+    p = cases.perturb_params_(O.default_params(D, 0, 0.1), 6)
+    hc = to_module(mhc.HyperConnection(dim=D), p).to(DEV)
+    ref_bi, ref_new = O.layer_forward(p.to(torch.float64), H.double(), torch.tanh)
+    with torch.inference_mode():
+        bi, add = hc(dev(H))
+        H1 = add(torch.tanh(bi), pool_for_next=True)
+        bi2, add2 = hc(H1)                      # consumes the attached sums
+        assert_close(bi, ref_bi, RT, 2 * AT); assert_close(H1, ref_new, RT, 4 * AT)
+    with torch.no_grad():
+        bi, add = hc(dev(H))
+        assert_close(add(torch.tanh(bi)), ref_new, RT, 4 * AT)
