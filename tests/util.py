@@ -1,7 +1,5 @@
 """Comparison helpers for the parity tests."""
 
-import torch
-
 
 def maxdiff(a, b):
     return float((a.detach().double().cpu() - b.detach().double().cpu()).abs().max()) if a.numel() else 0.0
