@@ -104,6 +104,8 @@ int mhc_sinkhorn_bwd(const void* M, const void* dP, void* dM, int64_t batch, int
 /* ---- Stream mix -----------------------------------------------------------------
  * branch_input[b,s,d] = sum_n H_pre[b,n] H[b,s,n,d];
  * H_residual[b,s,n,d] = sum_m H_res[b,n,m] H[b,s,m,d].
+ * H_residual may be NULL (H_res is then unused): only branch_input is written, for callers that
+ * add the residual with mhc_add_residual_mix_fwd.
  * Replaces stream_mix_forward, src/mhc/_kernels.py:617-652 (kernel :137-236). */
 int mhc_stream_mix_fwd(const void* H, const float* H_pre, const float* H_res, void* branch_input,
                        void* H_residual, int64_t B, int64_t S, int64_t D, int dtype,

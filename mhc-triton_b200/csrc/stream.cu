@@ -843,7 +843,7 @@ extern "C" int mhc_stream_mix_fwd(const void* H, const float* H_pre, const float
                                   mhc_stream_t stream) {
   if (int e = check_bsd("stream_mix_fwd", B, S, D, dtype)) return e;
   if (B == 0 || S == 0 || D == 0) return MHC_OK;
-  if (!H || !H_pre || !H_res || !branch_input || !H_residual) return fail(MHC_ERR_NULL_POINTER, "stream_mix_fwd: null pointer");
+  if (!H || !H_pre || !branch_input || (H_residual && !H_res)) return fail(MHC_ERR_NULL_POINTER, "stream_mix_fwd: null pointer");
   return stream_mix_fwd_impl(H, H_pre, H_res, branch_input, H_residual, B, S, D, dtype, (cudaStream_t)stream);
 }
 

@@ -30,8 +30,9 @@ def sinkhorn_forward(M: torch.Tensor, num_iters: int = 20, eps: float = 1e-8) ->
 
 
 def stream_mix_forward(H: torch.Tensor, H_pre: torch.Tensor, H_res: torch.Tensor,
-                       block_dim: int = 128) -> Tuple[torch.Tensor, torch.Tensor]:
-    """(branch_input [B,S,D], H_residual [B,S,4,D]) in H's dtype."""
+                       block_dim: int = 128, want_residual: bool = True) -> Tuple[torch.Tensor, torch.Tensor]:
+    """(branch_input [B,S,D], H_residual [B,S,4,D]) in H's dtype; with want_residual=False the
+    residual mix is not written and None is returned in its place."""
     _check(H.dim() == 4, "H must be [batch, seq, 4, dim]")
     B, S, n, D = H.shape
     _check(n == 4, "num_streams must be 4")
@@ -41,7 +42,7 @@ def stream_mix_forward(H: torch.Tensor, H_pre: torch.Tensor, H_res: torch.Tensor
     H = H.contiguous()
     H_pre, H_res = L.f32c(H_pre), L.f32c(H_res)
     bi = torch.empty(B, S, D, device=H.device, dtype=H.dtype)
-    Hr = torch.empty_like(H)
+    Hr = torch.empty_like(H) if want_residual else None
     with torch.cuda.device(H.device):
         L.call("mhc_stream_mix_fwd", L.stream_of(H), L.ptr(H), L.ptr(H_pre), L.ptr(H_res), L.ptr(bi), L.ptr(Hr), B, S, D,
                                             L.dtype_code(H))

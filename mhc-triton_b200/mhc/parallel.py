@@ -147,7 +147,9 @@ class _SequenceShardedMix(torch.autograd.Function):
         bias = torch.cat([H_pre_base.reshape(-1), H_post_base.reshape(-1), H_res_base.reshape(-1)]).float()
         H_pre, H_post, H_res, saved = fused_dynamic_weights_forward(
             x, phi, bias, alpha_pre, alpha_post, alpha_res, sinkhorn_iters, eps, return_saved=True)
-        branch_input, H_residual = stream_mix_forward(H, H_pre, H_res)
+        # the residual mix is not written: the closure recomputes it from H (see ops.add_residual_from_state)
+        branch_input, _ = stream_mix_forward(H, H_pre, H_res, want_residual=False)
+        H_residual = branch_input.new_empty(1).expand(H.shape)   # storage-less carrier of the residual's gradient
         ctx.save_for_backward(H, x, phi, bias, alpha_pre, alpha_post, alpha_res, saved, H_pre, H_res)
         ctx.meta = (sinkhorn_iters, eps, group, total_len, H_pre_base.shape, H_post_base.shape, H_res_base.shape)
         ctx.mark_non_differentiable(H_pre, H_res)
@@ -202,14 +204,14 @@ class SequenceShardedHyperConnection(torch.nn.Module):
         self.layer, self.group, self.total_len = layer, process_group, total_len
 
     def forward(self, H: torch.Tensor):
-        from .ops import fused_add_residual
+        from .ops import add_residual_from_state
         l = self.layer
         total = self.total_len if self.total_len is not None else H.shape[1] * _group_size(self.group)
-        branch_input, H_residual, H_post, _, _ = _SequenceShardedMix.apply(
+        branch_input, stand_in, H_post, _, H_res = _SequenceShardedMix.apply(
             H, l.H_pre_base, l.H_post_base, l.H_res_base, l.phi, l.alpha_pre, l.alpha_post, l.alpha_res,
             l.sinkhorn_iters, l.eps, self.group, total)
 
         def add_residual(branch_output: torch.Tensor) -> torch.Tensor:
-            return fused_add_residual(H_residual, branch_output, H_post)
+            return add_residual_from_state(stand_in, H, H_res, branch_output, H_post)
 
         return branch_input, add_residual
