@@ -1,5 +1,8 @@
 """Two GPU ranks over NCCL: batch-sharded HyperConnection with the in-backward gradient all-reduce
-against the unsharded CPU oracle.  Skipped on boxes with fewer than two GPUs."""
+against the unsharded CPU oracle, the sequence-sharded wrapper, and the layer under FSDP2
+(`fully_shard`) against the same block run unsharded.  Skipped on boxes with fewer than two GPUs."""
+
+import copy
 
 import os
 import socket
@@ -98,6 +101,62 @@ def _seq_worker(rank, world, port, q):
         dist.destroy_process_group()
 
 
+class _Block(torch.nn.Module):
+    """A residual block around the layer: H_new = add_residual(tanh(Linear(branch_input)))."""
+
+    def __init__(self, hc, D):
+        super().__init__()
+        self.hc = hc
+        self.branch = torch.nn.Linear(D, D)
+
+    def forward(self, H):
+        branch_input, add_residual = self.hc(H)
+        return add_residual(torch.tanh(self.branch(branch_input)))
+
+
+def _fsdp_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        import mhc
+        from mhc.parallel import shard_batch
+        from torch.distributed.fsdp import fully_shard
+        torch.manual_seed(2)
+        B, S, D = 4, 160, 128
+        H = torch.randn(B, S, 4, D)
+        g = torch.randn(B, S, 4, D)
+        p = cases.perturb_params_(O.default_params(D, 0, 0.1), 5)
+        ref = _Block(to_module(mhc.HyperConnection(dim=D), p), D).to(dev)   # same seed: same Linear on every rank
+        blk = copy.deepcopy(ref)
+        fully_shard(blk.hc)            # the layer's parameters are sharded, gathered for forward and backward,
+        fully_shard(blk)               # and freed in between (the layer is not the root)
+        Hf = H.to(dev).requires_grad_(True)
+        out_f = ref(Hf)
+        out_f.backward(g.to(dev))
+        Hs = shard_batch(H, rank, world).to(dev).requires_grad_(True)
+        lo = sum(shard_batch(H, r, world).shape[0] for r in range(rank))
+        n = Hs.shape[0]
+        for _ in range(2):
+            Hs.grad = None
+            blk.zero_grad(set_to_none=True)
+            out = blk(Hs)
+            out.backward(shard_batch(g, rank, world).to(dev))
+        torch.cuda.synchronize()
+        for k, a, b in (("H_new", out, out_f[lo:lo + n]), ("dH", Hs.grad, Hf.grad[lo:lo + n])):
+            assert (a - b).abs().max() <= 1e-5 * (1 + b.abs().max()), k
+        for (name, prm), (_, rp) in zip(blk.named_parameters(), ref.named_parameters()):
+            got = prm.grad.full_tensor() * world          # FSDP averages over ranks; the unsharded run sums
+            assert got.shape == rp.grad.shape, name
+            assert (got - rp.grad).abs().max() <= 1e-5 * (1 + rp.grad.abs().max()), name
+        q.put((rank, "ok"))
+    except Exception as e:
+        q.put((rank, f"{type(e).__name__}: {e}"))
+    finally:
+        dist.destroy_process_group()
+
+
 def _spawn2(worker):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
@@ -111,6 +170,10 @@ def _spawn2(worker):
     for pr in procs:
         pr.join(timeout=60)
     assert sorted(results) == [(0, "ok"), (1, "ok")], results
+
+
+def test_two_gpu_fsdp2_block_matches_unsharded():
+    _spawn2(_fsdp_worker)
 
 
 def test_two_gpu_sequence_sharded_layer_matches_oracle():
