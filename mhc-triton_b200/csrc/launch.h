@@ -93,6 +93,7 @@ int weights_bwd_impl(const float* x, const float* phi, BiasPtrs bias, const floa
 // Many-rows variants (weights_rows.cu), used from kManyRows rows on.
 constexpr int64_t kManyRows = 64;
 int phi_row_tiles(int64_t batch);
+int64_t rows_bwd_extra_floats(int64_t batch, int64_t K);
 int project_rows_launch(const float* x, const float* phi, float* part, int64_t batch, int64_t K, int ks_max,
                         cudaStream_t st, int* ks_used);
 int bwd_rows_launch(const float* x, const float* phi, const float* buf, float* phi_part, float* grad_x, float* grad_phi,

@@ -24,7 +24,7 @@ int64_t weights_fwd_scratch_bytes(int64_t batch, int64_t K) {
 }
 int64_t weights_bwd_scratch_bytes(int64_t batch, int64_t K) {
   int64_t n = batch * kBwdStride;                                   // per-row records
-  if (batch >= kManyRows) n += (int64_t)phi_row_tiles(batch) * K * 24;  // grad_phi partial sums per row tile
+  if (batch >= kManyRows) n += rows_bwd_extra_floats(batch, K);       // grad_phi partial sums, column sums
   return n * (int64_t)sizeof(float);
 }
 

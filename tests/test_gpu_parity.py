@@ -661,8 +661,7 @@ def test_layer_inside_a_compiled_model():
 def test_per_token_weights_through_reshape():
     """The paper's per-token formulation (weights from every token's own 4*D state, not from the
     sequence mean) is the same layer applied to H viewed as [B*S, 1, 4, D]: every entry point
-    takes any number of rows, so it runs correctly today (slowly: the projection is not tiled
-    over rows yet)."""
+    takes any number of rows, and from 64 rows on the dynamic-weights kernels tile over rows."""
     import mhc
     torch.manual_seed(31)
     B, S, D = 2, 37, 48
@@ -676,9 +675,12 @@ def test_per_token_weights_through_reshape():
         assert_close_norm(v, ref[k], 1e-4 if k.startswith("d") else RT, 4 * AT, k)
 
 
-@pytest.mark.parametrize("B,K", [(64, 4 * 64), (200, 4 * 100 + 4), (1000, 4 * 256)])
+@pytest.mark.parametrize("B,K", [(64, 4 * 64), (200, 4 * 100 + 4), (1000, 4 * 256), (130, 4 * 33 + 2), (300, 4 * 1100),
+                                 (2500, 4 * 128)])
 def test_dynamic_weights_many_rows(B, K):
-    """From 64 rows on the op switches to kernels tiled over rows (per-token use); same results."""
+    """From 64 rows on the op switches to kernels tiled over rows (per-token use); same results.
+    Covers the register-tiled projection (K % 4 == 0) with one and with several K slices, the scalar
+    projection (K % 4 != 0), ragged last row blocks, and several row tiles in the backward."""
     from mhc import fused_dynamic_weights
     torch.manual_seed(B + K)
     x = torch.randn(B, K)
