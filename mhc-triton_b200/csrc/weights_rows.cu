@@ -1,12 +1,13 @@
 // Dynamic weights for MANY rows (per-token use: x [B*S, 4D]).  The few-rows kernels in weights.cu
 // give every row its own CTAs, which re-reads phi once per row; from kManyRows rows on, these
 // kernels tile over rows instead so that phi (forward) and x (backward) are read once per tile:
-//   forward : one thread per row, 128 rows per CTA, x and phi staged through shared memory in
-//             32-wide K tiles; same [row, slice, 25] partial layout, so k_dw_finish is shared;
-//             (the register-tiled kernel below replaces it when K % 4 == 0 and the pointers are aligned);
-//   backward: one pass over x per (256 k) x (row tile) block gives grad_x and the grad_phi partial sums
-//             of the tile (fp32 inside a tile, tiles added in index order in fp64); bias / alpha column
-//             sums by up to 64 CTAs and one joining warp, in a fixed order.
+//   forward : 128 rows x one K slice per CTA, x and phi staged through shared memory; same
+//             [row, slice, 25] partial layout as the few-rows kernel, so k_dw_finish is shared;
+//   backward: one pass over x per (k block) x (row tile) gives grad_x and the grad_phi partial sums of
+//             the tile (tiles added in index order in fp64); bias / alpha column sums by up to 64 CTAs
+//             and one joining warp, in a fixed order.
+// Both directions run on the tensor cores (mma.sync TF32 with the 3xTF32 split) when K % 4 == 0 and the
+// pointers are 16-byte aligned, and as plain fp32 FMA kernels otherwise.
 #include "common.cuh"
 #include "launch.h"
 
@@ -74,17 +75,7 @@ k_dw_project_rows(const float* __restrict__ x, const float* __restrict__ phi, fl
 }
 
 // ---------------------------------------------------------------------------------------
-// Register-tiled projection for K % 4 == 0 and 16-byte aligned x / phi.
-// CTA = 128 rows x one K slice, 128 threads; thread (rg, cg) owns rows rg, rg+32, rg+64, rg+96 and
-// columns 6cg .. 6cg+5, i.e. 24 accumulators fed by 4 + 6 shared-memory float4 loads per 4 k:
-// 96 FMAs per 10 loads, so the FMA pipe is the limit, not shared memory.  Tiles of 32 k are
-// double-buffered with cp.async (x as 16-byte copies, phi transposed to [col][k] by 4-byte copies);
-// rows past the batch and k past the slice are zero-filled by the copy.  The row stride of 36
-// floats keeps float4 alignment and makes both load patterns bank-conflict free.
-// sum(x^2) is taken by the thread that copied the values (8 float4 per tile, fixed rows), then
-// added across the 8 lanes that share a row.
-constexpr int kPR = 128, kPK = 32, kPS = kPK + 4;
-
+// cp.async helpers: a copy with valid = false writes zeros and reads nothing.
 __device__ __forceinline__ void cp_async16(void* dst_smem, const void* src, bool valid) {
   const unsigned d = (unsigned)__cvta_generic_to_shared(dst_smem);
   const int n = valid ? 16 : 0;
@@ -99,25 +90,65 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-__global__ void __launch_bounds__(kPR)
-k_dw_project_rows_v4(const float* __restrict__ x, const float* __restrict__ phi, float* __restrict__ part,
-                     int64_t batch, int64_t K, int ks) {
-  __shared__ __align__(16) float xs[2][kPR][kPS];
-  __shared__ __align__(16) float ps[2][24][kPS];
+// ---------------------------------------------------------------------------------------
+// Tensor-core projection (K % 4 == 0, 16-byte aligned x / phi): mma.sync m16n8k8 TF32 with the
+// 3xTF32 split (x = hi + lo, both TF32; hi*hi + hi*lo + lo*hi, fp32 accumulate), which keeps fp32-level
+// accuracy.  CTA = 128 rows x one K slice, 4 warps; warp w owns rows 32w .. 32w+31 (two 16-row MMA
+// tiles) and all 24 columns (three 8-column tiles).  Tiles of 32 k are double-buffered with 16-byte
+// cp.async: x as [row][k] with a stride of 36 floats, phi as [k][col] with a stride of 40 floats, which
+// makes the A-fragment loads (bank 4g + t) and the B-fragment loads (bank 8t + g) conflict free.
+// sum(x^2) as in the FMA kernel: by the copying thread, then across the 8 lanes that share a row.
+constexpr int kMR = 128, kMK = 32, kMXS = 36, kMPS = 40;
+
+__device__ __forceinline__ void split_tf32(float v, uint32_t& hi, uint32_t& lo) {
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(v));
+  const float rest = v - __uint_as_float(hi);
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lo) : "f"(rest));
+}
+__device__ __forceinline__ void mma_tf32(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+// d = a * b (no accumulator input).
+__device__ __forceinline__ void mma_tf32_first(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+               : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]), "f"(0.f));
+}
+// c += a * b with the 3xTF32 terms (small ones first).  The tensor core adds into its accumulator with
+// truncation, which over hundreds of steps grows into a bias of several fp32 ulps; so the three products
+// of one 8-deep step are summed inside the tensor core starting from zero, and the running sum is kept
+// with an ordinary round-to-nearest fp32 add.
+__device__ __forceinline__ void mma_3xtf32_add(float (&c)[4], const uint32_t (&ah)[4], const uint32_t (&al)[4],
+                                               const uint32_t (&bh)[2], const uint32_t (&bl)[2]) {
+  float d[4];
+  mma_tf32_first(d, al, bh);
+  mma_tf32(d, ah, bl);
+  mma_tf32(d, ah, bh);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) c[i] += d[i];
+}
+
+__global__ void __launch_bounds__(128, 4)
+k_dw_project_rows_mma(const float* __restrict__ x, const float* __restrict__ phi, float* __restrict__ part,
+                      int64_t batch, int64_t K, int ks) {
+  __shared__ __align__(16) float xs[2][kMR][kMXS];
+  __shared__ __align__(16) float ps[2][kMK][kMPS];
   pdl_prologue();
   const int tid = threadIdx.x;
-  const int cg = tid & 3, rg = tid >> 2;
-  const int64_t row0 = (int64_t)(blockIdx.x / ks) * kPR;
+  const int w = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const int64_t row0 = (int64_t)(blockIdx.x / ks) * kMR;
   const int slice = (int)(blockIdx.x % ks);
   int64_t per = (K + ks - 1) / ks;
-  per = (per + kPK - 1) / kPK * kPK;
+  per = (per + kMK - 1) / kMK * kMK;
   const int64_t k0 = slice * per, k1 = min(k0 + per, K);
-  const int ntile = k1 > k0 ? (int)((k1 - k0 + kPK - 1) / kPK) : 0;
+  const int ntile = k1 > k0 ? (int)((k1 - k0 + kMK - 1) / kMK) : 0;
 
-  // copy assignments: 8 float4 of x (rows lr + 16 i, k offset 4 lq) and up to 2 float4-worth of phi
-  const int lr = tid >> 3, lq = tid & 7;
-  auto issue = [&](int t, int b) {
-    const int64_t kt = k0 + (int64_t)t * kPK;
+  const int lr = tid >> 3, lq = tid & 7;       // x copies: rows lr + 16 i, k offset 4 lq
+  auto issue = [&](int tt, int b) {
+    const int64_t kt = k0 + (int64_t)tt * kMK;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const int r = lr + 16 * i;
@@ -126,28 +157,32 @@ k_dw_project_rows_v4(const float* __restrict__ x, const float* __restrict__ phi,
       cp_async16(&xs[b][r][4 * lq], x + (ok ? row * K + k : 0), ok);
     }
 #pragma unroll
-    for (int i = 0; i < 6; ++i) {
-      const int f = i * kPR + tid;            // 0 .. 767 : element of the [32 k][24] tile
-      const int kk = f / 24, j = f % 24;
-      const bool ok = kt + kk < k1;
-      cp_async4(&ps[b][j][kk], phi + (ok ? (kt + kk) * 24 + j : 0), ok);
+    for (int i = 0; i < 2; ++i) {
+      const int f = i * 128 + tid;              // 0 .. 191 : float4 of the [32 k][24] tile
+      if (f < kMK * 6) {
+        const int kk = f / 6, q = f % 6;
+        const bool ok = kt + kk < k1;
+        cp_async16(&ps[b][kk][4 * q], phi + (ok ? (kt + kk) * 24 + 4 * q : 0), ok);
+      }
     }
     cp_async_commit();
   };
 
-  float acc[4][6];
+  float acc[2][3][4];
 #pragma unroll
-  for (int i = 0; i < 4; ++i)
+  for (int m = 0; m < 2; ++m)
 #pragma unroll
-    for (int c = 0; c < 6; ++c) acc[i][c] = 0.f;
+    for (int n = 0; n < 3; ++n)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[m][n][i] = 0.f;
   float sq[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) sq[i] = 0.f;
 
   if (ntile > 0) issue(0, 0);
-  for (int t = 0; t < ntile; ++t) {
-    const int b = t & 1;
-    if (t + 1 < ntile) { issue(t + 1, b ^ 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
+  for (int tt = 0; tt < ntile; ++tt) {
+    const int b = tt & 1;
+    if (tt + 1 < ntile) { issue(tt + 1, b ^ 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
 #pragma unroll
     for (int i = 0; i < 8; ++i) {   // this thread's own copies are visible to it after the wait
       const float4 v = *reinterpret_cast<const float4*>(&xs[b][lr + 16 * i][4 * lq]);
@@ -156,34 +191,38 @@ k_dw_project_rows_v4(const float* __restrict__ x, const float* __restrict__ phi,
     }
     __syncthreads();
 #pragma unroll
-    for (int k4 = 0; k4 < kPK / 4; ++k4) {
-      float4 xv[4];
+    for (int k8 = 0; k8 < kMK / 8; ++k8) {
+      uint32_t bh[3][2], bl[3][2];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) xv[i] = *reinterpret_cast<const float4*>(&xs[b][rg + 32 * i][4 * k4]);
+      for (int n = 0; n < 3; ++n)
 #pragma unroll
-      for (int c = 0; c < 6; ++c) {
-        const float4 pv = *reinterpret_cast<const float4*>(&ps[b][6 * cg + c][4 * k4]);
+        for (int h = 0; h < 2; ++h) split_tf32(ps[b][8 * k8 + t + 4 * h][8 * n + g], bh[n][h], bl[n][h]);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          float a = acc[i][c];
-          a = fmaf(xv[i].x, pv.x, a); a = fmaf(xv[i].y, pv.y, a);
-          a = fmaf(xv[i].z, pv.z, a); a = fmaf(xv[i].w, pv.w, a);
-          acc[i][c] = a;
-        }
+      for (int m = 0; m < 2; ++m) {
+        const int r = 32 * w + 16 * m + g;
+        uint32_t ah[4], al[4];
+        split_tf32(xs[b][r][8 * k8 + t], ah[0], al[0]);
+        split_tf32(xs[b][r + 8][8 * k8 + t], ah[1], al[1]);
+        split_tf32(xs[b][r][8 * k8 + t + 4], ah[2], al[2]);
+        split_tf32(xs[b][r + 8][8 * k8 + t + 4], ah[3], al[3]);
+#pragma unroll
+        for (int n = 0; n < 3; ++n) mma_3xtf32_add(acc[m][n], ah, al, bh[n], bl[n]);
       }
     }
     __syncthreads();   // the other buffer is refilled at the top of the next iteration
   }
 
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int64_t row = row0 + rg + 32 * i;
-    if (row < batch) {
-      float* o = part + (row * ks + slice) * 25 + 6 * cg;
+  for (int m = 0; m < 2; ++m)
 #pragma unroll
-      for (int c = 0; c < 6; ++c) o[c] = acc[i][c];
+    for (int h = 0; h < 2; ++h) {
+      const int64_t row = row0 + 32 * w + 16 * m + g + 8 * h;
+      if (row < batch) {
+        float* o = part + (row * ks + slice) * 25 + 2 * t;
+#pragma unroll
+        for (int n = 0; n < 3; ++n) { o[8 * n] = acc[m][n][2 * h]; o[8 * n + 1] = acc[m][n][2 * h + 1]; }
+      }
     }
-  }
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     float v = sq[i];
@@ -199,65 +238,242 @@ k_dw_project_rows_v4(const float* __restrict__ x, const float* __restrict__ phi,
 //   grad_x[row,k]       = coef[row] x[row,k] + sum_j d_raw[row,j] phi[k,j]
 //   phi_part[tile,k,j]  = sum over the tile's rows of x[row,k] d_raw[row,j]   (rows in index order, fp32)
 // One thread per k keeps phi[k,:] and the 24 partial sums in registers; the per-row records
-// (d_raw[24], coef) are staged 64 rows at a time through shared memory and read as broadcast float4s;
-// x is read once, four rows ahead of the arithmetic.
-constexpr int kBwdStage = 64;
+// (d_raw[24], coef) are staged 64 rows at a time through shared memory and read as broadcast float4s.
+// x is read once: every thread copies its own column 32 rows ahead of the arithmetic into a
+// shared-memory ring with 4-byte cp.async (8 groups of 4 rows in flight), which keeps enough bytes in
+// flight to cover the memory latency without spending registers; a thread only ever reads what it
+// copied itself, so the ring needs no barrier.
+constexpr int kBwdStage = 64, kXG = 8;
 
 __global__ void __launch_bounds__(256, 2)
 k_dw_bwd_x_rows(const float* __restrict__ x, const float* __restrict__ phi, const float* __restrict__ buf,
                 float* __restrict__ grad_x, float* __restrict__ phi_part, int64_t batch, int64_t K,
                 int64_t rows_per_tile) {
   __shared__ __align__(16) float s_d[kBwdStage][28];   // d_raw[24], coef, 3 unused
+  __shared__ float xs[kXG][4][256];
   pdl_prologue();
-  const int64_t k = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int tid = threadIdx.x;
+  const int64_t k = (int64_t)blockIdx.x * blockDim.x + tid;
   const bool active = k < K;
   const int64_t kc = active ? k : K - 1;
   const int64_t t0 = (int64_t)blockIdx.y * rows_per_tile, t1 = min(t0 + rows_per_tile, batch);
+  const int64_t ng = t1 > t0 ? (t1 - t0 + 3) / 4 : 0;
+  auto issue = [&](int64_t g) {     // group g = rows t0 + 4g .. t0 + 4g + 3, zero-filled past the tile
+    const int slot = (int)(g % kXG);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int64_t row = t0 + 4 * g + u;
+      const bool ok = active && row < t1;
+      cp_async4(&xs[slot][u][tid], x + (ok ? row * K + k : 0), ok);
+    }
+    cp_async_commit();
+  };
   float p[24], acc[24];
 #pragma unroll
   for (int j = 0; j < 24; ++j) { p[j] = __ldg(phi + kc * 24 + j); acc[j] = 0.f; }
-  for (int64_t r0 = t0; r0 < t1; r0 += kBwdStage) {
-    const int nr = (int)min((int64_t)kBwdStage, t1 - r0);
-    __syncthreads();
-    for (int i = threadIdx.x; i < kBwdStage * 25; i += blockDim.x) {
-      const int rr = i / 25, jj = i % 25;
-      s_d[rr][jj] = rr < nr ? __ldg(buf + (r0 + rr) * kBwdStrideRows + 24 + jj) : 0.f;
-    }
-    __syncthreads();
-    const float* xp = x + r0 * K + kc;
-    float xn[4];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) xn[u] = u < nr ? __ldg(xp + (int64_t)u * K) : 0.f;
-    for (int rr = 0; rr < nr; rr += 4) {
-      float xv[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) xv[u] = xn[u];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) xn[u] = rr + 4 + u < nr ? __ldg(xp + (int64_t)(rr + 4 + u) * K) : 0.f;
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const float4* dq = reinterpret_cast<const float4*>(&s_d[rr + u][0]);
-        float d[24];
-#pragma unroll
-        for (int q = 0; q < 6; ++q) {
-          const float4 v = dq[q];
-          d[4 * q] = v.x; d[4 * q + 1] = v.y; d[4 * q + 2] = v.z; d[4 * q + 3] = v.w;
-        }
-        float gx = s_d[rr + u][24] * xv[u];
-#pragma unroll
-        for (int j = 0; j < 24; ++j) {
-          gx = fmaf(d[j], p[j], gx);
-          acc[j] = fmaf(xv[u], d[j], acc[j]);     // rows past the tile have d = 0 and x = 0
-        }
-        if (active && rr + u < nr) grad_x[(r0 + rr + u) * K + k] = gx;
+  for (int g = 0; g < kXG; ++g) issue(g);
+  for (int64_t g = 0; g < ng; ++g) {
+    const int sg = (int)(g % (kBwdStage / 4));
+    if (sg == 0) {
+      const int64_t r0 = t0 + 4 * g;
+      const int nr = (int)min((int64_t)kBwdStage, t1 - r0);
+      __syncthreads();
+      for (int i = tid; i < kBwdStage * 25; i += blockDim.x) {
+        const int rr = i / 25, jj = i % 25;
+        s_d[rr][jj] = rr < nr ? __ldg(buf + (r0 + rr) * kBwdStrideRows + 24 + jj) : 0.f;
       }
+      __syncthreads();
     }
+    cp_async_wait<kXG - 1>();       // group g has landed; the 7 younger groups may still be in flight
+    const int slot = (int)(g % kXG);
+    float xv[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) xv[u] = xs[slot][u][tid];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int rr = 4 * sg + u;
+      const float4* dq = reinterpret_cast<const float4*>(&s_d[rr][0]);
+      float d[24];
+#pragma unroll
+      for (int q = 0; q < 6; ++q) {
+        const float4 v = dq[q];
+        d[4 * q] = v.x; d[4 * q + 1] = v.y; d[4 * q + 2] = v.z; d[4 * q + 3] = v.w;
+      }
+      float gx = s_d[rr][24] * xv[u];
+#pragma unroll
+      for (int j = 0; j < 24; ++j) {
+        gx = fmaf(d[j], p[j], gx);
+        acc[j] = fmaf(xv[u], d[j], acc[j]);     // rows past the tile have d = 0 and x = 0
+      }
+      const int64_t row = t0 + 4 * g + u;
+      if (active && row < t1) grad_x[row * K + k] = gx;
+    }
+    issue(g + kXG);                 // refill the slot just consumed
   }
+  cp_async_wait<0>();
   if (active) {
     float* o = phi_part + ((int64_t)blockIdx.y * K + k) * 24;
 #pragma unroll
     for (int j = 0; j < 24; ++j) o[j] = acc[j];
   }
+}
+
+// ---------------------------------------------------------------------------------------
+// Tensor-core backward over x (K % 4 == 0, 16-byte aligned x): the two products of the one-pass
+// backward as mma.sync m16n8k8 TF32 with the 3xTF32 split.  CTA = 64 k columns x one row tile, 4 warps;
+// warp w owns k columns 16w .. 16w+15 (the M side of both products):
+//   phi_part[k, j]  += sum_row x[row, k] d_raw[row, j]      A = x^T (from shared memory),  B = d_raw
+//   grad_x[row, k]   = coef[row] x[row, k] + sum_j phi[k, j] d_raw[row, j]
+//                                                             A = phi (registers, loaded once), B = d_raw^T
+// Rows are walked 32 at a time.  x stages ([32 rows][64 k], stride 72 floats) are copied with 16-byte
+// cp.async two stages ahead of the arithmetic; the per-row records are read one stage ahead into
+// registers, split into TF32 hi / lo once, and kept as [row][j ^ 4*(row/4 & 1)] with a stride of 40
+// floats, a layout that serves both B-fragment patterns without bank conflicts.
+constexpr int kTK = 64, kTR = 32, kTXS = kTK + 8, kTDS = 40;
+
+__global__ void __launch_bounds__(128, 4)
+k_dw_bwd_x_rows_mma(const float* __restrict__ x, const float* __restrict__ phi, const float* __restrict__ buf,
+                    float* __restrict__ grad_x, float* __restrict__ phi_part, int64_t batch, int64_t K,
+                    int64_t rows_per_tile) {
+  __shared__ __align__(16) float xs[3][kTR][kTXS];
+  __shared__ uint32_t dh[2][kTR][kTDS], dl[2][kTR][kTDS];
+  __shared__ float s_coef[2][kTR];
+  pdl_prologue();
+  const int tid = threadIdx.x;
+  const int w = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const int64_t kc0 = (int64_t)blockIdx.x * kTK;
+  const int64_t t0 = (int64_t)blockIdx.y * rows_per_tile, t1 = min(t0 + rows_per_tile, batch);
+  const int nst = t1 > t0 ? (int)((t1 - t0 + kTR - 1) / kTR) : 0;
+
+  auto issue = [&](int st) {       // x rows t0 + 32 st .. + 31 into ring slot st % 3 (zero-filled outside)
+    if (st < nst) {
+      const int64_t r0 = t0 + (int64_t)st * kTR;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int idx = i * 128 + tid, r = idx >> 4, q = idx & 15;
+        const int64_t row = r0 + r, k = kc0 + 4 * q;
+        const bool ok = row < t1 && k < K;
+        cp_async16(&xs[st % 3][r][4 * q], x + (ok ? row * K + k : 0), ok);
+      }
+    }
+    cp_async_commit();
+  };
+  float dreg[7];
+  auto load_d = [&](int st) {      // records of stage st into registers (zeros outside the tile)
+    const int64_t r0 = t0 + (int64_t)st * kTR;
+#pragma unroll
+    for (int i = 0; i < 7; ++i) {
+      const int idx = i * 128 + tid, rr = idx / 25, jj = idx % 25;
+      dreg[i] = (idx < kTR * 25 && st < nst && r0 + rr < t1) ? __ldg(buf + (r0 + rr) * kBwdStrideRows + 24 + jj) : 0.f;
+    }
+  };
+  auto store_d = [&](int b) {
+#pragma unroll
+    for (int i = 0; i < 7; ++i) {
+      const int idx = i * 128 + tid, rr = idx / 25, jj = idx % 25;
+      if (idx < kTR * 25) {
+        if (jj < 24) {
+          uint32_t hi, lo;
+          split_tf32(dreg[i], hi, lo);
+          const int c = jj ^ (((rr >> 2) & 1) << 2);
+          dh[b][rr][c] = hi;
+          dl[b][rr][c] = lo;
+        } else {
+          s_coef[b][rr] = dreg[i];
+        }
+      }
+    }
+  };
+
+  // phi rows of this warp's 16 k columns as A fragments of the grad_x product (3 steps over j)
+  uint32_t ph[3][4], pl[3][4];
+#pragma unroll
+  for (int q = 0; q < 3; ++q)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int64_t k = kc0 + 16 * w + g + 8 * (i & 1);
+      const int j = 8 * q + t + 4 * (i >> 1);
+      split_tf32(k < K ? __ldg(phi + k * 24 + j) : 0.f, ph[q][i], pl[q][i]);
+    }
+  float acc[3][4];
+#pragma unroll
+  for (int n = 0; n < 3; ++n)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
+
+  issue(0);
+  issue(1);
+  load_d(0);
+  store_d(0);
+  for (int st = 0; st < nst; ++st) {
+    const int b = st & 1, xb = st % 3;
+    load_d(st + 1);
+    cp_async_wait<1>();              // stage st has landed (stage st + 1 may still be in flight)
+    __syncthreads();                 // everyone is past stage st - 1: its x slot and record buffer are free
+    issue(st + 2);
+    const int64_t r0 = t0 + (int64_t)st * kTR;
+
+    // phi_part: 4 steps of 8 rows
+#pragma unroll
+    for (int s8 = 0; s8 < kTR / 8; ++s8) {
+      uint32_t ah[4], al[4];
+      split_tf32(xs[xb][8 * s8 + t][16 * w + g], ah[0], al[0]);
+      split_tf32(xs[xb][8 * s8 + t][16 * w + g + 8], ah[1], al[1]);
+      split_tf32(xs[xb][8 * s8 + t + 4][16 * w + g], ah[2], al[2]);
+      split_tf32(xs[xb][8 * s8 + t + 4][16 * w + g + 8], ah[3], al[3]);
+#pragma unroll
+      for (int n = 0; n < 3; ++n) {
+        uint32_t bh[2], bl[2];
+        bh[0] = dh[b][8 * s8 + t][8 * n + g];            bl[0] = dl[b][8 * s8 + t][8 * n + g];
+        bh[1] = dh[b][8 * s8 + t + 4][(8 * n + g) ^ 4];  bl[1] = dl[b][8 * s8 + t + 4][(8 * n + g) ^ 4];
+        mma_3xtf32_add(acc[n], ah, al, bh, bl);
+      }
+    }
+    // grad_x: 4 tiles of 8 rows
+#pragma unroll
+    for (int n = 0; n < kTR / 8; ++n) {
+      const int ra = 8 * n + 2 * t;
+      const float ca = s_coef[b][ra], cb = s_coef[b][ra + 1];
+      float c[4];
+      c[0] = ca * xs[xb][ra][16 * w + g];
+      c[1] = cb * xs[xb][ra + 1][16 * w + g];
+      c[2] = ca * xs[xb][ra][16 * w + g + 8];
+      c[3] = cb * xs[xb][ra + 1][16 * w + g + 8];
+      const int rb = 8 * n + g, sw = ((rb >> 2) & 1) << 2;
+#pragma unroll
+      for (int q = 0; q < 3; ++q) {
+        uint32_t bh[2], bl[2];
+        bh[0] = dh[b][rb][(8 * q + t) ^ sw];      bl[0] = dl[b][rb][(8 * q + t) ^ sw];
+        bh[1] = dh[b][rb][(8 * q + t + 4) ^ sw];  bl[1] = dl[b][rb][(8 * q + t + 4) ^ sw];
+        mma_tf32(c, pl[q], bh);
+        mma_tf32(c, ph[q], bl);
+        mma_tf32(c, ph[q], bh);
+      }
+      const int64_t rowa = r0 + ra, ka = kc0 + 16 * w + g;
+      if (rowa < t1) {
+        if (ka < K) grad_x[rowa * K + ka] = c[0];
+        if (ka + 8 < K) grad_x[rowa * K + ka + 8] = c[2];
+      }
+      if (rowa + 1 < t1) {
+        if (ka < K) grad_x[(rowa + 1) * K + ka] = c[1];
+        if (ka + 8 < K) grad_x[(rowa + 1) * K + ka + 8] = c[3];
+      }
+    }
+    store_d(b ^ 1);                  // records of stage st + 1; visible to the others after the next barrier
+  }
+  cp_async_wait<0>();
+#pragma unroll
+  for (int n = 0; n < 3; ++n)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int64_t k = kc0 + 16 * w + g + 8 * h;
+      if (k < K) {
+        float* o = phi_part + ((int64_t)blockIdx.y * K + k) * 24 + 8 * n + 2 * t;
+        o[0] = acc[n][2 * h];
+        o[1] = acc[n][2 * h + 1];
+      }
+    }
 }
 
 // grad_phi[k,j] (+)= sum_tile phi_part[tile,k,j], tiles in index order, fp64.
@@ -325,9 +541,8 @@ int64_t rows_bwd_extra_floats(int64_t batch, int64_t K) {
   return (int64_t)phi_row_tiles(batch) * K * 24 + (int64_t)kSumCtas * 27 * 2 + 2;
 }
 
-// K slices per 128-row block for the tiled projection: the smallest count whose CTAs fill whole waves of
-// the 4 CTAs per SM x 148 SMs that the kernel's registers and shared memory allow to at least 90 %
-// (otherwise the best fill).  Depends on the shape only.
+// K slices per 128-row block for the tensor-core projection: the smallest count whose CTAs fill whole
+// waves of 4 CTAs per SM x 148 SMs to at least 90 % (otherwise the best fill).  Depends on the shape only.
 static int pick_project_slices(int64_t row_ctas, int64_t kslices_max) {
   const int64_t slots = 4 * 148;
   int best = 1;
@@ -345,24 +560,24 @@ static int pick_project_slices(int64_t row_ctas, int64_t kslices_max) {
 
 int project_rows_launch(const float* x, const float* phi, float* part, int64_t batch, int64_t K, int ks_max,
                         cudaStream_t st, int* ks_used) {
-  const bool tiled = (K % 4 == 0) && is_aligned16(x) && is_aligned16(phi);
-  const int rows_per_cta = tiled ? kPR : kRowsPerCta;
-  const int ktile = tiled ? kPK : kKT;
+  const bool mma = (K % 4 == 0) && is_aligned16(x) && is_aligned16(phi);
+  const int rows_per_cta = mma ? kMR : kRowsPerCta;
+  const int ktile = mma ? kMK : kKT;
   const int64_t row_ctas = (batch + rows_per_cta - 1) / rows_per_cta;
   int64_t kmax = (K + ktile - 1) / ktile;
   if (kmax > ks_max) kmax = ks_max;
   if (kmax < 1) kmax = 1;
   int64_t ks;
-  if (tiled) {
+  if (mma) {
     ks = pick_project_slices(row_ctas, kmax);
   } else {
     ks = (2 * 148 + row_ctas - 1) / row_ctas;   // enough CTAs to fill the GPU twice
     if (ks > kmax) ks = kmax;
   }
   if (row_ctas * ks > kMaxGridItems) return fail(MHC_ERR_BAD_SHAPE, "dynamic_weights_fwd: batch too large");
-  if (tiled) {
-    ProfScope ps("k_dw_project_rows_v4", st);
-    launch_k(k_dw_project_rows_v4, (unsigned)(row_ctas * ks), kPR, 0, st, x, phi, part, batch, K, (int)ks);
+  if (mma) {
+    ProfScope ps("k_dw_project_rows_mma", st);
+    launch_k(k_dw_project_rows_mma, (unsigned)(row_ctas * ks), 128, 0, st, x, phi, part, batch, K, (int)ks);
   } else {
     ProfScope ps("k_dw_project_rows", st);
     launch_k(k_dw_project_rows, (unsigned)(row_ctas * ks), kRowsPerCta, 0, st, x, phi, part, batch, K, (int)ks);
@@ -373,9 +588,16 @@ int project_rows_launch(const float* x, const float* phi, float* part, int64_t b
 
 int bwd_rows_launch(const float* x, const float* phi, const float* buf, float* phi_part, float* grad_x, float* grad_phi,
                     float* grad_bias, float* grad_alpha, int64_t batch, int64_t K, int accumulate, cudaStream_t st) {
-  const unsigned kblocks = (unsigned)((K + 255) / 256);
   const int tiles = phi_row_tiles(batch);
-  {
+  if (K % 4 == 0 && is_aligned16(x)) {
+    ProfScope ps("k_dw_bwd_x_rows_mma", st);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)((K + kTK - 1) / kTK), (unsigned)tiles);
+    cfg.blockDim = dim3(128);
+    cfg.stream = st;
+    (void)cudaLaunchKernelEx(&cfg, k_dw_bwd_x_rows_mma, x, phi, buf, grad_x, phi_part, batch, K, phi_rows_per_tile(batch));
+  } else {
+    const unsigned kblocks = (unsigned)((K + 255) / 256);
     ProfScope ps("k_dw_bwd_x_rows", st);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(kblocks, (unsigned)tiles);
