@@ -191,13 +191,58 @@ def describe(name):
             f"fp32 phi[{4 * D},24], 20 Sinkhorn iters, identity branch")
 
 
+def run_per_token(args):
+    """Side workload, not the headline: the dynamic-weights op applied to every token's own state
+    (x [rows, K] fp32 with K = 4 D), forward + backward, one GPU.  Prints one JSON line with the time per
+    forward+backward and the per-kernel breakdown from the library's own CUDA events."""
+    from mhc import _lib
+    from mhc._backward import fused_dynamic_weights_backward
+    from mhc._kernels import fused_dynamic_weights_forward
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    rows, K = args.rows, args.k
+    gen = torch.Generator(device=dev).manual_seed(1234)
+    x = torch.randn(rows, K, device=dev, generator=gen)
+    phi = torch.randn(K, 24, device=dev, generator=gen) * 0.02
+    bias = torch.randn(24, device=dev, generator=gen)
+    al = [torch.full((1,), v, device=dev) for v in (0.3, -0.2, 0.5)]
+    gr = [torch.randn(rows, 4, device=dev, generator=gen), torch.randn(rows, 4, device=dev, generator=gen),
+          torch.randn(rows, 4, 4, device=dev, generator=gen)]
+
+    def step():
+        saved = fused_dynamic_weights_forward(x, phi, bias, *al, 20, 1e-6, return_saved=True)[3]
+        return fused_dynamic_weights_backward(x, phi, bias, *al, saved, *gr, 20, 1e-6)
+
+    for _ in range(max(args.warmup, 2)):
+        step()
+    torch.cuda.synchronize()
+    _lib.profile_start()
+    for _ in range(args.steps):
+        step()
+    prof = _lib.profile_stop()
+    per_kernel = {k: round(t / n * 1e3, 1) for k, (n, t) in prof.items()}          # microseconds per launch
+    ms = sum(t / n for n, t in prof.values())
+    x_bytes = rows * K * 4
+    print(json.dumps({
+        "metric": "dynamic_weights_fwd_bwd_rows_per_s", "value": round(rows / (ms * 1e-3), 1), "unit": "rows/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 2), "ms_per_step": round(ms, 4),
+        "higher_is_better": True, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"per-token dynamic weights, x [{rows}, {K}] fp32, forward + backward",
+                   "l2": "x is larger than L2" if x_bytes > 126e6 else "x fits in L2"},
+        "kernels_us": per_kernel,
+        "hbm_floor_ms": round(3 * x_bytes / (hbm_peak()[0] * 1e9) * 1e3, 4),   # read x twice, write grad_x once
+    }))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS) + ["per_token"])
+    ap.add_argument("--rows", type=int, default=32768, help="per_token workload: rows of x")
+    ap.add_argument("--k", type=int, default=16384, help="per_token workload: columns of x (4 * dim)")
     ap.add_argument("--batch", type=int, default=None, help="override the per-GPU batch (profiling small cases)")
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--cpu-steps", type=int, default=2)
@@ -213,6 +258,11 @@ def main():
                     help="replay the step from a CUDA graph (for small per-GPU batches, where the host would be the limit)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.workload == "per_token":
+        if args.impl != "ours" or args.gpus != 1:
+            raise SystemExit("the per_token workload is a single-GPU measurement of this library only")
+        args.steps = min(args.steps, 20)
+        return run_per_token(args)
     if args.impl == "reference":
         return run_reference(args)
 
