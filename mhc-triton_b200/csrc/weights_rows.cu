@@ -150,14 +150,15 @@ k_dw_project_rows_mma(const float* __restrict__ x, const float* __restrict__ phi
   const int ntile = k1 > k0 ? (int)((k1 - k0 + kMK - 1) / kMK) : 0;
 
   const int lr = tid >> 3, lq = tid & 7;       // x copies: rows lr + 16 i, k offset 4 lq
+  const float* xsrc = x + (row0 + lr) * K + 4 * lq;
+  const int rows_left = (int)min((int64_t)kMR, batch - row0) - lr;   // row lr + 16 i exists iff 16 i < rows_left
   auto issue = [&](int tt, int b) {
     const int64_t kt = k0 + (int64_t)tt * kMK;
+    const bool kok = kt + 4 * lq < k1;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      const int r = lr + 16 * i;
-      const int64_t row = row0 + r, k = kt + 4 * lq;
-      const bool ok = row < batch && k < k1;
-      cp_async16(&xs[b][r][4 * lq], x + (ok ? row * K + k : 0), ok);
+      const bool ok = kok && 16 * i < rows_left;
+      cp_async16(&xs[b][lr + 16 * i][4 * lq], ok ? xsrc + (int64_t)(16 * i) * K + kt : x, ok);
     }
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
@@ -165,7 +166,7 @@ k_dw_project_rows_mma(const float* __restrict__ x, const float* __restrict__ phi
       if (f < kMK * 6) {
         const int kk = f / 6, q = f % 6;
         const bool ok = kt + kk < k1;
-        cp_async16(&ps[b][kk][4 * q], phi + (ok ? (kt + kk) * 24 + 4 * q : 0), ok);
+        cp_async16(&ps[b][kk][4 * q], ok ? phi + (kt + kk) * 24 + 4 * q : phi, ok);
       }
     }
     cp_async_commit();
@@ -349,44 +350,45 @@ k_dw_bwd_x_rows_mma(const float* __restrict__ x, const float* __restrict__ phi, 
   const int64_t t0 = (int64_t)blockIdx.y * rows_per_tile, t1 = min(t0 + rows_per_tile, batch);
   const int nst = t1 > t0 ? (int)((t1 - t0 + kTR - 1) / kTR) : 0;
 
+  const int rows = (int)(t1 - t0);          // rows of this tile (rows_per_tile is far below 2^31)
+
+  // x copies: this thread always copies rows cr + 8 i (i < 4) of a stage at k offset 4 cq
+  const int cr = tid >> 4, cq = tid & 15;
+  const bool ck_ok = kc0 + 4 * cq < K;
+  const float* xsrc = x + (t0 + cr) * K + (ck_ok ? kc0 + 4 * cq : 0);
   auto issue = [&](int st) {       // x rows t0 + 32 st .. + 31 into ring slot st % 3 (zero-filled outside)
     if (st < nst) {
-      const int64_t r0 = t0 + (int64_t)st * kTR;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const int idx = i * 128 + tid, r = idx >> 4, q = idx & 15;
-        const int64_t row = r0 + r, k = kc0 + 4 * q;
-        const bool ok = row < t1 && k < K;
-        cp_async16(&xs[st % 3][r][4 * q], x + (ok ? row * K + k : 0), ok);
+        const int r = st * kTR + 8 * i + cr;
+        const bool ok = ck_ok && r < rows;
+        cp_async16(&xs[st % 3][8 * i + cr][4 * cq], ok ? xsrc + (int64_t)(st * kTR + 8 * i) * K : x, ok);
       }
     }
     cp_async_commit();
   };
-  float dreg[7];
+  // records: this thread always handles row dr of a stage, values 6 dp .. 6 dp + 5 (and coef when dp == 0)
+  const int dr = tid >> 2, dp = tid & 3;
+  const float* dsrc = buf + (t0 + dr) * kBwdStrideRows + 24 + 6 * dp;
+  float dreg[6], dcoef = 0.f;
   auto load_d = [&](int st) {      // records of stage st into registers (zeros outside the tile)
-    const int64_t r0 = t0 + (int64_t)st * kTR;
+    const bool ok = st < nst && st * kTR + dr < rows;
+    const float* q = dsrc + (int64_t)st * (kTR * kBwdStrideRows);
 #pragma unroll
-    for (int i = 0; i < 7; ++i) {
-      const int idx = i * 128 + tid, rr = idx / 25, jj = idx % 25;
-      dreg[i] = (idx < kTR * 25 && st < nst && r0 + rr < t1) ? __ldg(buf + (r0 + rr) * kBwdStrideRows + 24 + jj) : 0.f;
-    }
+    for (int e = 0; e < 6; ++e) dreg[e] = ok ? __ldg(q + e) : 0.f;
+    if (dp == 0) dcoef = ok ? __ldg(q + 24) : 0.f;
   };
   auto store_d = [&](int b) {
+    const int sw = ((dr >> 2) & 1) << 2;
 #pragma unroll
-    for (int i = 0; i < 7; ++i) {
-      const int idx = i * 128 + tid, rr = idx / 25, jj = idx % 25;
-      if (idx < kTR * 25) {
-        if (jj < 24) {
-          uint32_t hi, lo;
-          split_tf32(dreg[i], hi, lo);
-          const int c = jj ^ (((rr >> 2) & 1) << 2);
-          dh[b][rr][c] = hi;
-          dl[b][rr][c] = lo;
-        } else {
-          s_coef[b][rr] = dreg[i];
-        }
-      }
+    for (int e = 0; e < 6; ++e) {
+      uint32_t hi, lo;
+      split_tf32(dreg[e], hi, lo);
+      const int c = (6 * dp + e) ^ sw;
+      dh[b][dr][c] = hi;
+      dl[b][dr][c] = lo;
     }
+    if (dp == 0) s_coef[b][dr] = dcoef;
   };
 
   // phi rows of this warp's 16 k columns as A fragments of the grad_x product (3 steps over j)
@@ -404,6 +406,9 @@ k_dw_bwd_x_rows_mma(const float* __restrict__ x, const float* __restrict__ phi, 
   for (int n = 0; n < 3; ++n)
 #pragma unroll
     for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
+  // grad_x destination of c[0] in stage 0, row tile 0: row 2t, k column 16w + g
+  const bool ka_ok = kc0 + 16 * w + g < K, ka8_ok = kc0 + 16 * w + g + 8 < K;
+  float* gdst = grad_x + (t0 + 2 * t) * K + kc0 + 16 * w + g;
 
   issue(0);
   issue(1);
@@ -415,7 +420,6 @@ k_dw_bwd_x_rows_mma(const float* __restrict__ x, const float* __restrict__ phi, 
     cp_async_wait<1>();              // stage st has landed (stage st + 1 may still be in flight)
     __syncthreads();                 // everyone is past stage st - 1: its x slot and record buffer are free
     issue(st + 2);
-    const int64_t r0 = t0 + (int64_t)st * kTR;
 
     // phi_part: 4 steps of 8 rows
 #pragma unroll
@@ -444,23 +448,27 @@ k_dw_bwd_x_rows_mma(const float* __restrict__ x, const float* __restrict__ phi, 
       c[2] = ca * xs[xb][ra][16 * w + g + 8];
       c[3] = cb * xs[xb][ra + 1][16 * w + g + 8];
       const int rb = 8 * n + g, sw = ((rb >> 2) & 1) << 2;
+      float d[3][4];               // three independent MMA chains (one per 8 values of j), then fp32 adds
 #pragma unroll
       for (int q = 0; q < 3; ++q) {
         uint32_t bh[2], bl[2];
         bh[0] = dh[b][rb][(8 * q + t) ^ sw];      bl[0] = dl[b][rb][(8 * q + t) ^ sw];
         bh[1] = dh[b][rb][(8 * q + t + 4) ^ sw];  bl[1] = dl[b][rb][(8 * q + t + 4) ^ sw];
-        mma_tf32(c, pl[q], bh);
-        mma_tf32(c, ph[q], bl);
-        mma_tf32(c, ph[q], bh);
+        mma_tf32_first(d[q], pl[q], bh);
+        mma_tf32(d[q], ph[q], bl);
+        mma_tf32(d[q], ph[q], bh);
       }
-      const int64_t rowa = r0 + ra, ka = kc0 + 16 * w + g;
-      if (rowa < t1) {
-        if (ka < K) grad_x[rowa * K + ka] = c[0];
-        if (ka + 8 < K) grad_x[rowa * K + ka + 8] = c[2];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) c[i] += (d[0][i] + d[1][i]) + d[2][i];
+      const int left = rows - st * kTR - ra;                 // rows of the tile from row ra of this stage on
+      float* o = gdst + (int64_t)(st * kTR + 8 * n) * K;
+      if (left > 0) {
+        if (ka_ok) o[0] = c[0];
+        if (ka8_ok) o[8] = c[2];
       }
-      if (rowa + 1 < t1) {
-        if (ka < K) grad_x[(rowa + 1) * K + ka] = c[1];
-        if (ka + 8 < K) grad_x[(rowa + 1) * K + ka + 8] = c[3];
+      if (left > 1) {
+        if (ka_ok) o[K] = c[1];
+        if (ka8_ok) o[K + 8] = c[3];
       }
     }
     store_d(b ^ 1);                  // records of stage st + 1; visible to the others after the next barrier
