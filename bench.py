@@ -16,6 +16,9 @@ metric end to end from pinned host buffers, and the CPU oracle timed on the host
 
 `--impl reference` times the CPU implementation of the same layer (the oracle under oracle/,
 a restatement of the reference's pure-PyTorch path) on the host cores, on a bounded sample.
+
+`--workload per_token [--rows R --k K]` is a side measurement, not the headline: the dynamic-weights
+op on one row per token (x [R, K] fp32), forward + backward, with the per-kernel times.
 """
 
 import argparse
