@@ -197,6 +197,11 @@ int mhc_meanpool_fwd(const void* H, float* x, void* scratch, int64_t scratch_byt
  * H_res = Sinkhorn_iters(|s[8:24]| + eps).  alpha_* are device pointers to one float each
  * (no host read of the scales).  saved [batch, 32] fp32 receives raw (24 values), sum(x^2),
  * inv_rms and padding for the backward; it may be NULL.
+ * Any batch is accepted.  Below 64 rows every row gets its own CTAs (the sequence-pooled use, batch =
+ * number of sequences); from 64 rows on (per-token use, batch = number of tokens) both directions tile
+ * over rows and, when K % 4 == 0 and x / phi are 16-byte aligned, compute x phi, grad_x and grad_phi
+ * with TF32 tensor-core MMAs on hi/lo splits of both operands (3xTF32) and fp32 running sums: same
+ * results as the fp32 FMA path to within the fp32 parity band, not bit-identical to it.
  * Replaces fused_dynamic_weights_forward, src/mhc/_kernels.py:690-752 (kernel :318-590). */
 int mhc_dynamic_weights_fwd(const float* x, const float* phi, const float* bias,
                             const float* alpha_pre, const float* alpha_post,
