@@ -57,6 +57,17 @@ def test_scratch_sizes():
     # per-batch-element layout: scratch is linear in B
     assert lib.mhc_scratch_bytes(_lib.OP_MEANPOOL_FWD, 2 * B, S, D, 1) == 2 * lib.mhc_scratch_bytes(_lib.OP_MEANPOOL_FWD, B, S, D, 1)
     assert lib.mhc_scratch_bytes(99, B, S, D, 1) < 0 and lib.mhc_scratch_bytes(0, -1, S, D, 1) < 0
+    # dynamic weights: per-row records only below 64 rows; from 64 rows on (per-token use) also the
+    # grad_phi partial sums of up to 32 row tiles and the column sums of up to 64 summing CTAs
+    K = 4 * D
+    few = lib.mhc_scratch_bytes(_lib.OP_DYNAMIC_WEIGHTS_BWD, 16, 0, D, 0)
+    assert few == 16 * 56 * 4
+    many = lib.mhc_scratch_bytes(_lib.OP_DYNAMIC_WEIGHTS_BWD, 32768, 0, D, 0)
+    assert many == 4 * (32768 * 56 + 32 * K * 24 + 64 * 27 * 2 + 2)
+    one_tile = lib.mhc_scratch_bytes(_lib.OP_DYNAMIC_WEIGHTS_BWD, 100, 0, D, 0)
+    assert one_tile == 4 * (100 * 56 + 1 * K * 24 + 64 * 27 * 2 + 2)
+    # forward: [row, K slice, 25] partial sums with at most 128 slices of at least 256 k
+    assert lib.mhc_scratch_bytes(_lib.OP_DYNAMIC_WEIGHTS_FWD, 8, 0, D, 0) == 8 * 64 * 25 * 4
 
 
 def test_no_cpu_fallback():
