@@ -4,8 +4,20 @@
  * Every entry point takes raw device pointers, 64-bit sizes and the CUDA stream
  * to launch on; nothing here depends on PyTorch.  The library never allocates
  * or frees device memory: outputs and scratch are caller-owned (scratch sizes
- * come from mhc_scratch_bytes).  Inputs are never written.  All launches go to
+ * come from mhc_scratch_bytes).  The one piece of device memory the library
+ * holds itself is the fixed 1 MiB array of mhc_add_residual_bwd_noalloc, which
+ * is part of the library image.  Inputs are never written.  All launches go to
  * the stream passed in; no call synchronises the device or the host.
+ *
+ * Ticket counters.  Entry points with a `tickets` argument can finish their
+ * deterministic sums inside the producing kernel instead of in a second launch:
+ * the CTA that stores the last partial sum of a batch element (detected with an
+ * integer counter) adds all partial sums up in the usual fixed order.  `tickets`
+ * points to at least max(B, 1) int32 counters in device memory that are ZERO on
+ * entry; every kernel leaves them zero again, so one buffer zeroed once serves
+ * all later calls.  Calls that may overlap on the GPU (different streams) need
+ * different counters.  NULL selects the separate finish kernels; the results are
+ * bit-identical either way.
  *
  * Each declaration names the function of the reference project
  * (WithNucleusAI/mHC-triton, paths relative to its root) that it replaces.
@@ -32,7 +44,7 @@
 extern "C" {
 #endif
 
-#define MHC_B200_VERSION 100 /* major*10000 + minor*100 + patch */
+#define MHC_B200_VERSION 200 /* major*10000 + minor*100 + patch */
 
 typedef enum mhc_dtype { MHC_F32 = 0, MHC_BF16 = 1, MHC_F16 = 2 } mhc_dtype;
 
@@ -64,6 +76,7 @@ typedef enum mhc_op {
 } mhc_op;
 
 typedef void* mhc_stream_t; /* a cudaStream_t */
+typedef void* mhc_event_t;  /* a cudaEvent_t */
 
 int mhc_version(void);
 const char* mhc_last_error_string(void);
@@ -139,11 +152,6 @@ int mhc_add_residual_fwd(const void* H_residual, const void* branch_output, cons
                          void* H_new, int64_t B, int64_t S, int64_t D, int dtype,
                          mhc_stream_t stream);
 
-/* Add residual that also leaves, for the next layer, the token sums of the H_new it writes:
- * pool_partials [B, mhc_add_residual_pool_chunks(S, D), 4*D] fp32, to be handed to that layer's
- * mhc_hc_mix_fwd as pooled_partials.  The next layer then reads H once instead of twice
- * (the reference reads it twice: H.mean(dim=1), src/mhc/module.py:123, then the stream-mix
- * kernel, src/mhc/_kernels.py:137-236).  H_new is identical to mhc_add_residual_fwd's. */
 /* Add residual with the residual mix recomputed from H instead of read from a materialised
  * H_residual: H_new[b,s,n,d] = (sum_m H_res[b,n,m] H[b,s,m,d]) + H_post[b,n] branch_output[b,s,d].
  * Together with mhc_hc_mix_fwd called with H_residual == NULL (which then writes branch_input
@@ -155,18 +163,24 @@ int mhc_add_residual_mix_fwd(const void* H, const float* H_res, const void* bran
                              const float* H_post, void* H_new, float* pool_partials, int64_t B,
                              int64_t S, int64_t D, int dtype, mhc_stream_t stream);
 
+/* Add residual that also leaves, for the next layer, the token sums of the H_new it writes:
+ * pool_partials [B, mhc_add_residual_pool_chunks(S, D), 4*D] fp32, to be handed to that layer's
+ * mhc_hc_mix_fwd as pooled_partials.  The next layer then reads H once instead of twice
+ * (the reference reads it twice: H.mean(dim=1), src/mhc/module.py:123, then the stream-mix
+ * kernel, src/mhc/_kernels.py:137-236).  H_new is identical to mhc_add_residual_fwd's. */
 int mhc_add_residual_pool_fwd(const void* H_residual, const void* branch_output, const float* H_post,
                               void* H_new, float* pool_partials, int64_t B, int64_t S, int64_t D,
                               int dtype, mhc_stream_t stream);
 int64_t mhc_add_residual_pool_chunks(int64_t S, int64_t D);
 
 /* d_branch_output and dH_post [B,4] (fp32).  dH_residual equals dH_new and is not written:
- * the caller aliases it.  Replaces add_residual_backward, src/mhc/_backward.py:533-575
+ * the caller aliases it.  `tickets`: see "Ticket counters" above (may be NULL).
+ * Replaces add_residual_backward, src/mhc/_backward.py:533-575
  * (kernel :269-351) including its torch.sum (:573). */
 int mhc_add_residual_bwd(const void* dH_new, const void* branch_output, const float* H_post,
                          void* d_branch_output, float* dH_post, void* scratch,
-                         int64_t scratch_bytes, int64_t B, int64_t S, int64_t D, int dtype,
-                         mhc_stream_t stream);
+                         int64_t scratch_bytes, int32_t* tickets, int64_t B, int64_t S, int64_t D,
+                         int dtype, mhc_stream_t stream);
 
 /* Same result as mhc_add_residual_bwd for callers that cannot supply scratch memory because they
  * have no way to allocate on the device (a C/C++ host without a caching allocator whose serving
@@ -179,6 +193,8 @@ int mhc_add_residual_bwd(const void* dH_new, const void* branch_output, const fl
  * call on each device looks up the array's device address (with that device current) and should
  * therefore come before any stream capture.  All calls on a device share the one array: two calls
  * that may overlap on the GPU (different streams) race and must be ordered by the caller.
+ * `stream` must belong to the device that is current when the call is made (the array's address
+ * is looked up for the current device).
  * This entry point has no counterpart in the reference. */
 int mhc_add_residual_bwd_noalloc(const void* dH_new, const void* branch_output, const float* H_post,
                                  void* d_branch_output, float* dH_post, int64_t B, int64_t S,
@@ -228,20 +244,28 @@ int mhc_dynamic_weights_bwd(const float* x, const float* phi, const float* bias,
  * res [16]), then the stream mix.  If pooled_partials is not NULL it holds the token sums of H
  * as left by mhc_add_residual_pool_fwd of the previous layer ([B, pooled_chunks, 4*D] fp32) and
  * the pass over H for pooling is skipped.  H_residual may be NULL: only branch_input is then
- * written and the caller uses mhc_add_residual_mix_fwd afterwards.  Replaces the chain HyperConnection._compute_weights (fused
- * branch, src/mhc/module.py:119-139) + fused_stream_mix (src/mhc/module.py:177). */
+ * written and the caller uses mhc_add_residual_mix_fwd afterwards.  `tickets`: see "Ticket
+ * counters" above (may be NULL); with them the call is three launches (pooling, projection that
+ * also finishes the weights, stream mix).  Replaces the chain
+ * HyperConnection._compute_weights (fused branch, src/mhc/module.py:119-139) + fused_stream_mix
+ * (src/mhc/module.py:177). */
 int mhc_hc_mix_fwd(const void* H, const float* phi, const float* H_pre_base, const float* H_post_base,
                    const float* H_res_base, const float* alpha_pre, const float* alpha_post,
                    const float* alpha_res, float* x, float* H_pre, float* H_post, float* H_res,
                    float* saved, void* branch_input, void* H_residual,
                    const float* pooled_partials, int64_t pooled_chunks, void* scratch,
-                   int64_t scratch_bytes, int64_t B, int64_t S, int64_t D, int dtype, int iters,
-                   float eps, mhc_stream_t stream);
+                   int64_t scratch_bytes, int32_t* tickets, int64_t B, int64_t S, int64_t D,
+                   int dtype, int iters, float eps, mhc_stream_t stream);
 
 /* Backward of the same chain in one call.  In: gradients of branch_input, H_residual and H_post
  * plus what the forward left (H, x, saved, H_pre, H_res).  Out: dH (including grad_x / S, i.e.
  * the gradient through the mean-pool), grad_phi [4D,24], grad_bias [24] (pre, post, res bases),
  * grad_alpha [3]; grad_x [B,4D], dH_pre [B,4] and dH_res [B,16] are also written (fp32).
+ * `tickets`: see "Ticket counters" above (may be NULL); with them the call is three launches
+ * (reduction pass, weights backward, apply pass).  `weight_grads_ready` (may be NULL) is a CUDA
+ * event that the call records on `stream` after the kernels that write grad_phi / grad_bias /
+ * grad_alpha and before the apply pass that writes dH, so that a collective on another stream can
+ * reduce the parameter gradients while dH is still being written.
  * Replaces _FusedStreamMix.backward + _FusedDynamicWeights.backward (src/mhc/ops.py:42-49,
  * 109-228) and autograd's backward of H.mean(dim=1) and torch.cat (src/mhc/module.py:123-131). */
 int mhc_hc_mix_bwd(const void* d_branch_input, const void* dH_residual, const float* dH_post,
@@ -250,8 +274,9 @@ int mhc_hc_mix_bwd(const void* d_branch_input, const void* dH_residual, const fl
                    const float* alpha_post, const float* alpha_res, const float* saved,
                    const float* H_pre, const float* H_res, void* dH, float* grad_phi, float* grad_bias,
                    float* grad_alpha, float* grad_x, float* dH_pre, float* dH_res, void* scratch,
-                   int64_t scratch_bytes, int64_t B, int64_t S, int64_t D, int dtype, int iters,
-                   float eps, int abs_grad_at_zero, int accumulate_params, mhc_stream_t stream);
+                   int64_t scratch_bytes, int32_t* tickets, mhc_event_t weight_grads_ready, int64_t B,
+                   int64_t S, int64_t D, int dtype, int iters, float eps, int abs_grad_at_zero,
+                   int accumulate_params, mhc_stream_t stream);
 
 #ifdef __cplusplus
 }

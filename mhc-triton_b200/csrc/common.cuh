@@ -41,11 +41,17 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(flo
 template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
 
 // Read-only 16-byte load that does not allocate in L1 (every byte is used exactly once per kernel).
+// Volatile with a memory clobber so that the compiler never moves it above griddepcontrol.wait: the
+// tensor may have been written by the kernel before this one on the stream, which can still be
+// running when a kernel launched with programmatic serialization starts.  After that wait nobody
+// writes the tensor any more, and no line of it can sit in this SM's L1 from earlier (the loads never
+// allocate there), so the non-coherent path returns what the previous kernel wrote.
 __device__ __forceinline__ uint4 ld_stream16(const void* p) {
   uint4 r;
-  asm("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-      : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
-      : "l"(p));
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+               : "l"(p)
+               : "memory");
   return r;
 }
 #ifndef MHC_ST_MODE
@@ -330,6 +336,9 @@ __device__ __forceinline__ double sum_strided_f64(const float* __restrict__ p, i
 // t, t+256, ... (all loads issued before any use), a xor-shuffle tree adds the lanes of each warp,
 // and after the barrier sm[w][j] holds warp w's sum of column j; callers add the 8 warps in index
 // order.  fp64 throughout; the order depends only on `slots`.
+// FRESH: the rows were written by other CTAs of the SAME kernel (last-arriving-CTA finish), so they
+// are read with ld.global.cg (L2, never a stale or non-coherent cache line).
+template <bool FRESH = false>
 __device__ __forceinline__ void block_column_sums_f64(const float* __restrict__ p, int64_t slots, int W,
                                                       double (*sm)[20]) {
   double a[20];
@@ -339,7 +348,7 @@ __device__ __forceinline__ void block_column_sums_f64(const float* __restrict__ 
     const float* q = p + s * W;
 #pragma unroll
     for (int j = 0; j < 20; ++j)
-      if (j < W) a[j] += (double)__ldg(q + j);
+      if (j < W) a[j] += (double)(FRESH ? __ldcg(q + j) : __ldg(q + j));
   }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 #pragma unroll
@@ -350,6 +359,28 @@ __device__ __forceinline__ void block_column_sums_f64(const float* __restrict__ 
     }
   }
   __syncthreads();
+}
+
+// Last-arriving-CTA detection for a group of `expected` CTAs that share the counter *ticket.
+// Every CTA of the group calls this after its global writes; exactly one call (the one that
+// arrives last) returns true, and by then the writes of all the others are visible to it (read
+// them with ld.global.cg).  The counter must be 0 before the kernel starts and is 0 again when the
+// kernel ends, so one zero-initialised buffer serves every launch on a stream.  Only an integer
+// counter is contended: whatever the last CTA then sums, it sums in a fixed order.
+// All threads of the CTA must call this (it contains barriers).
+__device__ __forceinline__ bool cta_arrives_last(int* ticket, int expected) {
+  __shared__ int s_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int old = atomicAdd(ticket, 1);
+    s_last = (old == expected - 1) ? 1 : 0;
+    if (s_last) *ticket = 0;
+  }
+  __syncthreads();
+  const bool last = s_last != 0;
+  if (last) __threadfence();
+  return last;
 }
 
 // ---------------------------------------------------------------------------------------

@@ -18,6 +18,7 @@ int fail(int status, const char* fmt, ...);  // records the message for mhc_last
 int check_launch(const char* what);          // cudaGetLastError -> status
 
 inline bool is_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline bool is_aligned_to(const void* p, unsigned n) { return (reinterpret_cast<uintptr_t>(p) & (n - 1u)) == 0; }
 
 // Geometry of a streaming kernel over [B, S, 4, D].
 //   vec   : elements per pack (1 = scalar path for odd D or unaligned pointers)
@@ -72,7 +73,8 @@ int meanpool_partial_impl(const void* H, float* part, int64_t B, int64_t S, int6
                           int* nchunk);
 int mix_bwd_partials_impl(int mode, const void* dbi, const void* dHr, const void* H, const float* H_pre,
                           const float* H_res, void* dH, float* part, int64_t B, int64_t S, int64_t D, int dtype,
-                          cudaStream_t st, int64_t* slots);
+                          cudaStream_t st, int64_t* slots, int* tickets, float* dH_pre, float* dH_res);
+bool ticket_finish_supported();
 int64_t add_residual_bwd_need_bytes(const void* dH_new, const void* bo, const void* dbo, int64_t B, int64_t S,
                                     int64_t D, int dtype);
 int check_bsd_pub(const char* what, int64_t B, int64_t S, int64_t D, int dtype);
@@ -83,7 +85,7 @@ int64_t mix_bwd_scratch_floats(int64_t B, int64_t S, int64_t D);
 int weights_fwd_impl(const float* xsrc, int nsrc, double scale, float* x_out, const float* phi, BiasPtrs bias,
                      const float* alpha_pre, const float* alpha_post, const float* alpha_res, float* H_pre,
                      float* H_post, float* H_res, float* saved, float* part, int64_t batch, int64_t K, int iters,
-                     float eps, cudaStream_t st);
+                     float eps, int* tickets, cudaStream_t st);
 int weights_bwd_impl(const float* x, const float* phi, BiasPtrs bias, const float* alpha_pre, const float* alpha_post,
                      const float* alpha_res, const float* saved, const float* part20, int64_t slots, float* dH_pre,
                      const float* dH_post, float* dH_res, float* grad_x, float* grad_phi, float* grad_bias,

@@ -68,5 +68,5 @@ extern "C" int mhc_add_residual_bwd_noalloc(const void* dH_new, const void* bran
   // Every partial-sum slot the finish kernel reads is written by the main kernel of the same call,
   // so nothing in the area has to be cleared between calls.
   return mhc_add_residual_bwd(dH_new, branch_output, H_post, d_branch_output, dH_post, scratch,
-                              mhc_add_residual_bwd_noalloc_max_bytes(), B, S, D, dtype, stream);
+                              mhc_add_residual_bwd_noalloc_max_bytes(), nullptr, B, S, D, dtype, stream);
 }

@@ -196,11 +196,12 @@ extern "C" int mhc_sinkhorn_fwd(const void* M, void* P, int64_t batch, int dtype
 extern "C" int mhc_sinkhorn_bwd(const void* M, const void* dP, void* dM, int64_t batch, int dtype, int iters,
                                 float eps, int abs_grad_at_zero, mhc_stream_t stream) {
   if (batch == 0) return MHC_OK;
-  if (!M || !dP || !dM) return fail(MHC_ERR_NULL_POINTER, "sinkhorn_bwd: null pointer");
+  // scalar arguments first, pointers last: a call with bad scalars and null pointers reports the scalars
   if (batch < 0 || batch > kMaxGridItems * 128) return fail(MHC_ERR_BAD_SHAPE, "sinkhorn_bwd: bad batch");
   if (iters < 0) return fail(MHC_ERR_BAD_ARGUMENT, "sinkhorn_bwd: iters < 0");
   if (abs_grad_at_zero != MHC_ABS0_ZERO && abs_grad_at_zero != MHC_ABS0_PLUS_ONE)
     return fail(MHC_ERR_BAD_ARGUMENT, "sinkhorn_bwd: abs_grad_at_zero must be 0 or 1");
+  if (!M || !dP || !dM) return fail(MHC_ERR_NULL_POINTER, "sinkhorn_bwd: null pointer");
   const float sz = abs_grad_at_zero == MHC_ABS0_PLUS_ONE ? 1.f : 0.f;
   cudaStream_t st = (cudaStream_t)stream;
   switch (dtype) {

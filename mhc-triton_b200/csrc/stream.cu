@@ -379,14 +379,33 @@ k_add_residual_mix_fwd(const T* __restrict__ H, const float* __restrict__ Hres, 
   }
 }
 
+// Sum the [slots, W] per-CTA partial sums of batch element b (written by the CTAs of THIS kernel) in
+// fp64, fixed order, exactly as k_reduce_partials does; columns [0, W0) go to out0, the rest to
+// out1.  Called by the one CTA of the batch element that arrived last (cta_arrives_last); `sm` is
+// 8 x 20 doubles of shared memory no longer used for anything else.
+__device__ __forceinline__ void finish_partials(const float* __restrict__ part, int64_t b, int64_t slots, int W, int W0,
+                                                float* __restrict__ out0, float* __restrict__ out1,
+                                                double (*sm)[20]) {
+  block_column_sums_f64<true>(part + b * slots * W, slots, W, sm);
+  const int j = threadIdx.x;
+  if (j < W) {
+    double t = 0.0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) t += sm[w][j];
+    if (j < W0) out0[b * W0 + j] = (float)t;
+    else out1[b * (W - W0) + (j - W0)] = (float)t;
+  }
+}
+
 // d_branch_output[s,d] = sum_n H_post[n] g[s,n,d];  partial dH_post[n] = sum_{s,d} g[s,n,d] bo[s,d].
-// part: [B, slots, 4].
+// part: [B, slots, 4].  With tickets (one zeroed counter per batch element) the CTA of a batch
+// element that stores its partial last also adds them all up into dH_post[b].
 template <typename T, int V>
 __global__ void __launch_bounds__(MHC_MAX_COLS)
 k_add_residual_bwd(const T* __restrict__ G, const T* __restrict__ bo, const float* __restrict__ Hpost,
-                   T* __restrict__ dbo, float* __restrict__ part, Geo g) {
+                   T* __restrict__ dbo, float* __restrict__ part, Geo g, int* tickets, float* __restrict__ dH_post) {
   pdl_prologue();
-  __shared__ float red[32 * 4];
+  __shared__ __align__(8) float red[32 * 20];
   const Item it = decode_item(g);
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
   if (it.col < g.DV) {
@@ -421,18 +440,25 @@ k_add_residual_bwd(const T* __restrict__ G, const T* __restrict__ bo, const floa
         });
   }
   block_reduce_store<4>(acc, part + (it.b * geo_slots_dev(g) + it.slot) * 4, red);
+  if (!tickets) return;
+  const int64_t slots = geo_slots_dev(g);
+  if (cta_arrives_last(tickets + it.b, (int)slots))
+    finish_partials(part, it.b, slots, 4, 4, dH_post, nullptr, reinterpret_cast<double (*)[20]>(red));
 }
 
 // ---------------------------------------------------------------------- stream mix backward
 // MODE 0: dH and partials.  MODE 1: partials only (the apply pass writes dH later).
-// part: [B, slots, 20] = dH_pre[4] then dH_res[4][4] row-major.
+// part: [B, slots, 20] = dH_pre[4] then dH_res[4][4] row-major.  With tickets (one zeroed counter per
+// batch element) the CTA of a batch element that stores its partial last also adds them all up into
+// dH_pre[b] / dH_res[b].
 template <typename T, int V, int MODE>
 __global__ void __launch_bounds__(MHC_MAX_COLS, MODE == 0 ? 1 : 512 / MHC_MAX_COLS)
 k_stream_mix_bwd(const T* __restrict__ dbi, const T* __restrict__ dHr, const T* __restrict__ H,
                  const float* __restrict__ Hpre, const float* __restrict__ Hres, T* __restrict__ dH,
-                 float* __restrict__ part, Geo g) {
+                 float* __restrict__ part, Geo g, int* tickets, float* __restrict__ dH_pre,
+                 float* __restrict__ dH_res) {
   pdl_prologue();
-  __shared__ float red[32 * 20];
+  __shared__ __align__(8) float red[32 * 20];
   const Item it = decode_item(g);
   float acc[20];
 #pragma unroll
@@ -485,6 +511,10 @@ k_stream_mix_bwd(const T* __restrict__ dbi, const T* __restrict__ dHr, const T* 
         });
   }
   block_reduce_store<20>(acc, part + (it.b * geo_slots_dev(g) + it.slot) * 20, red);
+  if (!tickets) return;
+  const int64_t slots = geo_slots_dev(g);
+  if (cta_arrives_last(tickets + it.b, (int)slots))
+    finish_partials(part, it.b, slots, 20, 4, dH_pre, dH_res, reinterpret_cast<double (*)[20]>(red));
 }
 
 // dH[s,m,d] = H_pre[m] d_bi[s,d] + sum_n H_res[n,m] dH_residual[s,n,d] + inv_S * gx[m*D + d].
@@ -697,6 +727,9 @@ static int check_bsd(const char* what, int64_t B, int64_t S, int64_t D, int dtyp
   return MHC_OK;
 }
 
+// The in-kernel finish of the per-CTA partial sums is written for CTAs of 256 threads.
+bool ticket_finish_supported() { return MHC_MAX_COLS == 256; }
+
 static int check_grid(const char* what, int64_t items) {
   if (items > kMaxGridItems) return fail(MHC_ERR_BAD_SHAPE, "%s: too many work items (%lld)", what, (long long)items);
   return MHC_OK;
@@ -761,9 +794,11 @@ int meanpool_partial_impl(const void* H, float* part, int64_t B, int64_t S, int6
 }
 
 // mode 0: dH + partials; mode 1: partials only.
+// tickets != null: the kernel itself finishes the sums into dH_pre / dH_res (see k_stream_mix_bwd).
 int mix_bwd_partials_impl(int mode, const void* dbi, const void* dHr, const void* H, const float* H_pre,
                           const float* H_res, void* dH, float* part, int64_t B, int64_t S, int64_t D, int dtype,
-                          cudaStream_t st, int64_t* slots) {
+                          cudaStream_t st, int64_t* slots, int* tickets, float* dH_pre, float* dH_res) {
+  if (!ticket_finish_supported()) tickets = nullptr;
   const int vec = pick_vec(dtype, D, {dbi, dHr, H, dH});
   Geo g = make_geo(S, D, vec, GeoKind::Reduce, MHC_TPC_MIXBWD);
   g.reverse = (MHC_REV_MASK >> 4) & 1;
@@ -773,11 +808,13 @@ int mix_bwd_partials_impl(int mode, const void* dbi, const void* dHr, const void
   if (mode == 0) {
     ProfScope ps("k_stream_mix_bwd_full", st);
     MHC_DISPATCH(dtype, vec, (launch_k(k_stream_mix_bwd<T, V, 0>, (unsigned)items, geo_block(g), 0, st, 
-                                 (const T*)dbi, (const T*)dHr, (const T*)H, H_pre, H_res, (T*)dH, part, g)));
+                                 (const T*)dbi, (const T*)dHr, (const T*)H, H_pre, H_res, (T*)dH, part, g, tickets,
+                                 dH_pre, dH_res)));
   } else {
     ProfScope ps("k_stream_mix_bwd_reduce", st);
     MHC_DISPATCH(dtype, vec, (launch_k(k_stream_mix_bwd<T, V, 1>, (unsigned)items, geo_block(g), 0, st, 
-                                 (const T*)dbi, (const T*)dHr, (const T*)H, nullptr, nullptr, nullptr, part, g)));
+                                 (const T*)dbi, (const T*)dHr, (const T*)H, nullptr, nullptr, nullptr, part, g, tickets,
+                                 dH_pre, dH_res)));
   }
   return check_launch("stream_mix_bwd");
 }
@@ -933,17 +970,17 @@ extern "C" int mhc_add_residual_pool_fwd(const void* H_residual, const void* bra
 
 extern "C" int mhc_add_residual_bwd(const void* dH_new, const void* branch_output, const float* H_post,
                                     void* d_branch_output, float* dH_post, void* scratch, int64_t scratch_bytes,
-                                    int64_t B, int64_t S, int64_t D, int dtype, mhc_stream_t stream) {
+                                    int32_t* tickets, int64_t B, int64_t S, int64_t D, int dtype,
+                                    mhc_stream_t stream) {
   if (int e = check_bsd("add_residual_bwd", B, S, D, dtype)) return e;
   if (B == 0) return MHC_OK;
-  if (!dH_post) return fail(MHC_ERR_NULL_POINTER, "add_residual_bwd: null pointer");
   cudaStream_t st = (cudaStream_t)stream;
   if (S == 0 || D == 0) {
+    if (!dH_post) return fail(MHC_ERR_NULL_POINTER, "add_residual_bwd: null pointer");
     if (cudaMemsetAsync(dH_post, 0, B * 4 * sizeof(float), st) != cudaSuccess) return check_launch("add_residual_bwd");
     return MHC_OK;
   }
-  if (!dH_new || !branch_output || !H_post || !d_branch_output || !scratch)
-    return fail(MHC_ERR_NULL_POINTER, "add_residual_bwd: null pointer");
+  // sizes first, pointers last: a call whose scratch is too small says so even with null pointers
   const int vec = pick_vec(dtype, D, {dH_new, branch_output, d_branch_output});
   Geo g = make_geo(S, D, vec, GeoKind::Reduce, MHC_TPC_ADDBWD);
   g.reverse = (MHC_REV_MASK >> 3) & 1;
@@ -952,13 +989,19 @@ extern "C" int mhc_add_residual_bwd(const void* dH_new, const void* branch_outpu
   if (scratch_bytes < items * 4 * (int64_t)sizeof(float))
     return fail(MHC_ERR_SCRATCH_TOO_SMALL, "add_residual_bwd: scratch %lld < %lld bytes", (long long)scratch_bytes,
                 (long long)(items * 4 * sizeof(float)));
+  if (!dH_new || !branch_output || !H_post || !d_branch_output || !dH_post || !scratch)
+    return fail(MHC_ERR_NULL_POINTER, "add_residual_bwd: null pointer");
+  if (!is_aligned_to(tickets, 4) || !is_aligned_to(scratch, 4) || !is_aligned_to(dH_post, 4))
+    return fail(MHC_ERR_MISALIGNED, "add_residual_bwd: tickets / scratch / dH_post must be 4-byte aligned");
+  if (!ticket_finish_supported()) tickets = nullptr;
   {
     ProfScope ps("k_add_residual_bwd", st);
     MHC_DISPATCH(dtype, vec, (launch_k(k_add_residual_bwd<T, V>, (unsigned)items, geo_block(g), 0, st, 
                                  (const T*)dH_new, (const T*)branch_output, H_post, (T*)d_branch_output,
-                                 (float*)scratch, g)));
+                                 (float*)scratch, g, (int*)tickets, dH_post)));
   }
   if (int e = check_launch("add_residual_bwd")) return e;
+  if (tickets) return MHC_OK;   // the last CTA of every batch element has written dH_post
   return launch_reduce((const float*)scratch, B, slots, 4, 4, dH_post, nullptr, st, "add_residual_bwd(reduce)");
 }
 
@@ -981,7 +1024,8 @@ static int mix_bwd_common(const char* what, int mode, const void* dbi, const voi
     return fail(MHC_ERR_SCRATCH_TOO_SMALL, "%s: scratch %lld < %lld bytes", what, (long long)scratch_bytes,
                 (long long)(mix_bwd_scratch_floats(B, S, D) * sizeof(float)));
   int64_t slots = 0;
-  if (int e = mix_bwd_partials_impl(mode, dbi, dHr, H, H_pre, H_res, dH, (float*)scratch, B, S, D, dtype, st, &slots))
+  if (int e = mix_bwd_partials_impl(mode, dbi, dHr, H, H_pre, H_res, dH, (float*)scratch, B, S, D, dtype, st, &slots,
+                                    nullptr, nullptr, nullptr))
     return e;
   return launch_reduce((const float*)scratch, B, slots, 20, 4, dH_pre, dH_res, st, what);
 }

@@ -59,7 +59,7 @@ def add_residual_backward(dH_new: torch.Tensor, branch_output: torch.Tensor, H_p
     buf, nbytes = L.scratch(L.OP_ADD_RESIDUAL_BWD, B, S, D, dH_new)
     with torch.cuda.device(dH_new.device):
         L.call("mhc_add_residual_bwd", L.stream_of(dH_new), L.ptr(dH_new), L.ptr(branch_output), L.ptr(H_post), L.ptr(d_bo),
-                                              L.ptr(dH_post), L.ptr(buf), nbytes, B, S, D, L.dtype_code(dH_new))
+               L.ptr(dH_post), L.ptr(buf), nbytes, L.tickets(dH_new, B), B, S, D, L.dtype_code(dH_new))
     return dH_new, d_bo, dH_post
 
 
@@ -153,10 +153,13 @@ def fused_dynamic_weights_backward(x, phi, bias, alpha_pre, alpha_post, alpha_re
 
 def hc_mix_backward(d_branch_input, dH_residual, dH_post, H, x, phi, H_pre_base, H_post_base, H_res_base,
                     alpha_pre, alpha_post, alpha_res, saved, H_pre, H_res, sinkhorn_iters: int = 20,
-                    eps: float = 1e-6, param_grads=None, accumulate: bool = False):
+                    eps: float = 1e-6, param_grads=None, accumulate: bool = False, ready_event=None):
     """Fused backward of hc_mix_forward in ONE library call.  Returns
     (dH, grad_phi [4D,24], grad_bias [24], grad_alpha [3]) with the last three being views of the
-    flat fp32 record `param_grads` (allocated here when not given; layout phi | bias | alpha)."""
+    flat fp32 record `param_grads` (allocated here when not given; layout phi | bias | alpha).
+    `ready_event` (a torch.cuda.Event that has been recorded at least once, so that it owns a CUDA
+    event) is recorded by the library on the current stream between the kernels that write the
+    parameter gradients and the pass that writes dH."""
     B, S, _, D = H.shape
     K = 4 * D
     d_bi, dHr, H = _mix_bwd_inputs(d_branch_input, dH_residual, H)
@@ -180,6 +183,7 @@ def hc_mix_backward(d_branch_input, dH_residual, dH_post, H, x, phi, H_pre_base,
         L.call("mhc_hc_mix_bwd", L.stream_of(H), L.ptr(d_bi), L.ptr(dHr), L.ptr(dH_post), L.ptr(H), L.ptr(x), L.ptr(phi),
                L.ptr(pre_b), L.ptr(post_b), L.ptr(res_b), L.ptr(a[0]), L.ptr(a[1]), L.ptr(a[2]), L.ptr(saved),
                L.ptr(H_pre), L.ptr(H_res), L.ptr(dH), L.ptr(g_phi), L.ptr(g_bias), L.ptr(g_alpha), L.ptr(grad_x),
-               L.ptr(dH_pre), L.ptr(dH_res), L.ptr(buf), nbytes, B, S, D, L.dtype_code(H), int(sinkhorn_iters),
-               float(eps), _ABS0[_abs_grad_at_zero], 1 if accumulate else 0)
+               L.ptr(dH_pre), L.ptr(dH_res), L.ptr(buf), nbytes, L.tickets(H, B),
+               (ready_event.cuda_event or None) if ready_event is not None else None, B, S, D, L.dtype_code(H),
+               int(sinkhorn_iters), float(eps), _ABS0[_abs_grad_at_zero], 1 if accumulate else 0)
     return dH, g_phi, g_bias, g_alpha

@@ -164,8 +164,8 @@ def hc_mix_forward(H, H_pre_base, H_post_base, H_res_base, phi, alpha_pre, alpha
     with torch.cuda.device(dev):
         L.call("mhc_hc_mix_fwd", L.stream_of(H), L.ptr(H), L.ptr(phi), L.ptr(pre_b), L.ptr(post_b), L.ptr(res_b),
                L.ptr(a[0]), L.ptr(a[1]), L.ptr(a[2]), L.ptr(x), L.ptr(H_pre), L.ptr(H_post), L.ptr(H_res), L.ptr(saved),
-               L.ptr(bi), L.ptr(Hr), L.ptr(pooled), chunks, L.ptr(buf), nbytes, B, S, D, L.dtype_code(H),
-               int(sinkhorn_iters), float(eps))
+               L.ptr(bi), L.ptr(Hr), L.ptr(pooled), chunks, L.ptr(buf), nbytes, L.tickets(H, B), B, S, D,
+               L.dtype_code(H), int(sinkhorn_iters), float(eps))
     return bi, Hr, H_post, H_pre, H_res, x, saved
 
 

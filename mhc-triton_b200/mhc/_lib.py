@@ -33,15 +33,15 @@ _PROTOTYPES = {
     "mhc_stream_mix_bwd_reduce": [_P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _I, _P],
     "mhc_stream_mix_bwd_apply": [_P, _P, _P, _P, _P, _F, _P, _L, _L, _L, _I, _P],
     "mhc_add_residual_fwd": [_P, _P, _P, _P, _L, _L, _L, _I, _P],
-    "mhc_add_residual_bwd": [_P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _I, _P],
+    "mhc_add_residual_bwd": [_P, _P, _P, _P, _P, _P, _L, _P, _L, _L, _L, _I, _P],
     "mhc_meanpool_fwd": [_P, _P, _P, _L, _L, _L, _L, _I, _P],
     "mhc_dynamic_weights_fwd": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _I, _F, _P],
     "mhc_dynamic_weights_bwd": [_P] * 15 + [_L, _L, _L, _I, _F, _I, _I, _P],
     "mhc_add_residual_bwd_noalloc": [_P, _P, _P, _P, _P, _L, _L, _L, _I, _P],
-    "mhc_hc_mix_fwd": [_P] * 16 + [_L, _P, _L, _L, _L, _L, _I, _I, _F, _P],
+    "mhc_hc_mix_fwd": [_P] * 16 + [_L, _P, _L, _P, _L, _L, _L, _I, _I, _F, _P],
     "mhc_add_residual_pool_fwd": [_P, _P, _P, _P, _P, _L, _L, _L, _I, _P],
     "mhc_add_residual_mix_fwd": [_P, _P, _P, _P, _P, _P, _L, _L, _L, _I, _P],
-    "mhc_hc_mix_bwd": [_P] * 23 + [_L, _L, _L, _L, _I, _I, _F, _I, _I, _P],
+    "mhc_hc_mix_bwd": [_P] * 23 + [_L, _P, _P, _L, _L, _L, _I, _I, _F, _I, _I, _P],
 }
 
 EXPORTS = sorted(list(_PROTOTYPES) + ["mhc_version", "mhc_last_error_string", "mhc_status_name", "mhc_scratch_bytes",
@@ -157,6 +157,26 @@ def scratch(op, B, S, D, like: torch.Tensor):
     if n < 0:
         raise MhcError("mhc_scratch_bytes: bad arguments")
     return torch.empty(max(n, 4) // 4, device=like.device, dtype=torch.float32), n
+
+
+_tickets = {}
+
+
+def tickets(like: torch.Tensor, n: int):
+    """Device pointer of at least `n` zeroed int32 ticket counters for calls on `like`'s device and
+    torch's current stream there.  The kernels leave the counters zero, so the buffer is zeroed only
+    when it is created; it is kept per (device, stream) because calls that can overlap on the GPU
+    must not share counters.  Created outside of stream capture on first use (warm up before
+    capturing a CUDA graph, as torch requires anyway)."""
+    dev = like.device.index if like.device.index is not None else torch.cuda.current_device()
+    key = (dev, stream_of(like))
+    buf = _tickets.get(key)
+    if buf is None or buf.numel() < n:
+        if torch.cuda.is_current_stream_capturing():
+            return None          # never allocate the persistent counters from a graph's private pool
+        buf = torch.zeros(max(1024, 2 * n), device=like.device, dtype=torch.int32)
+        _tickets[key] = buf
+    return buf.data_ptr()
 
 
 def f32c(t: torch.Tensor) -> torch.Tensor:

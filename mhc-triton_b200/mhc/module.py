@@ -10,8 +10,8 @@ from typing import Callable, Tuple
 import torch
 import torch.nn as nn
 
-from .ops import (add_residual_from_state, fused_add_residual, version_of, fused_dynamic_weights, fused_stream_mix, hyper_connection_mix, pooled_sums_of,
-                  sequence_mean_pool, sinkhorn_knopp)
+from .ops import (add_residual_from_state, fused_add_residual, fused_dynamic_weights, fused_stream_mix,
+                  hyper_connection_mix, pooled_sums_of, sequence_mean_pool, sinkhorn_knopp, version_of)
 
 
 class HyperConnection(nn.Module):
@@ -51,6 +51,7 @@ class HyperConnection(nn.Module):
         # into it back to back (see mhc.parallel).
         self.grad_sink = None
         self.grads_ready_hook = None
+        self.grads_ready_event = None  # torch.cuda.Event recorded by the backward once grad_sink is complete
         self.grad_accumulate = False   # add to grad_sink instead of overwriting it
         # Fused dynamic path: do not write H_residual in forward(); add_residual() recomputes the residual
         # mix from H in the same kernel that adds the branch output (8 of 46 bytes per element less).
@@ -117,7 +118,7 @@ class HyperConnection(nn.Module):
             branch_input, H_residual, H_post, _, H_res = hyper_connection_mix(
                 H, self.H_pre_base, self.H_post_base, self.H_res_base, self.phi, self.alpha_pre, self.alpha_post,
                 self.alpha_res, self.sinkhorn_iters, self.eps, self.grad_sink, self.grads_ready_hook,
-                self.grad_accumulate, pooled_sums_of(H), lazy)
+                self.grad_accumulate, pooled_sums_of(H), lazy, self.grads_ready_event)
             if lazy:
                 version = version_of(H)
 

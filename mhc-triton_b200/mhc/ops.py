@@ -163,12 +163,14 @@ class _HyperConnectionMix(torch.autograd.Function):
     dH_res), the small weights backward, then one apply pass that writes dH once, including
     grad_x / S.  When `grad_sink` (a flat fp32
     buffer of 4*D*24 + 27 elements) is given, grad_phi / grad_bias / grad_alpha are written
-    straight into it, ready for one all-reduce, and `ready_hook` is told so.
+    straight into it, ready for one all-reduce, and `ready_hook` is told so; `ready_event`, if
+    given, is recorded on the stream between the kernels that fill the buffer and the pass that
+    writes dH, so a collective that waits for it overlaps that pass.
     """
 
     @staticmethod
     def forward(ctx, H, H_pre_base, H_post_base, H_res_base, phi, alpha_pre, alpha_post, alpha_res,
-                sinkhorn_iters, eps, grad_sink, ready_hook, accumulate, pooled, lazy_residual):
+                sinkhorn_iters, eps, grad_sink, ready_hook, accumulate, pooled, lazy_residual, ready_event=None):
         branch_input, H_residual, H_post, H_pre, H_res, x, saved = hc_mix_forward(
             H, H_pre_base, H_post_base, H_res_base, phi, alpha_pre, alpha_post, alpha_res, sinkhorn_iters, eps,
             pooled=pooled, want_residual=not lazy_residual)
@@ -180,6 +182,7 @@ class _HyperConnectionMix(torch.autograd.Function):
                               saved, H_pre, H_res)
         ctx.sinkhorn_iters, ctx.eps, ctx.grad_sink, ctx.ready_hook = sinkhorn_iters, eps, grad_sink, ready_hook
         ctx.accumulate = bool(accumulate) and grad_sink is not None
+        ctx.ready_event = ready_event
         ctx.mark_non_differentiable(H_pre, H_res)
         ctx.set_materialize_grads(False)   # no zero-filled gradients for outputs nobody used
         return branch_input, H_residual, H_post, H_pre, H_res
@@ -196,16 +199,17 @@ class _HyperConnectionMix(torch.autograd.Function):
             dH_post = torch.zeros(B, 4, device=H.device, dtype=torch.float32)
         dH, gphi, gbias, galpha = hc_mix_backward(
             d_branch_input, dH_residual, dH_post, H, x, phi, pre_b, post_b, res_b, alpha_pre, alpha_post, alpha_res,
-            saved, H_pre, H_res, ctx.sinkhorn_iters, ctx.eps, param_grads=ctx.grad_sink, accumulate=ctx.accumulate)
+            saved, H_pre, H_res, ctx.sinkhorn_iters, ctx.eps, param_grads=ctx.grad_sink, accumulate=ctx.accumulate,
+            ready_event=ctx.ready_event)
         if ctx.ready_hook is not None:
             ctx.ready_hook(ctx.grad_sink)
         if ctx.grad_sink is not None:  # the parameters' .grad tensors are views of the sink already
-            return (dH,) + (None,) * 14
+            return (dH,) + (None,) * 15
         return (dH, gbias[0:4].reshape(pre_b.shape).to(pre_b.dtype), gbias[4:8].reshape(post_b.shape).to(post_b.dtype),
                 gbias[8:24].reshape(res_b.shape).to(res_b.dtype), gphi.to(phi.dtype),
                 galpha[0:1].reshape_as(alpha_pre).to(alpha_pre.dtype),
                 galpha[1:2].reshape_as(alpha_post).to(alpha_post.dtype),
-                galpha[2:3].reshape_as(alpha_res).to(alpha_res.dtype), None, None, None, None, None, None, None)
+                galpha[2:3].reshape_as(alpha_res).to(alpha_res.dtype), None, None, None, None, None, None, None, None)
 
 
 @torch.compiler.disable
@@ -284,7 +288,7 @@ def sequence_mean_pool(H: torch.Tensor) -> torch.Tensor:
 @torch.compiler.disable
 def hyper_connection_mix(H, H_pre_base, H_post_base, H_res_base, phi, alpha_pre, alpha_post, alpha_res,
                          sinkhorn_iters: int = 20, eps: float = 1e-6, grad_sink=None, ready_hook=None,
-                         accumulate: bool = False, pooled=None, lazy_residual: bool = False):
+                         accumulate: bool = False, pooled=None, lazy_residual: bool = False, ready_event=None):
     """Fused pooled-weights + stream-mix node; returns
     (branch_input, H_residual, H_post, H_pre, H_res); the last two carry no gradient.
     With `grad_sink` the parameter gradients are written into that flat buffer and no
@@ -292,6 +296,9 @@ def hyper_connection_mix(H, H_pre_base, H_post_base, H_res_base, phi, alpha_pre,
     the kernels that fill it have been launched; `accumulate` adds to the buffer instead of
     overwriting it; `pooled` are token sums of H from the previous layer (see fused_add_residual).
     With lazy_residual=True the second output is a storage-less stand-in to be passed to
-    add_residual_from_state, which recomputes the residual mix from H."""
+    add_residual_from_state, which recomputes the residual mix from H.  `ready_event`: a
+    torch.cuda.Event the backward records once the parameter gradients are complete in stream
+    order (before dH is)."""
     return _HyperConnectionMix.apply(H, H_pre_base, H_post_base, H_res_base, phi, alpha_pre, alpha_post, alpha_res,
-                                     sinkhorn_iters, eps, grad_sink, ready_hook, accumulate, pooled, lazy_residual)
+                                     sinkhorn_iters, eps, grad_sink, ready_hook, accumulate, pooled, lazy_residual,
+                                     ready_event)

@@ -41,8 +41,15 @@ class GradSync:
     `finish()` makes the current stream wait for the all-reduces.  Typical step:
 
         sync = GradSync(layers)            # once
+        opt.zero_grad()                    # any form: see below
         loss.backward()                    # all-reduces start inside the backward
         sync.finish()                      # before the optimizer reads .grad
+        opt.step()
+
+    `zero_grad(set_to_none=True)` (torch's default) drops the views; the backward of each layer
+    and `finish()` bind them again (`attach()`), so the optimizer always finds the freshly written
+    record in `.grad`.  `zero_grad(set_to_none=False)` merely zeroes a record the next backward
+    overwrites.
     """
 
     def __init__(self, layers: Iterable[torch.nn.Module], process_group=None, overlap: bool = True,
@@ -63,6 +70,7 @@ class GradSync:
             sizes.append(sink_numel(l.dim))
         self.flat = torch.zeros(sum(sizes), device=dev, dtype=torch.float32)
         self.records = []
+        self._views = {}     # record address -> [(parameter, its view of the record)]
         off = 0
         for l, n in zip(self.layers, sizes):
             rec = self.flat[off:off + n]
@@ -70,27 +78,54 @@ class GradSync:
             K24 = 4 * l.dim * 24
             l.grad_sink = rec
             l.grads_ready_hook = self._on_layer_ready
-            l.phi.grad = rec[:K24].view(4 * l.dim, 24)
-            l.H_pre_base.grad = rec[K24:K24 + 4]
-            l.H_post_base.grad = rec[K24 + 4:K24 + 8]
-            l.H_res_base.grad = rec[K24 + 8:K24 + 24].view(4, 4)
-            l.alpha_pre.grad = rec[K24 + 24:K24 + 25]
-            l.alpha_post.grad = rec[K24 + 25:K24 + 26]
-            l.alpha_res.grad = rec[K24 + 26:K24 + 27]
+            self._views[rec.data_ptr()] = [
+                (l.phi, rec[:K24].view(4 * l.dim, 24)),
+                (l.H_pre_base, rec[K24:K24 + 4]),
+                (l.H_post_base, rec[K24 + 4:K24 + 8]),
+                (l.H_res_base, rec[K24 + 8:K24 + 24].view(4, 4)),
+                (l.alpha_pre, rec[K24 + 24:K24 + 25]),
+                (l.alpha_post, rec[K24 + 25:K24 + 26]),
+                (l.alpha_res, rec[K24 + 26:K24 + 27]),
+            ]
             self.records.append(rec)
+        self.attach()
         if check_ranks and self._distributed():
             self._check_same_layout(sizes)
         self.overlap = overlap and dev.type == "cuda"
         self.side = torch.cuda.Stream(device=dev) if self.overlap else None
         self._pending = []
+        # One event per layer, recorded by the layer's backward between the kernels that complete the
+        # record and the pass that writes dH: the collective on the side stream waits for it and so
+        # runs beside that pass.  (Recorded once here so that it owns a CUDA event.)
+        self._events = {}
+        if self.overlap and self._distributed():
+            with torch.cuda.device(dev):
+                for l, rec in zip(self.layers, self.records):
+                    ev = torch.cuda.Event()
+                    ev.record()
+                    self._events[rec.data_ptr()] = ev
+                    l.grads_ready_event = ev
+
+    def attach(self, rec: Optional[torch.Tensor] = None) -> None:
+        """Make .grad of every parameter (of the layer owning `rec`, or of all layers) the view of the
+        flat record again.  Needed after anything that replaced or dropped .grad, e.g.
+        `optimizer.zero_grad()` with set_to_none=True; the backward and `finish()` call it."""
+        groups = self._views.values() if rec is None else (self._views[rec.data_ptr()],)
+        for views in groups:
+            for p, v in views:
+                if p.grad is not v:
+                    p.grad = v
 
     # -- called from the backward of a layer, right after its weight-gradient kernels were launched
     def _on_layer_ready(self, rec: torch.Tensor) -> None:
+        self.attach(rec)
         if not self._distributed():
             return
         if self.overlap:
-            ev = torch.cuda.Event()
-            ev.record()
+            ev = self._events.get(rec.data_ptr())
+            if ev is None:       # no event of the layer's own: order after everything launched so far
+                ev = torch.cuda.Event()
+                ev.record()
             self.side.wait_event(ev)
             with torch.cuda.stream(self.side):
                 dist.all_reduce(rec, op=dist.ReduceOp.SUM, group=self.group)
@@ -114,7 +149,9 @@ class GradSync:
         return dist.is_available() and dist.is_initialized() and dist.get_world_size(self.group) > 1
 
     def finish(self) -> None:
-        """Order everything after the collectives started during the backward."""
+        """Order everything after the collectives started during the backward, and make sure the
+        parameters' .grad are the views of the record."""
+        self.attach()
         for ev in self._pending:
             torch.cuda.current_stream().wait_event(ev)
         self._pending.clear()
@@ -123,6 +160,37 @@ class GradSync:
         """One collective over the whole flat buffer (for callers that do not use the hooks)."""
         if self._distributed():
             dist.all_reduce(self.flat, op=dist.ReduceOp.SUM, group=self.group)
+
+    def all_reduce_async(self) -> None:
+        """One collective over the whole flat buffer on the side stream, after everything launched so
+        far on the current stream; `finish()` (or `wait_reduced()`) orders later work after it.  For
+        steps replayed from CUDA graphs, which keep collectives out of the graph: replay, call this,
+        and wait only where the reduced gradients are used or the record is written again."""
+        if not self._distributed():
+            return
+        if not self.overlap:
+            return self.all_reduce_now()
+        ev = torch.cuda.Event()
+        ev.record()
+        self.side.wait_event(ev)
+        with torch.cuda.stream(self.side):
+            dist.all_reduce(self.flat, op=dist.ReduceOp.SUM, group=self.group)
+            done = torch.cuda.Event()
+            done.record()
+        self._pending.append(done)
+
+    def wait_reduced(self) -> None:
+        """Make the current stream wait for the collectives started so far (no re-binding of .grad)."""
+        for ev in self._pending:
+            torch.cuda.current_stream().wait_event(ev)
+        self._pending.clear()
+
+    def set_hooks(self, enabled: bool) -> None:
+        """Enable or disable the in-backward start of the collectives (disable while capturing the
+        step into a CUDA graph: collectives stay outside the graph, see all_reduce_async)."""
+        for l, rec in zip(self.layers, self.records):
+            l.grads_ready_hook = self._on_layer_ready if enabled else None
+            l.grads_ready_event = self._events.get(rec.data_ptr()) if enabled else None
 
     def zero(self) -> None:
         self.flat.zero_()

@@ -3,33 +3,29 @@ against the unsharded CPU oracle, the sequence-sharded wrapper, and the layer un
 (`fully_shard`) against the same block run unsharded.  Skipped on boxes with fewer than two GPUs."""
 
 import copy
-
+import datetime
 import os
-import socket
 
 import pytest
 import torch
 import torch.distributed as dist
-import torch.multiprocessing as mp
 
 from oracle import mhc_oracle as O
 from tests import cases
-from tests.util import to_module
+from tests.util import run_ranks, to_module
 
 pytestmark = pytest.mark.gpu
 
-
-def _free_port():
-    with socket.socket() as s:
-        s.bind(("127.0.0.1", 0))
-        return s.getsockname()[1]
+# A rank whose peer failed before a collective gives up after this long instead of sitting in an
+# NCCL kernel until the default watchdog limit.
+_PG_TIMEOUT = datetime.timedelta(seconds=90)
 
 
 def _worker(rank, world, port, q):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev, timeout=_PG_TIMEOUT)
     try:
         import mhc
         from mhc.parallel import GradSync, shard_batch
@@ -69,7 +65,7 @@ def _seq_worker(rank, world, port, q):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev, timeout=_PG_TIMEOUT)
     try:
         import mhc
         from mhc.parallel import SequenceShardedHyperConnection
@@ -101,6 +97,52 @@ def _seq_worker(rank, world, port, q):
         dist.destroy_process_group()
 
 
+def _adam_worker(rank, world, port, q):
+    """Three Adam steps with the stock `opt.zero_grad()` (set_to_none=True) under GradSync on a batch
+    shard per rank equal three Adam steps of the same layer on the whole batch without GradSync."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev, timeout=_PG_TIMEOUT)
+    try:
+        import mhc
+        from mhc.parallel import GradSync, shard_batch
+        torch.manual_seed(3)
+        B, S, D = 4, 96, 64
+        H = torch.randn(B, S, 4, D)
+        g = torch.randn(B, S, 4, D)
+        p = cases.perturb_params_(O.default_params(D, 0, 0.1), 9)
+        layer = to_module(mhc.HyperConnection(dim=D), p).to(dev)
+        ref = copy.deepcopy(layer)
+        sync = GradSync([layer])
+        opt = torch.optim.Adam(layer.parameters(), lr=1e-2)
+        ref_opt = torch.optim.Adam(ref.parameters(), lr=1e-2)
+        Hs, gs = shard_batch(H, rank, world).to(dev), shard_batch(g, rank, world).to(dev)
+        Hf, gf = H.to(dev), g.to(dev)
+        start = layer.phi.detach().clone()
+        for _ in range(3):
+            opt.zero_grad()
+            assert layer.phi.grad is None
+            bi, add = layer(Hs)
+            add(bi).backward(gs)
+            sync.finish()
+            assert layer.phi.grad is not None
+            opt.step()
+            ref_opt.zero_grad()
+            bi, add = ref(Hf)
+            add(bi).backward(gf)
+            ref_opt.step()
+        torch.cuda.synchronize()
+        assert (layer.phi - start).abs().max() > 1e-3
+        for (name, a), (_, b) in zip(layer.named_parameters(), ref.named_parameters()):
+            assert (a - b).abs().max() <= 1e-4 * (1 + b.abs().max()), name
+        q.put((rank, "ok"))
+    except Exception as e:
+        q.put((rank, f"{type(e).__name__}: {e}"))
+    finally:
+        dist.destroy_process_group()
+
+
 class _Block(torch.nn.Module):
     """A residual block around the layer: H_new = add_residual(tanh(Linear(branch_input)))."""
 
@@ -118,7 +160,7 @@ def _fsdp_worker(rank, world, port, q):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev, timeout=_PG_TIMEOUT)
     try:
         import mhc
         from mhc.parallel import shard_batch
@@ -160,16 +202,8 @@ def _fsdp_worker(rank, world, port, q):
 def _spawn2(worker):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
-    ctx = mp.get_context("spawn")
-    q = ctx.Queue()
-    port = _free_port()
-    procs = [ctx.Process(target=worker, args=(r, 2, port, q)) for r in range(2)]
-    for pr in procs:
-        pr.start()
-    results = [q.get(timeout=300) for _ in procs]
-    for pr in procs:
-        pr.join(timeout=60)
-    assert sorted(results) == [(0, "ok"), (1, "ok")], results
+    results = run_ranks(worker, 2, timeout=300)
+    assert results == [(0, "ok"), (1, "ok")], results
 
 
 def test_two_gpu_fsdp2_block_matches_unsharded():
@@ -181,15 +215,8 @@ def test_two_gpu_sequence_sharded_layer_matches_oracle():
 
 
 def test_two_gpu_sharded_layer_matches_oracle():
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
-    ctx = mp.get_context("spawn")
-    q = ctx.Queue()
-    port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
-    for pr in procs:
-        pr.start()
-    results = [q.get(timeout=300) for _ in procs]
-    for pr in procs:
-        pr.join(timeout=60)
-    assert sorted(results) == [(0, "ok"), (1, "ok")], results
+    _spawn2(_worker)
+
+
+def test_two_gpu_adam_steps_with_stock_zero_grad():
+    _spawn2(_adam_worker)

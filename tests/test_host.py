@@ -26,7 +26,7 @@ def test_library_exports_every_declared_symbol():
     for n in names:
         assert hasattr(lib, n), n
     assert sorted(_lib.EXPORTS) == names
-    assert lib.mhc_version() == 100
+    assert lib.mhc_version() == 200
 
 
 def test_status_codes_without_gpu():
@@ -39,10 +39,16 @@ def test_status_codes_without_gpu():
     assert lib.mhc_sinkhorn_fwd(None, None, 0, _lib.MHC_F32, 20, 1e-8, None) == 0      # empty batch is a no-op
     assert lib.mhc_stream_mix_fwd(None, None, None, None, None, 2, 8, 16, 7, None) == 3  # unknown dtype
     assert lib.mhc_stream_mix_fwd(None, None, None, None, None, -1, 8, 16, 0, None) == 2
+    # Scalar arguments are checked before pointers, so these cases pass null pointers throughout: even
+    # if the check aimed at regressed, the null-pointer check behind it would still stop any launch.
+    assert lib.mhc_add_residual_bwd(None, None, None, None, None, None, 8, None, 2, 64, 64, 0, None) == 5  # scratch too small
+    assert lib.mhc_sinkhorn_bwd(None, None, None, 1, 0, 20, 1e-8, 9, None) == 4
+    assert lib.mhc_add_residual_bwd(None, None, None, None, None, None, 1 << 30, None, 2, 64, 64, 0, None) == 1
+    # a ticket pointer that is not 4-byte aligned is refused (host addresses; nothing is launched)
     buf = ctypes.create_string_buffer(64)
-    p = ctypes.addressof(buf)
-    assert lib.mhc_add_residual_bwd(p, p, p, p, p, p, 8, 2, 64, 64, 0, None) == 5          # scratch too small
-    assert lib.mhc_sinkhorn_bwd(p, p, p, 1, 0, 20, 1e-8, 9, None) == 4
+    p = (ctypes.addressof(buf) + 15) & ~15
+    assert lib.mhc_add_residual_bwd(p, p, p, p, p, p, 1 << 30, p + 2, 2, 64, 64, 0, None) == 6
+    assert lib.mhc_status_name(6) == b"MHC_ERR_MISALIGNED"
     with pytest.raises(_lib.MhcError):
         _lib.check(5)
 

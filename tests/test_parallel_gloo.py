@@ -7,21 +7,14 @@ gradients must equal the corresponding slices of the unsharded run.
 """
 
 import os
-import socket
 
 import pytest
 import torch
 import torch.distributed as dist
-import torch.multiprocessing as mp
 
 from oracle import mhc_oracle as O
 from tests import cases
-
-
-def _free_port():
-    with socket.socket() as s:
-        s.bind(("127.0.0.1", 0))
-        return s.getsockname()[1]
+from tests.util import run_ranks
 
 
 def _fill_record(layer, grads):
@@ -76,16 +69,61 @@ def _worker(rank, world, port, B, use_hook, q):
 
 @pytest.mark.parametrize("B,use_hook", [(4, False), (5, True)])
 def test_two_rank_gradient_allreduce(B, use_hook):
-    ctx = mp.get_context("spawn")
-    q = ctx.Queue()
-    port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, B, use_hook, q)) for r in range(2)]
-    for pr in procs:
-        pr.start()
-    results = [q.get(timeout=120) for _ in procs]
-    for pr in procs:
-        pr.join(timeout=60)
-    assert sorted(results) == [(0, "ok"), (1, "ok")], results
+    results = run_ranks(_worker, 2, B, use_hook, timeout=120)
+    assert results == [(0, "ok"), (1, "ok")], results
+
+
+def _params_of(layer):
+    """The layer's current parameters as oracle LayerParams (detached copies)."""
+    return O.LayerParams(**{k: v.detach().clone() for k, v in layer.named_parameters()})
+
+
+def _optimizer_worker(rank, world, port, q):
+    """Three Adam steps with the stock `opt.zero_grad()` (which sets every .grad to None) under GradSync
+    must move the parameters exactly as three Adam steps on the unsharded gradients do."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import copy
+        import mhc
+        from mhc.parallel import GradSync, shard_batch
+        from tests.util import to_module
+        torch.manual_seed(0)
+        B, S, D = 4, 16, 16
+        H = torch.randn(B, S, 4, D)
+        g = torch.randn(B, S, 4, D)
+        layer = to_module(mhc.HyperConnection(dim=D), cases.perturb_params_(O.default_params(D, 0, 0.1), 7))
+        ref = copy.deepcopy(layer)
+        sync = GradSync([layer])
+        opt = torch.optim.Adam(layer.parameters(), lr=1e-2)
+        ref_opt = torch.optim.Adam(ref.parameters(), lr=1e-2)
+        Hs, gs = shard_batch(H, rank, world), shard_batch(g, rank, world)
+        start = layer.phi.detach().clone()
+        for _ in range(3):
+            opt.zero_grad()
+            assert layer.phi.grad is None                       # this is what the stock call does
+            mine = O.layer_fwd_bwd(_params_of(layer), Hs, gs, None, "fused")
+            _fill_record(layer, mine)                           # what the CUDA backward does on a GPU
+            layer.grads_ready_hook(layer.grad_sink)
+            sync.finish()
+            assert layer.phi.grad is not None and layer.phi.grad.data_ptr() == sync.flat.data_ptr()
+            opt.step()
+            full = O.layer_fwd_bwd(_params_of(ref), H, g, None, "fused")
+            for name, q_ in ref.named_parameters():
+                q_.grad = full["d" + name].clone()
+            ref_opt.step()
+        assert (layer.phi - start).abs().max() > 1e-3           # the optimizer did move the parameters
+        for (name, a), (_, b) in zip(layer.named_parameters(), ref.named_parameters()):
+            assert (a - b).abs().max() <= 1e-4 * (1 + b.abs().max()), name
+        q.put((rank, "ok"))
+    except Exception as e:
+        q.put((rank, f"{type(e).__name__}: {e}"))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_three_adam_steps_with_stock_zero_grad():
+    assert run_ranks(_optimizer_worker, 2, timeout=120) == [(0, "ok"), (1, "ok")]
 
 
 def test_shard_batch_covers_batch_once():
@@ -131,13 +169,5 @@ def _mismatch_worker(rank, world, port, q):
 def test_mismatched_layers_are_reported_on_every_rank():
     """A configuration fault injected on the host: ranks built with different layer widths.  The
     check runs before any collective on gradients, so nothing hangs and every rank raises."""
-    ctx = mp.get_context("spawn")
-    q = ctx.Queue()
-    port = _free_port()
-    procs = [ctx.Process(target=_mismatch_worker, args=(r, 2, port, q)) for r in range(2)]
-    for pr in procs:
-        pr.start()
-    results = [q.get(timeout=120) for _ in procs]
-    for pr in procs:
-        pr.join(timeout=60)
-    assert sorted(results) == [(0, "ValueError"), (1, "ValueError")], results
+    results = run_ranks(_mismatch_worker, 2, timeout=120)
+    assert results == [(0, "ValueError"), (1, "ValueError")], results

@@ -24,7 +24,7 @@ def _both(lib, L, g, bo, H_post):
     nbytes = lib.mhc_scratch_bytes(L.OP_ADD_RESIDUAL_BWD, B, S, D, code)
     scratch = torch.empty(nbytes // 4 + 1, device=g.device)
     L.check(lib.mhc_add_residual_bwd(g.data_ptr(), bo.data_ptr(), H_post.data_ptr(), ref_dbo.data_ptr(),
-                                     ref_post.data_ptr(), scratch.data_ptr(), nbytes, B, S, D, code, st))
+                                     ref_post.data_ptr(), scratch.data_ptr(), nbytes, None, B, S, D, code, st))
     new_dbo, new_post = torch.full_like(bo, float("nan")), torch.full((B, 4), float("nan"), device=g.device)
     L.check(lib.mhc_add_residual_bwd_noalloc(g.data_ptr(), bo.data_ptr(), H_post.data_ptr(), new_dbo.data_ptr(),
                                              new_post.data_ptr(), B, S, D, code, st))
@@ -57,8 +57,8 @@ def test_noalloc_rejects_oversized_shapes():
     lib = L.load()
     cap = lib.mhc_add_residual_bwd_noalloc_max_bytes()
     assert cap == 1 << 20
-    B, S, D = 64, 65536, 8192          # partial sums far beyond the built-in area; no kernel is launched
-    t = torch.zeros(16, device="cuda")
-    rc = lib.mhc_add_residual_bwd_noalloc(t.data_ptr(), t.data_ptr(), t.data_ptr(), t.data_ptr(), t.data_ptr(),
-                                          B, S, D, L.MHC_BF16, None)
+    # Partial sums far beyond the built-in area.  The size check comes before the pointer checks, so the
+    # call is made with null pointers: nothing could be launched even if the size check were lost.
+    B, S, D = 64, 65536, 8192
+    rc = lib.mhc_add_residual_bwd_noalloc(None, None, None, None, None, B, S, D, L.MHC_BF16, None)
     assert rc == 5 and b"built-in area" in lib.mhc_last_error_string()
