@@ -15,7 +15,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "mhc", "libmhc_b200.so")
-SOURCES = ["api.cu", "sinkhorn.cu", "stream.cu", "weights.cu", "weights_rows.cu", "fused.cu", "noalloc.cu"]
+SOURCES = ["api.cu", "sinkhorn.cu", "stream.cu", "weights.cu", "weights_rows.cu", "weights_rows_tc.cu", "fused.cu", "noalloc.cu"]
 HEADERS = ["common.cuh", "launch.h", os.path.join("..", "..", "include", "mhc_b200.h")]
 
 
@@ -38,8 +38,7 @@ def build(force=False, verbose=False, defines=(), out=OUT):
     if not force and out == OUT and up_to_date():
         return OUT
     cmd = [nvcc_path(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-           "--use_fast_math=false", "-shared", "-Xcompiler", "-fPIC", "-cudart", "static"]
-    cmd = [c for c in cmd if c != "--use_fast_math=false"]
+           "-shared", "-Xcompiler", "-fPIC", "-cudart", "static"]
     if verbose:
         cmd += ["-Xptxas", "-v"]
     cmd += [f"-D{d}" for d in defines]

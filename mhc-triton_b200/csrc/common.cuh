@@ -324,6 +324,13 @@ __device__ __forceinline__ double warp_sum_f64(double v) {
 __device__ __forceinline__ double sum_strided_f64(const float* __restrict__ p, int64_t stride, int n) {
   double t[4] = {0.0, 0.0, 0.0, 0.0};
   int c = 0;
+  for (; c + 16 <= n; c += 16) {   // sixteen loads in flight; same chains, same order as the 4-wide loop below
+    float v[16];
+#pragma unroll
+    for (int u = 0; u < 16; ++u) v[u] = __ldg(p + (int64_t)(c + u) * stride);
+#pragma unroll
+    for (int u = 0; u < 16; ++u) t[u & 3] += (double)v[u];
+  }
   for (; c + 4 <= n; c += 4) {
 #pragma unroll
     for (int u = 0; u < 4; ++u) t[u] += (double)__ldg(p + (int64_t)(c + u) * stride);
@@ -381,6 +388,55 @@ __device__ __forceinline__ bool cta_arrives_last(int* ticket, int expected) {
   const bool last = s_last != 0;
   if (last) __threadfence();
   return last;
+}
+
+// The same sums in the same order (thread t adds rows t, t + 256, ... one after the other in fp64)
+// for a compile-time W that is a multiple of 4: rows are read as 16-byte vectors, several rows of
+// loads in flight before the first add (two rows of 20 or eight rows of 4), which is what bounds the single CTA that finishes a batch
+// element's partial sums while the rest of the GPU waits.  Falls back to 4-byte loads when the
+// array is not 16-byte aligned.
+template <int W, bool FRESH>
+__device__ __forceinline__ void block_column_sums_fast(const float* __restrict__ p, int64_t slots, double (*sm)[20]) {
+  static_assert(W % 4 == 0 && W <= 20, "row width");
+  double a[W];
+#pragma unroll
+  for (int j = 0; j < W; ++j) a[j] = 0.0;
+  const bool vec = (reinterpret_cast<uintptr_t>(p) & 15u) == 0;   // row pitch W * 4 bytes is a multiple of 16
+  constexpr int kRows = W > 8 ? 2 : 8;   // rows in flight per thread: 40 or 32 values
+  for (int64_t s0 = threadIdx.x; s0 < slots; s0 += 256 * kRows) {
+    float v[kRows][W];
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) {
+      const int64_t s = s0 + (int64_t)r * 256;
+      if (s < slots) {
+        const float* q = p + s * W;
+        if (vec) {
+#pragma unroll
+          for (int j = 0; j < W; j += 4) {
+            const float4 t = FRESH ? __ldcg(reinterpret_cast<const float4*>(q + j))
+                                   : __ldg(reinterpret_cast<const float4*>(q + j));
+            v[r][j] = t.x; v[r][j + 1] = t.y; v[r][j + 2] = t.z; v[r][j + 3] = t.w;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < W; ++j) v[r][j] = FRESH ? __ldcg(q + j) : __ldg(q + j);
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < kRows; ++r)
+      if (s0 + (int64_t)r * 256 < slots) {
+#pragma unroll
+        for (int j = 0; j < W; ++j) a[j] += (double)v[r][j];
+      }
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll
+  for (int j = 0; j < W; ++j) {
+    const double t = warp_sum_f64(a[j]);
+    if (lane == 0) sm[warp][j] = t;
+  }
+  __syncthreads();
 }
 
 // ---------------------------------------------------------------------------------------

@@ -25,7 +25,8 @@ inline bool is_aligned_to(const void* p, unsigned n) { return (reinterpret_cast<
 //   kind  : Stream = no partial sums (short chunks), Reduce = leaves per-CTA partial sums,
 //           Pool = the mean-pool kernel (long chunks, sub-groups inside the CTA)
 enum class GeoKind { Stream, Reduce, Pool };
-Geo make_geo(int64_t S, int64_t D, int vec, GeoKind kind, int tpc);
+Geo make_geo(int64_t S, int64_t D, int vec, GeoKind kind, int tpc, int occ = 0);
+int sm_count();
 inline int geo_block(const Geo& g) { return g.cols * g.sub; }
 inline int64_t geo_slots(const Geo& g) { return (int64_t)g.nchunk * g.CG; }  // partial rows per batch element
 
@@ -100,6 +101,13 @@ int project_rows_launch(const float* x, const float* phi, float* part, int64_t b
                         cudaStream_t st, int* ks_used);
 int bwd_rows_launch(const float* x, const float* phi, const float* buf, float* phi_part, float* grad_x, float* grad_phi,
                     float* grad_bias, float* grad_alpha, int64_t batch, int64_t K, int accumulate, cudaStream_t st);
+
+// Tensor-core (tcgen05) kernels for many rows (weights_rows_tc.cu).
+int64_t rows_tc_fwd_scratch_bytes(int64_t K);
+bool rows_tc_usable(const float* x, int64_t batch, int64_t K);
+int rows_fwd_tc_launch(const float* x, const float* phi, BiasPtrs bias, const float* alpha_pre, const float* alpha_post,
+                       const float* alpha_res, float* H_pre, float* H_post, float* H_res, float* saved, void* scratch,
+                       int64_t batch, int64_t K, int iters, float eps, cudaStream_t st);
 
 int64_t weights_fwd_scratch_bytes(int64_t batch, int64_t K);
 int64_t weights_bwd_scratch_bytes(int64_t batch, int64_t K);

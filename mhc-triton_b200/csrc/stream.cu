@@ -37,14 +37,20 @@ namespace mhc {
 #ifndef MHC_APPLY_MINB
 #define MHC_APPLY_MINB 3
 #endif
+// Mean-pool: tokens per CTA (adjusted to fill whole waves, see wave_tpc), packs along D per CTA (the CTA
+// has 4 x MHC_POOL_COLS threads, one per stream row and pack), loads in flight per thread, and
+// the resident CTAs per SM the chunking is sized for.
 #ifndef MHC_POOL_TPC
-#define MHC_POOL_TPC 256
+#define MHC_POOL_TPC 112
 #endif
 #ifndef MHC_POOL_COLS
-#define MHC_POOL_COLS 64
+#define MHC_POOL_COLS 32
 #endif
-#ifndef MHC_POOL_THREADS
-#define MHC_POOL_THREADS 256
+#ifndef MHC_POOL_DEPTH
+#define MHC_POOL_DEPTH 8
+#endif
+#ifndef MHC_POOL_OCC
+#define MHC_POOL_OCC 7
 #endif
 // Walking direction per kernel (bit set = from the end of the tensor to its start): bit 0 mean-pool,
 // 1 stream mix, 2 add residual, 3 add-residual backward, 4 stream-mix backward reduce / full,
@@ -71,6 +77,10 @@ namespace mhc {
 #endif
 #ifndef MHC_TPC_MIXBWD
 #define MHC_TPC_MIXBWD 8
+#endif
+// Resident CTAs per SM of the add-residual backward (80 registers x 256 threads), for wave_tpc.
+#ifndef MHC_ADDBWD_OCC
+#define MHC_ADDBWD_OCC 3
 #endif
 
 template <typename T, int V, int N> struct Bundle { RawPack<T, V> p[N]; };
@@ -386,7 +396,9 @@ k_add_residual_mix_fwd(const T* __restrict__ H, const float* __restrict__ Hres, 
 __device__ __forceinline__ void finish_partials(const float* __restrict__ part, int64_t b, int64_t slots, int W, int W0,
                                                 float* __restrict__ out0, float* __restrict__ out1,
                                                 double (*sm)[20]) {
-  block_column_sums_f64<true>(part + b * slots * W, slots, W, sm);
+  if (W == 20) block_column_sums_fast<20, true>(part + b * slots * W, slots, sm);
+  else if (W == 4) block_column_sums_fast<4, true>(part + b * slots * W, slots, sm);
+  else block_column_sums_f64<true>(part + b * slots * W, slots, W, sm);
   const int j = threadIdx.x;
   if (j < W) {
     double t = 0.0;
@@ -577,77 +589,41 @@ k_stream_mix_bwd_apply(const T* __restrict__ dbi, const T* __restrict__ dHr, con
 }
 
 // --------------------------------------------------------------------------------- mean-pool
-// part[b, chunk, n*D + d] = sum over the chunk's tokens of H[b,s,n,d]  (fp32).
-// blockDim.x = cols * sub: thread (col, j) sums tokens j, j+sub, ... of the chunk (two tokens in
-// flight); the sub-groups are then added in index order through shared memory.
+// part[b, chunk, n*D + d] = sum over the chunk's tokens of H[b,s,n,d]  (fp32, tokens in index order).
+// blockDim.x = 4 * cols: thread (n, c) owns one 16-byte pack of stream row n and walks all tokens of
+// the chunk with MHC_POOL_DEPTH loads in flight.  One pack per thread keeps the state small (V
+// accumulators), so many CTAs fit an SM and a single sequence still fills the machine.
 template <typename T, int V>
-__global__ void __launch_bounds__(MHC_POOL_THREADS)
+__global__ void __launch_bounds__(4 * MHC_POOL_COLS)
 k_meanpool_partial(const T* __restrict__ H, float* __restrict__ part, Geo g) {
   pdl_prologue();
-  extern __shared__ float sm[];  // [2*V][sub][cols]
-  const Item it = decode_item(g);
-  const int64_t D = g.D, c0 = (int64_t)it.col * V, tok = it.b * g.S;
-  float acc[4][V];
+  const Item it = decode_item(g);   // it.col = pack along D, it.sub = stream row n
+  if (it.col >= g.DV) return;
+  const int64_t D = g.D, c0 = (int64_t)it.col * V;
+  const T* h = H + (it.b * g.S * 4 + it.sub) * D + c0;
+  float acc[V];
 #pragma unroll
-  for (int n = 0; n < 4; ++n)
+  for (int e = 0; e < V; ++e) acc[e] = 0.f;
+  constexpr int kDepth = MHC_POOL_DEPTH;
+  for (int64_t s = it.s0; s < it.s1; s += kDepth) {
+    RawPack<T, V> r[kDepth];
 #pragma unroll
-    for (int e = 0; e < V; ++e) acc[n][e] = 0.f;
-  const bool live = it.col < g.DV;
-  if (live) {
-    using B8 = Bundle<T, V, 8>;  // two tokens per pipeline stage
-    const int64_t step = g.sub;
-    for_tokens_pipelined<B8>(
-        it.s0 + it.sub, it.s1, 2 * step,
-        [&](B8& u, int64_t s) {
-          const T* h = H + (tok + s) * 4 * D + c0;
+    for (int u = 0; u < kDepth; ++u)
+      if (s + u < it.s1) r[u] = ld_raw<T, V>(h + (s + u) * 4 * D);
 #pragma unroll
-          for (int n = 0; n < 4; ++n) u.p[n] = ld_raw<T, V>(h + n * D);
-          if (s + step < it.s1) {
+    for (int u = 0; u < kDepth; ++u)
+      if (s + u < it.s1) {
 #pragma unroll
-            for (int n = 0; n < 4; ++n) u.p[4 + n] = ld_raw<T, V>(h + step * 4 * D + n * D);
-          }
-        },
-        [&](const B8& u, int64_t s) {
-#pragma unroll
-          for (int n = 0; n < 4; ++n)
-#pragma unroll
-            for (int e = 0; e < V; ++e) acc[n][e] += raw_get<V>(u.p[n], e);
-          if (s + step < it.s1) {
-#pragma unroll
-            for (int n = 0; n < 4; ++n)
-#pragma unroll
-              for (int e = 0; e < V; ++e) acc[n][e] += raw_get<V>(u.p[4 + n], e);
-          }
-        });
-  }
-  const int c = threadIdx.x % g.cols;
-  if (g.sub > 1) {  // add the sub-groups in index order, two stream rows at a time (halves the shared memory)
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      if (half) __syncthreads();
-#pragma unroll
-      for (int n = 0; n < 2; ++n)
-#pragma unroll
-        for (int e = 0; e < V; ++e) sm[((n * V + e) * g.sub + it.sub) * g.cols + c] = acc[2 * half + n][e];
-      __syncthreads();
-      if (it.sub == 0) {
-#pragma unroll
-        for (int n = 0; n < 2; ++n)
-#pragma unroll
-          for (int e = 0; e < V; ++e) {
-            float t = acc[2 * half + n][e];
-            for (int j = 1; j < g.sub; ++j) t += sm[((n * V + e) * g.sub + j) * g.cols + c];
-            acc[2 * half + n][e] = t;
-          }
+        for (int e = 0; e < V; ++e) acc[e] += raw_get<V>(r[u], e);
       }
-    }
   }
-  if (live && it.sub == 0) {
-    float* o = part + (it.b * g.nchunk + it.chunk) * 4 * D + c0;
+  float* o = part + (it.b * g.nchunk + it.chunk) * 4 * D + it.sub * D + c0;
+  if constexpr (V % 4 == 0) {
 #pragma unroll
-    for (int n = 0; n < 4; ++n)
+    for (int e = 0; e < V; e += 4) *reinterpret_cast<float4*>(o + e) = make_float4(acc[e], acc[e + 1], acc[e + 2], acc[e + 3]);
+  } else {
 #pragma unroll
-      for (int e = 0; e < V; ++e) o[n * D + e] = acc[n][e];
+    for (int e = 0; e < V; ++e) o[e] = acc[e];
   }
 }
 
@@ -673,7 +649,9 @@ k_reduce_partials(const float* __restrict__ part, int64_t slots, int W, int W0, 
   __shared__ double sm[8][20];
   const int64_t b = blockIdx.x;
   const float* p = part + b * slots * W;
-  block_column_sums_f64(p, slots, W, sm);
+  if (W == 20) block_column_sums_fast<20, false>(p, slots, sm);
+  else if (W == 4) block_column_sums_fast<4, false>(p, slots, sm);
+  else block_column_sums_f64(p, slots, W, sm);
   const int j = threadIdx.x;
   if (j < W) {
     double t = 0.0;
@@ -685,7 +663,54 @@ k_reduce_partials(const float* __restrict__ part, int64_t slots, int W, int W0, 
 }
 
 // -------------------------------------------------------------------------------- host side
-Geo make_geo(int64_t S, int64_t D, int vec, GeoKind kind, int tpc) {
+int sm_count() {
+  static const int n = [] {
+    int dev = 0, v = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) {
+      (void)cudaGetLastError();
+      v = 148;   // no device (size queries on a build machine): the B200 count
+    }
+    return v;
+  }();
+  return n;
+}
+
+// Range of tokens per CTA that wave_tpc may choose from around `base`.
+static inline int tpc_lo(int base) { return base - base / 4 > 1 ? base - base / 4 : 1; }
+static inline int tpc_hi(int base) { return base + base / 4; }
+
+// Tokens per CTA near `base` such that the CTAs of ONE batch element fill whole waves of the
+// device's `occ` resident CTAs per SM.  Every thread of these kernels keeps a fixed number of bytes
+// in flight, so a CTA takes about the same time however many others run beside it, and a last wave
+// that is one-third full costs as much as a full one: with a single sequence per GPU (a batch
+// sharded over many GPUs) that was up to 14 % of a kernel.  Kernels whose CTAs all fit the device
+// at once keep `base`.  The choice depends on S, the column groups and the device, never on the
+// batch, so the partial-sum layout of a batch element is the same whatever batch it is part of.
+// `abreast` = tokens a CTA walks side by side.
+static int wave_tpc(int64_t S, int CG, int abreast, int base, int occ) {
+  if (occ <= 0 || S <= 0) return base;
+  const int64_t slots = (int64_t)sm_count() * occ;
+  auto fill = [&](int t, int64_t* waves_out) {   // share of the slot-time the CTAs use, in 1/1000
+    const int64_t chunks = (S + (int64_t)t * abreast - 1) / ((int64_t)t * abreast);
+    const int64_t items = chunks * CG, waves = (items + slots - 1) / slots;
+    *waves_out = waves;
+    return items * 1000 / (waves * slots);
+  };
+  int64_t waves = 0;
+  int best = base;
+  int64_t best_fill = fill(base, &waves);
+  if (waves <= 1) return base;
+  for (int t = tpc_lo(base); t <= tpc_hi(base); ++t) {
+    const int64_t f = fill(t, &waves);
+    if (f > best_fill + 30 && f > fill(best, &waves)) { best = t; }
+  }
+  return best;
+}
+
+// occ > 0: adjust the tokens per CTA to the device's waves (wave_tpc); occ < 0: the smallest chunk
+// wave_tpc could choose, i.e. an upper bound of the number of chunks (scratch-size queries).
+Geo make_geo(int64_t S, int64_t D, int vec, GeoKind kind, int tpc, int occ) {
   Geo g;
   g.reverse = 0;
   g.S = S;
@@ -698,14 +723,15 @@ Geo make_geo(int64_t S, int64_t D, int vec, GeoKind kind, int tpc) {
   g.cols = cols;
   g.CG = (g.DV + cols - 1) / cols;
   if (pool) {
-    g.sub = MHC_POOL_THREADS / cols;
-    g.tpc = MHC_POOL_TPC;
+    g.sub = 4;   // the four stream rows: blockDim.x = 4 * cols
+    g.tpc = occ < 0 ? tpc_lo(tpc) : wave_tpc(S, g.CG, 1, tpc, occ);
   } else {
-    // Tokens per CTA: a per-kernel constant, so the chunking (and with it the layout of the per-CTA
-    // partial sums) depends on S only, never on the batch size.
+    // Tokens per CTA: a per-kernel constant (adjusted to the device's waves), so the chunking (and
+    // with it the layout of the per-CTA partial sums) depends on S and D only, never on the batch size.
     // Narrow rows (fewer than 256 packs): the CTA keeps 256 threads by walking 256/cols tokens abreast.
     g.sub = MHC_MAX_COLS / cols;
-    g.tpc = tpc * g.sub;
+    const int t = occ < 0 ? tpc_lo(tpc) : wave_tpc(S, g.CG, g.sub, tpc, occ);
+    g.tpc = t * g.sub;
   }
   if (g.tpc > S) g.tpc = (int32_t)(S > 0 ? S : 1);
   g.nchunk = (int32_t)((S + g.tpc - 1) / g.tpc);
@@ -774,20 +800,20 @@ int stream_mix_fwd_impl(const void* H, const float* H_pre, const float* H_res, v
   return check_launch("stream_mix_fwd");
 }
 
-int64_t meanpool_scratch_floats(int64_t B, int64_t S, int64_t D) { return B * make_geo(S, D, 1, GeoKind::Pool, MHC_POOL_TPC).nchunk * 4 * D; }
-int64_t mix_bwd_scratch_floats(int64_t B, int64_t S, int64_t D) { return B * geo_slots(make_geo(S, D, 1, GeoKind::Reduce, MHC_TPC_MIXBWD)) * 20; }
+// Scratch sizes are upper bounds over the pack widths and the chunk lengths a launch may pick.
+int64_t meanpool_scratch_floats(int64_t B, int64_t S, int64_t D) { return B * make_geo(S, D, 1, GeoKind::Pool, MHC_POOL_TPC, -1).nchunk * 4 * D; }
+int64_t mix_bwd_scratch_floats(int64_t B, int64_t S, int64_t D) { return B * geo_slots(make_geo(S, D, 1, GeoKind::Reduce, MHC_TPC_MIXBWD, -1)) * 20; }
 
 int meanpool_partial_impl(const void* H, float* part, int64_t B, int64_t S, int64_t D, int dtype, cudaStream_t st,
                           int* nchunk) {
   const int vec = pick_vec(dtype, D, {H});
-  Geo g = make_geo(S, D, vec, GeoKind::Pool, MHC_POOL_TPC);
+  Geo g = make_geo(S, D, vec, GeoKind::Pool, MHC_POOL_TPC, MHC_POOL_OCC);
   g.reverse = MHC_REV_MASK & 1;
   const int64_t items = B * geo_slots(g);
   if (int e = check_grid("meanpool_fwd", items)) return e;
-  const size_t smem = (size_t)2 * vec * geo_block(g) * sizeof(float);
   {
     ProfScope ps("k_meanpool_partial", st);
-    MHC_DISPATCH(dtype, vec, (launch_k(k_meanpool_partial<T, V>, (unsigned)items, geo_block(g), smem, st, (const T*)H, part, g)));
+    MHC_DISPATCH(dtype, vec, (launch_k(k_meanpool_partial<T, V>, (unsigned)items, geo_block(g), 0, st, (const T*)H, part, g)));
   }
   *nchunk = g.nchunk;
   return check_launch("meanpool_fwd");
@@ -800,7 +826,7 @@ int mix_bwd_partials_impl(int mode, const void* dbi, const void* dHr, const void
                           cudaStream_t st, int64_t* slots, int* tickets, float* dH_pre, float* dH_res) {
   if (!ticket_finish_supported()) tickets = nullptr;
   const int vec = pick_vec(dtype, D, {dbi, dHr, H, dH});
-  Geo g = make_geo(S, D, vec, GeoKind::Reduce, MHC_TPC_MIXBWD);
+  Geo g = make_geo(S, D, vec, GeoKind::Reduce, MHC_TPC_MIXBWD, mode == 0 ? 1 : 512 / MHC_MAX_COLS);
   g.reverse = (MHC_REV_MASK >> 4) & 1;
   *slots = geo_slots(g);
   const int64_t items = B * *slots;
@@ -822,7 +848,7 @@ int mix_bwd_partials_impl(int mode, const void* dbi, const void* dHr, const void
 int mix_bwd_apply_impl(const void* dbi, const void* dHr, const float* H_pre, const float* H_res, const float* gx,
                        float inv_S, void* dH, int64_t B, int64_t S, int64_t D, int dtype, cudaStream_t st) {
   const int vec = pick_vec(dtype, D, {dbi, dHr, dH});
-  Geo g = make_geo(S, D, vec, GeoKind::Stream, MHC_TPC_APPLY);
+  Geo g = make_geo(S, D, vec, GeoKind::Stream, MHC_TPC_APPLY, MHC_APPLY_MINB);
   g.reverse = (MHC_REV_MASK >> 5) & 1;
   const int64_t items = B * geo_slots(g);
   if (int e = check_grid("stream_mix_bwd_apply", items)) return e;
@@ -840,7 +866,7 @@ int64_t add_residual_bwd_need_bytes(const void* dH_new, const void* bo, const vo
                                     int64_t D, int dtype) {
   if (B <= 0 || S <= 0 || D <= 0) return 0;
   const int vec = pick_vec(dtype, D, {dH_new, bo, dbo});
-  return B * geo_slots(make_geo(S, D, vec, GeoKind::Reduce, MHC_TPC_ADDBWD)) * 4 * (int64_t)sizeof(float);
+  return B * geo_slots(make_geo(S, D, vec, GeoKind::Reduce, MHC_TPC_ADDBWD, MHC_ADDBWD_OCC)) * 4 * (int64_t)sizeof(float);
 }
 
 int check_bsd_pub(const char* what, int64_t B, int64_t S, int64_t D, int dtype) { return check_bsd(what, B, S, D, dtype); }
@@ -864,7 +890,7 @@ extern "C" int64_t mhc_scratch_bytes(int op, int64_t B, int64_t S, int64_t D, in
   const int64_t f = (int64_t)sizeof(float);
   // Sized for the scalar path (pack width 1), which has the most column groups.
   switch (op) {
-    case MHC_OP_ADD_RESIDUAL_BWD: return B * geo_slots(make_geo(S, D, 1, GeoKind::Reduce, MHC_TPC_ADDBWD)) * 4 * f;
+    case MHC_OP_ADD_RESIDUAL_BWD: return B * geo_slots(make_geo(S, D, 1, GeoKind::Reduce, MHC_TPC_ADDBWD, -1)) * 4 * f;
     case MHC_OP_STREAM_MIX_BWD: return mix_bwd_scratch_floats(B, S, D) * f;
     case MHC_OP_MEANPOOL_FWD: return meanpool_scratch_floats(B, S, D) * f;
     case MHC_OP_DYNAMIC_WEIGHTS_FWD: return weights_fwd_scratch_bytes(B, 4 * D);
@@ -982,7 +1008,7 @@ extern "C" int mhc_add_residual_bwd(const void* dH_new, const void* branch_outpu
   }
   // sizes first, pointers last: a call whose scratch is too small says so even with null pointers
   const int vec = pick_vec(dtype, D, {dH_new, branch_output, d_branch_output});
-  Geo g = make_geo(S, D, vec, GeoKind::Reduce, MHC_TPC_ADDBWD);
+  Geo g = make_geo(S, D, vec, GeoKind::Reduce, MHC_TPC_ADDBWD, MHC_ADDBWD_OCC);
   g.reverse = (MHC_REV_MASK >> 3) & 1;
   const int64_t slots = geo_slots(g), items = B * slots;
   if (int e = check_grid("add_residual_bwd", items)) return e;

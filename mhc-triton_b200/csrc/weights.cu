@@ -20,7 +20,10 @@ static inline int k_slices(int64_t K) {
 }
 
 int64_t weights_fwd_scratch_bytes(int64_t batch, int64_t K) {
-  return batch * k_slices(K) * kProjW * (int64_t)sizeof(float);
+  const int64_t n = batch * k_slices(K) * kProjW * (int64_t)sizeof(float);
+  if (batch < kManyRows) return n;
+  const int64_t tc = rows_tc_fwd_scratch_bytes(K);   // the tensor-core path keeps a split copy of phi instead
+  return n > tc ? n : tc;
 }
 int64_t weights_bwd_scratch_bytes(int64_t batch, int64_t K) {
   int64_t n = batch * kBwdStride;                                   // per-row records
@@ -298,7 +301,7 @@ k_dw_bwd_rows(const float* __restrict__ saved, BiasPtrs bias, const float* __res
   const int64_t row = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (part20) {
-    block_column_sums_f64(part20 + row * slots * 20, slots, 20, s_red);
+    block_column_sums_fast<20, false>(part20 + row * slots * 20, slots, s_red);
     if (threadIdx.x < 20) {
       double t = 0.0;
 #pragma unroll
@@ -487,6 +490,9 @@ int weights_fwd_impl(const float* xsrc, int nsrc, double scale, float* x_out, co
                      float eps, int* tickets, cudaStream_t st) {
   int ks = k_slices(K);
   const bool many_rows = nsrc == 1 && scale == 1.0 && !x_out && batch >= kManyRows;
+  if (many_rows && rows_tc_usable(xsrc, batch, K))   // tcgen05 projection with the finish as its epilogue
+    return rows_fwd_tc_launch(xsrc, phi, bias, alpha_pre, alpha_post, alpha_res, H_pre, H_post, H_res, saved, part, batch,
+                              K, iters, eps, st);
   if (many_rows) {
     if (int e = project_rows_launch(xsrc, phi, part, batch, K, ks, st, &ks)) return e;
   } else {

@@ -1,0 +1,475 @@
+// Dynamic weights for many rows (per-token use: x [rows, K] fp32) on the fifth-generation tensor
+// cores: the projection x * phi runs as tcgen05.mma kind::tf32 with the accumulator in tensor
+// memory, x and phi tiles arrive by TMA (cp.async.bulk.tensor, 128-byte swizzle), and the whole
+// finish of a row (RMS norm, scale + bias, sigmoids, register Sinkhorn) is the kernel's epilogue,
+// so one kernel goes from x to (H_pre, H_post, H_res, saved).
+//
+// fp32 parity needs more than one TF32 product: x = hi + lo and phi = hi + lo (each half rounded to
+// TF32), and x * phi ~ hi*hi + hi*lo + lo*hi.  The tensor core reads its B operand from shared
+// memory and its A operand from shared OR tensor memory; splitting x inside shared memory would
+// triple the shared-memory traffic of an HBM-bound kernel, so the rows take the tensor-memory road:
+//
+//   warp 4 (one lane)   TMA producer: x tile [128 rows x 32 k] + the pre-split phi^T tiles (hi, lo)
+//                       [32 outputs x 32 k] per stage, three stages.
+//   warps 0-3           thread t owns row t: reads its 128 bytes of the x tile from shared memory,
+//                       splits them into hi / lo in registers, adds up x^2, and writes both halves to
+//                       tensor memory (tcgen05.st), lane t, as the A operand [128 x 32].
+//   warp 5 (one lane)   issues 4 k-steps x 3 products of tcgen05.mma (M 128, N 32, K 8) per tile into
+//                       one of two accumulators [128 x 32] in tensor memory, then tcgen05.commit.
+//   warps 0-3 again     drain the accumulator of the previous tile (tcgen05.ld) into fp32 registers:
+//                       the tensor core starts every 32-deep tile from zero and the running sums are
+//                       ordinary round-to-nearest fp32 adds, which keeps its truncating adds out of
+//                       the long sum over K.
+//
+// phi^T (hi, lo), padded to 32 outputs and to a multiple of 32 in K, is produced once per call by a
+// small kernel into caller scratch.  Every mbarrier wait is bounded (about a second); a wait that
+// runs out sets the status word in the scratch, the affected rows are filled with NaN, tensor
+// memory is released and the kernel returns.  No TMA multicast, no clusters, this GPU's memory only.
+#include <cuda.h>
+
+#include <cstdlib>
+#include <cstring>
+
+#include "common.cuh"
+#include "launch.h"
+
+namespace mhc {
+namespace tc {
+
+constexpr int kBM = 128;   // rows per CTA = lanes of tensor memory
+constexpr int kBK = 32;    // k per tile: 128 bytes of fp32, one swizzle span
+constexpr int kBN = 32;    // the 24 outputs, padded
+constexpr int kStages = 3;
+constexpr uint32_t kXBytes = kBM * kBK * 4;          // 16 KiB
+constexpr uint32_t kPBytes = kBN * kBK * 4;          // 4 KiB
+constexpr uint32_t kStageBytes = kXBytes + 2 * kPBytes;
+constexpr uint32_t kTmemCols = 256;                  // A: 3 stages x (32 hi + 32 lo); D: 2 x 32
+constexpr uint32_t kColA = 0, kColD = kStages * 64;
+constexpr int kThreads = 192;
+constexpr size_t kSmemBytes = 1024 + kStages * kStageBytes + 256;
+constexpr long long kWaitCycles = 2000000000LL;      // about one second
+
+// status word values (first int of the scratch): which wait ran out
+enum { kOk = 0, kErrFull = 1001, kErrAReady = 1002, kErrStageFree = 1003, kErrDFull = 1004, kErrDEmpty = 1005 };
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Bounded wait.  Returns false when the barrier did not complete within kWaitCycles (the status
+// word and the CTA's abort flag are then set) or when another thread of the CTA has already given up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (uint32_t i = 1;; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 31u) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > kWaitCycles) {
+        *abort_flag = 1;
+        atomicCAS(status, 0, code);
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t holder_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(holder_smem), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t base, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(base), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// D[128 x 32] (+)= A[128 x 8] (tensor memory) * B[32 x 8]^T (shared memory, K-major), TF32 inputs, fp32 sums.
+__device__ __forceinline__ void mma_tf32_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (32 fp32) under the
+// 128-byte swizzle: 8-row groups are 1024 bytes apart; the leading-dimension offset is not used in
+// this mode.  Bits: [0,14) address >> 4, [16,30) leading offset >> 4, [32,46) stride offset >> 4,
+// [46,48) descriptor version 1, [61,64) layout 2 = 128-byte swizzle.
+__device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024u >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+// Instruction descriptor: fp32 accumulator (bits [4,6) = 1), A and B TF32 (bits [7,10) = [10,13) = 2),
+// both K-major (bits 15, 16 = 0), N >> 3 in bits [17,23), M >> 4 in bits [24,29).
+constexpr uint32_t kIdesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+
+#define MHC_R32(a) a[0], a[1], a[2], a[3], a[4], a[5], a[6], a[7], a[8], a[9], a[10], a[11], a[12], a[13], a[14], a[15], \
+                   a[16], a[17], a[18], a[19], a[20], a[21], a[22], a[23], a[24], a[25], a[26], a[27], a[28], a[29], a[30], a[31]
+
+// 32 consecutive columns of this thread's lane: registers -> tensor memory.
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+        "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]),
+        "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]),
+        "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+      : "memory");
+}
+// tensor memory -> registers, same shape.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+        "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+        "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Round-to-nearest split of an fp32 value into two TF32 values: v ~ hi + lo.
+__device__ __forceinline__ uint32_t tf32_rn(float v) { return (__float_as_uint(v) + 0x1000u) & 0xFFFFE000u; }
+
+// phiT_hi / phiT_lo [32, Kp] from phi [K, 24]: rows 24..31 and columns K..Kp-1 are zero.  Also clears
+// the status word.
+__global__ void __launch_bounds__(256)
+k_phi_split_t(const float* __restrict__ phi, float* __restrict__ hi, float* __restrict__ lo, int64_t K, int64_t Kp,
+              int* __restrict__ status) {
+  pdl_prologue();
+  if (blockIdx.x == 0 && threadIdx.x == 0) *status = kOk;
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;   // index into [32, Kp]
+  if (i >= 32 * Kp) return;
+  const int64_t j = i / Kp, k = i - j * Kp;
+  float h = 0.f, l = 0.f;
+  if (j < 24 && k < K) {
+    const float v = __ldg(phi + k * 24 + j);
+    h = __uint_as_float(tf32_rn(v));
+    l = __uint_as_float(tf32_rn(v - h));
+  }
+  hi[i] = h;
+  lo[i] = l;
+}
+
+struct RowsFinish {
+  BiasPtrs bias;
+  const float *alpha_pre, *alpha_post, *alpha_res;
+  float *H_pre, *H_post, *H_res, *saved;
+  int iters;
+  float eps;
+};
+
+__global__ void __launch_bounds__(kThreads, 2)
+k_dw_rows_fwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_phi_hi,
+                 const __grid_constant__ CUtensorMap map_phi_lo, RowsFinish fin, int64_t rows, int64_t K, int* status) {
+  pdl_prologue();
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;   // tiles need 1024-byte alignment for the swizzle
+  const uint32_t bars = base + kStages * kStageBytes;
+  // barriers: full[3] a_ready[3] stage_free[3] d_full[2] d_empty[2]
+  auto bar_full = [&](int s) { return bars + 8u * s; };
+  auto bar_aready = [&](int s) { return bars + 8u * (kStages + s); };
+  auto bar_free = [&](int s) { return bars + 8u * (2 * kStages + s); };
+  auto bar_dfull = [&](int d) { return bars + 8u * (3 * kStages + d); };
+  auto bar_dempty = [&](int d) { return bars + 8u * (3 * kStages + 2 + d); };
+  const uint32_t holder = bars + 8u * (3 * kStages + 4);
+  __shared__ int s_abort;
+  volatile int* abort_flag = &s_abort;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t row0 = (int64_t)blockIdx.x * kBM;
+  const int nk = (int)((K + kBK - 1) / kBK);
+
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(bar_full(s), 1);
+      mbar_init(bar_aready(s), kBM);
+      mbar_init(bar_free(s), 1);
+    }
+    for (int d = 0; d < 2; ++d) {
+      mbar_init(bar_dfull(d), 1);
+      mbar_init(bar_dempty(d), kBM);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 5) tmem_alloc(holder, kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  uint32_t tmem_base;
+  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(holder) : "memory");
+
+  if (warp == 4) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      for (int i = 0; i < nk; ++i) {
+        const int s = i % kStages;
+        if (i >= kStages && !mbar_wait(bar_free(s), ((i / kStages) - 1) & 1, abort_flag, status, kErrStageFree)) break;
+        const uint32_t dst = base + s * kStageBytes;
+        mbar_expect_tx(bar_full(s), kStageBytes);
+        tma_load_2d(dst, &map_x, i * kBK, (int)row0, bar_full(s));
+        tma_load_2d(dst + kXBytes, &map_phi_hi, i * kBK, 0, bar_full(s));
+        tma_load_2d(dst + kXBytes + kPBytes, &map_phi_lo, i * kBK, 0, bar_full(s));
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      for (int i = 0; i < nk; ++i) {
+        const int s = i % kStages, d = i & 1;
+        const uint32_t ph = (i / kStages) & 1;
+        if (!mbar_wait(bar_full(s), ph, abort_flag, status, kErrFull)) break;
+        if (!mbar_wait(bar_aready(s), ph, abort_flag, status, kErrAReady)) break;
+        if (i >= 2 && !mbar_wait(bar_dempty(d), ((i >> 1) - 1) & 1, abort_flag, status, kErrDEmpty)) break;
+        tc_fence_after();
+        const uint32_t stage = base + s * kStageBytes;
+        const uint64_t b_hi = make_kmajor_sw128_desc(stage + kXBytes);
+        const uint64_t b_lo = make_kmajor_sw128_desc(stage + kXBytes + kPBytes);
+        const uint32_t a_hi = tmem_base + kColA + s * 64, a_lo = a_hi + 32, dd = tmem_base + kColD + d * 32;
+#pragma unroll
+        for (int j = 0; j < kBK / 8; ++j) {   // a k-step of 8 is 32 bytes of a swizzled row: descriptor address + 2
+          mma_tf32_ts(dd, a_hi + 8 * j, b_hi + 2 * j, kIdesc, j > 0);
+          mma_tf32_ts(dd, a_hi + 8 * j, b_lo + 2 * j, kIdesc, 1);
+          mma_tf32_ts(dd, a_lo + 8 * j, b_hi + 2 * j, kIdesc, 1);
+        }
+        tc_commit(bar_free(s));    // stage s (shared memory and its A columns) may be refilled
+        tc_commit(bar_dfull(d));   // accumulator d holds this tile's sums
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ rows: split, accumulate, finish
+    const int t = threadIdx.x;                   // row within the tile = lane of tensor memory
+    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    float acc[24];
+#pragma unroll
+    for (int j = 0; j < 24; ++j) acc[j] = 0.f;
+    float q = 0.f;
+    bool ok = true;
+    auto drain = [&](int i) {   // add tile i's accumulator to the running sums
+      const int d = i & 1;
+      if (!mbar_wait(bar_dfull(d), (i >> 1) & 1, abort_flag, status, kErrDFull)) return false;
+      tc_fence_after();
+      uint32_t v[32];
+      tmem_ld32(tmem_base + lane_addr + kColD + d * 32, v);
+      tmem_wait_ld();
+#pragma unroll
+      for (int j = 0; j < 24; ++j) acc[j] += __uint_as_float(v[j]);
+      tc_fence_before();
+      mbar_arrive(bar_dempty(d));
+      return true;
+    };
+    for (int i = 0; i < nk && ok; ++i) {
+      const int s = i % kStages;
+      if (!mbar_wait(bar_full(s), (i / kStages) & 1, abort_flag, status, kErrFull)) { ok = false; break; }
+      const uint32_t rowp = base + s * kStageBytes + (uint32_t)t * 128u;
+      uint32_t hi[32], lo[32];
+      float qt = 0.f;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {   // 16-byte chunk c of row t sits at chunk position c ^ (t & 7)
+        float4 v;
+        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                     : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                     : "r"(rowp + (uint32_t)((c ^ (t & 7)) << 4))
+                     : "memory");
+        const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const uint32_t h = tf32_rn(e[u]);
+          hi[4 * c + u] = h;
+          lo[4 * c + u] = tf32_rn(e[u] - __uint_as_float(h));
+          qt = fmaf(e[u], e[u], qt);
+        }
+      }
+      q += qt;
+      const uint32_t a_hi = tmem_base + lane_addr + kColA + s * 64;
+      tmem_st32(a_hi, hi);
+      tmem_st32(a_hi + 32, lo);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(bar_aready(s));
+      if (i >= 1) ok = drain(i - 1);
+    }
+    if (ok && nk > 0) ok = drain(nk - 1);
+    const int64_t row = row0 + t;
+    if (row < rows) {
+      const float nanv = __int_as_float(0x7fc00000);
+      if (!ok) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { fin.H_pre[row * 4 + j] = nanv; fin.H_post[row * 4 + j] = nanv; }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) fin.H_res[row * 16 + j] = nanv;
+      } else {
+        // the finish of one row, thread-resident (same formulas and orders as the warp-per-row finish)
+        const float eps = fin.eps;
+        const float inv_rms = 1.f / sqrtf(q / (float)K + eps);
+        const float a_pre = __ldg(fin.alpha_pre), a_post = __ldg(fin.alpha_post), a_res = __ldg(fin.alpha_res);
+        float sc[24];
+#pragma unroll
+        for (int j = 0; j < 24; ++j) {
+          const float al = j < 4 ? a_pre : (j < 8 ? a_post : a_res);
+          const float b = j < 4 ? __ldg(fin.bias.pre + j) : (j < 8 ? __ldg(fin.bias.post + j - 4) : __ldg(fin.bias.res + j - 8));
+          sc[j] = (inv_rms * al) * acc[j] + b;
+        }
+        if (fin.saved) {
+          float* sv = fin.saved + row * kSavedStride;
+#pragma unroll
+          for (int j = 0; j < 24; ++j) sv[j] = acc[j];
+          sv[24] = q;
+          sv[25] = inv_rms;
+        }
+        float sg[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sg[j] = sigmoidf_(sc[j]);
+        const float ssum = (((sg[0] + sg[1]) + sg[2]) + sg[3]) + eps;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          fin.H_pre[row * 4 + j] = sg[j] / ssum;
+          fin.H_post[row * 4 + j] = 2.f * sg[4 + j];
+        }
+        float m[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) m[j] = fabsf(sc[8 + j]) + eps;
+        for (int it = 0; it < fin.iters; ++it) sinkhorn_step(m, eps);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) fin.H_res[row * 16 + j] = m[j];
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static const EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess) {
+      (void)cudaGetLastError();
+      p = nullptr;
+    }
+    return (EncodeTiledFn)p;
+  }();
+  return fn;
+}
+
+// A [rows, cols] fp32 row-major tensor (row pitch cols * 4 bytes) cut into [box_rows x 32] tiles under
+// the 128-byte swizzle; out-of-range elements read as zero.
+static bool make_map_2d(CUtensorMap* m, const float* ptr, int64_t rows, int64_t cols, int box_rows) {
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)cols * 4};
+  const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  return enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(ptr), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+static bool enabled() {
+  static const bool on = [] {
+    const char* e = std::getenv("MHC_ROWS_TC");
+    return !(e && std::strcmp(e, "0") == 0);
+  }();
+  return on;
+}
+
+}  // namespace tc
+
+static inline int64_t round_up(int64_t v, int64_t m) { return (v + m - 1) / m * m; }
+
+// Scratch of the tensor-core forward: a 256-byte header (status word) + phi^T hi and lo [32, Kp].
+int64_t rows_tc_fwd_scratch_bytes(int64_t K) { return 256 + 2 * 32 * round_up(K, tc::kBK) * (int64_t)sizeof(float); }
+
+// The tensor-core path needs TMA-compatible x rows (16-byte aligned base and pitch); MHC_ROWS_TC=0 in
+// the environment turns it off (the mma.sync kernels then run).
+bool rows_tc_usable(const float* x, int64_t batch, int64_t K) {
+  return tc::enabled() && batch >= kManyRows && K % 4 == 0 && K >= 4 && is_aligned16(x) && batch < (1LL << 31) &&
+         K < (1LL << 31) && tc::encode_fn() != nullptr;
+}
+
+int rows_fwd_tc_launch(const float* x, const float* phi, BiasPtrs bias, const float* alpha_pre, const float* alpha_post,
+                       const float* alpha_res, float* H_pre, float* H_post, float* H_res, float* saved, void* scratch,
+                       int64_t batch, int64_t K, int iters, float eps, cudaStream_t st) {
+  using namespace tc;
+  if (!is_aligned16(scratch)) return fail(MHC_ERR_MISALIGNED, "dynamic_weights_fwd: scratch must be 16-byte aligned");
+  const int64_t Kp = round_up(K, kBK);
+  int* status = (int*)scratch;
+  float* phi_hi = (float*)((char*)scratch + 256);
+  float* phi_lo = phi_hi + 32 * Kp;
+  CUtensorMap mx, mh, ml;
+  if (!make_map_2d(&mx, x, batch, K, kBM) || !make_map_2d(&mh, phi_hi, 32, Kp, kBN) || !make_map_2d(&ml, phi_lo, 32, Kp, kBN))
+    return fail(MHC_ERR_CUDA, "dynamic_weights_fwd: cuTensorMapEncodeTiled failed");
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(k_dw_rows_fwd_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes) != cudaSuccess)
+      return check_launch("dynamic_weights_fwd(tc attribute)");
+    attr_set = true;
+  }
+  {
+    ProfScope ps("k_phi_split_t", st);
+    launch_k(k_phi_split_t, (unsigned)((32 * Kp + 255) / 256), 256, 0, st, phi, phi_hi, phi_lo, K, Kp, status);
+  }
+  if (int e = check_launch("dynamic_weights_fwd(phi split)")) return e;
+  const RowsFinish fin{bias, alpha_pre, alpha_post, alpha_res, H_pre, H_post, H_res, saved, iters, eps};
+  {
+    ProfScope ps("k_dw_rows_fwd_tc", st);
+    launch_k(k_dw_rows_fwd_tc, (unsigned)((batch + kBM - 1) / kBM), kThreads, kSmemBytes, st, mx, mh, ml, fin, batch, K, status);
+  }
+  return check_launch("dynamic_weights_fwd(tc)");
+}
+
+}  // namespace mhc

@@ -160,6 +160,14 @@ def scratch(op, B, S, D, like: torch.Tensor):
 
 
 _tickets = {}
+_tickets_on = os.environ.get("MHC_TICKETS", "1") != "0"
+
+
+def set_ticket_finish(enabled: bool) -> None:
+    """Finish the deterministic sums inside the producing kernels (default; MHC_TICKETS=0 in the
+    environment turns it off) or with the separate finish kernels.  Results are bit-identical."""
+    global _tickets_on
+    _tickets_on = bool(enabled)
 
 
 def tickets(like: torch.Tensor, n: int):
@@ -168,6 +176,8 @@ def tickets(like: torch.Tensor, n: int):
     when it is created; it is kept per (device, stream) because calls that can overlap on the GPU
     must not share counters.  Created outside of stream capture on first use (warm up before
     capturing a CUDA graph, as torch requires anyway)."""
+    if not _tickets_on:
+        return None
     dev = like.device.index if like.device.index is not None else torch.cuda.current_device()
     key = (dev, stream_of(like))
     buf = _tickets.get(key)

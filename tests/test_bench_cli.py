@@ -21,7 +21,9 @@ def test_reference_arm_prints_contract_line():
     line = json.loads(r.stdout.strip().splitlines()[-1])
     assert line["impl"] == "reference" and line["metric"] == "hc_fwd_bwd_tokens_per_s" and line["unit"] == "tokens/s"
     assert line["higher_is_better"] is True and line["value"] > 0 and line["steps"] == 1
-    assert line["cpu_baseline"]["kind"] == "port" and line["cpu_baseline"]["cores"] >= 1
+    have_ref = os.path.exists(os.path.join(ROOT, "baseline", "_ref", "mhc", "_torch_baseline.py"))
+    assert line["cpu_baseline"]["kind"] == ("reference" if have_ref else "port") and line["cpu_baseline"]["cores"] >= 1
+    assert set(line["config"]) >= {"workload", "global_tokens", "sharding", "per_gpu_batch", "layers", "cuda_graph"}
     assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["e2e"]["d2h_bytes_per_step"] == 0
     assert line["e2e"]["value"] == line["value"]
 
