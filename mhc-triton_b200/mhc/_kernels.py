@@ -91,6 +91,9 @@ def meanpool_forward(H: torch.Tensor) -> torch.Tensor:
     return x
 
 
+last_dynamic_weights_scratch = None
+
+
 def _alpha_dev(a, like: torch.Tensor) -> torch.Tensor:
     """A scale as a one-element fp32 device tensor (Python floats are uploaded without a sync)."""
     if torch.is_tensor(a):
@@ -121,6 +124,8 @@ def fused_dynamic_weights_forward(x: torch.Tensor, phi: torch.Tensor, bias: torc
     H_res = torch.empty(B, 4, 4, device=x.device, dtype=torch.float32)
     saved = torch.empty(B, 32, device=x.device, dtype=torch.float32)
     buf, nbytes = L.scratch(L.OP_DYNAMIC_WEIGHTS_FWD, B, 0, (K + 3) // 4, x)
+    global last_dynamic_weights_scratch
+    last_dynamic_weights_scratch = buf     # its first int is the status word of the many-rows kernels (0 = fine)
     with torch.cuda.device(x.device):
         L.call("mhc_dynamic_weights_fwd", L.stream_of(x), L.ptr(x), L.ptr(phi), L.ptr(bias), L.ptr(a[0]), L.ptr(a[1]),
                                                  L.ptr(a[2]), L.ptr(H_pre), L.ptr(H_post), L.ptr(H_res), L.ptr(saved),

@@ -115,3 +115,27 @@ def test_results_do_not_depend_on_programmatic_dependent_launch(tmp_path):
         outs.append(torch.load(path))
     for a, b in zip(*outs):
         assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("rows,K", [(64, 64), (128, 32), (300, 4 * 100 + 4), (1000, 4 * 256), (4096 + 17, 2048)])
+def test_many_rows_tensor_core_forward_status_and_parity(rows, K):
+    """The tcgen05 forward of the many-rows dynamic weights: every bounded wait completed (status
+    word 0), outputs within the fp32 band of the fp64 oracle, and the saved record (raw projections,
+    sum of squares, inverse RMS) matches what the backward expects."""
+    from mhc import _kernels as KK
+    torch.manual_seed(rows + K)
+    x = torch.randn(rows, K)
+    phi = torch.randn(K, 24) * 0.05
+    bias = torch.randn(24)
+    al = [torch.tensor([0.3]), torch.tensor([-0.2]), torch.tensor([0.5])]
+    a, b, c = O.dynamic_weights(x.double(), phi.double(), bias.double(), *[t.double() for t in al], 20, 1e-6)
+    d = lambda t: t.to(DEV)
+    a2, b2, c2, saved = KK.fused_dynamic_weights_forward(d(x), d(phi), d(bias), *[d(t) for t in al], 20, 1e-6, return_saved=True)
+    torch.cuda.synchronize()
+    assert int(KK.last_dynamic_weights_scratch.view(torch.int32)[0]) == 0
+    from tests.util import assert_close
+    assert_close(a2, a, 1e-5, 1e-6, "H_pre"); assert_close(b2, b, 1e-5, 1e-6, "H_post"); assert_close(c2, c, 2e-5, 4e-6, "H_res")
+    raw = x.double() @ phi.double()
+    assert (saved[:, :24].double().cpu() - raw).abs().max() <= 1e-5 * raw.abs().max() + 1e-6
+    q = (x.double() ** 2).sum(-1)
+    assert ((saved[:, 24].double().cpu() - q).abs() <= 1e-5 * q).all()
