@@ -489,6 +489,43 @@ __device__ __forceinline__ void sinkhorn_step_bwd(float (&d)[16], const float (&
   }
 }
 
+// Gradient d (with respect to the output of `iters` Sinkhorn iterations started from |m0| + eps) pulled
+// back to the start matrix, in place, with no stored states: the iterations are cut into kSinkhornCk + 1
+// segments of L = ceil(iters / (kSinkhornCk + 1)); one forward sweep keeps the state entering each segment
+// in registers, and the state entering iteration t is then recomputed from its segment's checkpoint (at
+// most L - 1 steps) instead of from m0 (t steps).  The recomputation runs the same step function
+// from the same values, so the result is bit-identical to recomputing from m0 every time, for about
+// iters * (L + 3) / 2 steps instead of iters * (iters + 1) / 2.  The sign of m0 is NOT applied.
+constexpr int kSinkhornCk = 4;
+__device__ __forceinline__ void sinkhorn_backward_ck(const float (&m0)[16], float (&d)[16], int iters, float eps) {
+  const int L = (iters + kSinkhornCk) / (kSinkhornCk + 1);
+  float ck[kSinkhornCk][16];
+  {
+    float m[16];
+#pragma unroll
+    for (int k = 0; k < 16; ++k) m[k] = fabsf(m0[k]) + eps;
+#pragma unroll
+    for (int k = 0; k < kSinkhornCk; ++k) {
+      const int t1 = min((k + 1) * L, iters);
+      for (int t = k * L; t < t1; ++t) sinkhorn_step(m, eps);
+#pragma unroll
+      for (int e = 0; e < 16; ++e) ck[k][e] = m[e];  // state entering iteration (k + 1) * L
+    }
+  }
+#pragma unroll
+  for (int k = kSinkhornCk; k >= 0; --k) {
+    const int t0 = k * L, t1 = min((k + 1) * L, iters);
+    for (int t = t1 - 1; t >= t0; --t) {
+      float m[16], r[4], c[4], mr[16];
+#pragma unroll
+      for (int e = 0; e < 16; ++e) m[e] = k == 0 ? fabsf(m0[e]) + eps : ck[k == 0 ? 0 : k - 1][e];
+      for (int f = t0; f < t; ++f) sinkhorn_step(m, eps);
+      sinkhorn_step(m, eps, r, mr, c);
+      sinkhorn_step_bwd(d, m, r, mr, c);
+    }
+  }
+}
+
 __device__ __forceinline__ float sigmoidf_(float v) { return 1.f / (1.f + expf(-v)); }
 
 }  // namespace mhc

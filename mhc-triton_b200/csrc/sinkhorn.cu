@@ -100,41 +100,17 @@ __global__ void __launch_bounds__(128) k_sinkhorn_bwd(const T* __restrict__ M, c
 // (at most L - 1 steps) instead of from M (t steps).  The recomputation runs the same step
 // function from the same values, so the result is bit-identical to k_sinkhorn_bwd, for about
 // iters * (L + 3) / 2 steps instead of iters * (iters + 1) / 2.  Still nothing but M and dP is read.
-constexpr int kCk = 4;
 template <typename T>
 __global__ void __launch_bounds__(128) k_sinkhorn_bwd_ck(const T* __restrict__ M, const T* __restrict__ dP,
-                                                         T* __restrict__ dM, int64_t batch, int iters, int L,
+                                                         T* __restrict__ dM, int64_t batch, int iters,
                                                          float eps, float sign_at_zero, bool aligned) {
   pdl_prologue();
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= batch) return;
-  float m0[16], d[16], ck[kCk][16];
+  float m0[16], d[16];
   load_matrix(M + i * 16, m0, aligned);
   load_matrix(dP + i * 16, d, aligned);
-  {
-    float m[16];
-#pragma unroll
-    for (int k = 0; k < 16; ++k) m[k] = fabsf(m0[k]) + eps;
-#pragma unroll
-    for (int k = 0; k < kCk; ++k) {
-      const int t1 = min((k + 1) * L, iters);
-      for (int t = k * L; t < t1; ++t) sinkhorn_step(m, eps);
-#pragma unroll
-      for (int e = 0; e < 16; ++e) ck[k][e] = m[e];  // state entering iteration (k + 1) * L
-    }
-  }
-#pragma unroll
-  for (int k = kCk; k >= 0; --k) {
-    const int t0 = k * L, t1 = min((k + 1) * L, iters);
-    for (int t = t1 - 1; t >= t0; --t) {
-      float m[16], r[4], c[4], mr[16];
-#pragma unroll
-      for (int e = 0; e < 16; ++e) m[e] = k == 0 ? fabsf(m0[e]) + eps : ck[k == 0 ? 0 : k - 1][e];
-      for (int f = t0; f < t; ++f) sinkhorn_step(m, eps);
-      sinkhorn_step(m, eps, r, mr, c);
-      sinkhorn_step_bwd(d, m, r, mr, c);
-    }
-  }
+  sinkhorn_backward_ck(m0, d, iters, eps);
 #pragma unroll
   for (int k = 0; k < 16; ++k) {
     const float sg = m0[k] > 0.f ? 1.f : (m0[k] < 0.f ? -1.f : sign_at_zero);
@@ -167,8 +143,7 @@ static int launch_bwd(const void* M, const void* dP, void* dM, int64_t batch, in
              aligned);
   } else {
     ProfScope ps("k_sinkhorn_bwd_ck", st);
-    const int L = (iters + kCk) / (kCk + 1);
-    launch_k(k_sinkhorn_bwd_ck<T>, (unsigned)grid, block, 0, st, (const T*)M, (const T*)dP, (T*)dM, batch, iters, L, eps,
+    launch_k(k_sinkhorn_bwd_ck<T>, (unsigned)grid, block, 0, st, (const T*)M, (const T*)dP, (T*)dM, batch, iters, eps,
              sz, aligned);
   }
   return check_launch("sinkhorn_bwd");

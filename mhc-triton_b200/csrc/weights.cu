@@ -331,6 +331,77 @@ k_dw_bwd_rows(const float* __restrict__ saved, BiasPtrs bias, const float* __res
   }
 }
 
+// The same per-row records for MANY rows (per-token use): one THREAD per row, everything in registers,
+// the Sinkhorn reverse sweep with register checkpoints (sinkhorn_backward_ck) instead of states in
+// shared memory.  Same formulas and summation orders as dw_bwd_row_warp, so the records are
+// bit-identical to k_dw_bwd_rows'.  dH_pre / dH_res hold finished sums.
+__global__ void __launch_bounds__(128)
+k_dw_bwd_rows_thread(const float* __restrict__ saved, BiasPtrs bias, const float* __restrict__ alpha_pre,
+                     const float* __restrict__ alpha_post, const float* __restrict__ alpha_res,
+                     const float* __restrict__ dH_pre, const float* __restrict__ dH_post,
+                     const float* __restrict__ dH_res, float* __restrict__ buf, int64_t batch, int64_t K, int iters,
+                     float eps, float sign_at_zero) {
+  pdl_prologue();
+  const int64_t row = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= batch) return;
+  const float* sv = saved + row * kSavedStride;
+  const float inv_rms = __ldg(sv + 25);
+  const float a_pre = __ldg(alpha_pre), a_post = __ldg(alpha_post), a_res = __ldg(alpha_res);
+  float raw[24], sc[24], ds[24];
+#pragma unroll
+  for (int j = 0; j < 24; ++j) {
+    raw[j] = __ldg(sv + j);
+    sc[j] = (inv_rms * group_alpha(j, a_pre, a_post, a_res)) * raw[j] + bias_at(bias, j);
+  }
+  float sg[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) sg[j] = sigmoidf_(sc[j]);
+  const float ssum = (((sg[0] + sg[1]) + sg[2]) + sg[3]) + eps;
+  float g[8];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    g[j] = __ldg(dH_pre + row * 4 + j);
+    g[4 + j] = __ldg(dH_post + row * 4 + j);
+  }
+  const float dot = ((g[0] * (sg[0] / ssum) + g[1] * (sg[1] / ssum)) + g[2] * (sg[2] / ssum)) + g[3] * (sg[3] / ssum);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    ds[j] = ((g[j] - dot) / ssum) * sg[j] * (1.f - sg[j]);
+    ds[4 + j] = g[4 + j] * 2.f * sg[4 + j] * (1.f - sg[4 + j]);
+  }
+  {
+    float m0[16], d[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      m0[i] = sc[8 + i];
+      d[i] = __ldg(dH_res + row * 16 + i);
+    }
+    sinkhorn_backward_ck(m0, d, iters, eps);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float sgn = m0[i] > 0.f ? 1.f : (m0[i] < 0.f ? -1.f : sign_at_zero);
+      ds[8 + i] = d[i] * sgn;
+    }
+  }
+  float inv_g[3] = {0.f, 0.f, 0.f}, ga[3] = {0.f, 0.f, 0.f};
+  float* o = buf + row * kBwdStride;
+#pragma unroll
+  for (int j = 0; j < 24; ++j) {
+    const float alpha = group_alpha(j, a_pre, a_post, a_res);
+    const int gi = j < 4 ? 0 : (j < 8 ? 1 : 2);
+    inv_g[gi] += (ds[j] * alpha) * raw[j];
+    ga[gi] += (ds[j] * inv_rms) * raw[j];
+    o[j] = ds[j];
+    o[24 + j] = (ds[j] * inv_rms) * alpha;
+  }
+  const float d_inv_rms = (inv_g[0] + inv_g[1]) + inv_g[2];
+  const float d_rms = d_inv_rms * (-(inv_rms * inv_rms));
+  o[48] = d_rms * inv_rms / (float)K;
+  o[49] = ga[0];
+  o[50] = ga[1];
+  o[51] = ga[2];
+}
+
 // grad_x[row,k] = sum_j d_raw[row,j] phi[k,j] + coef[row] x[row,k];  grad_phi[k,j] = sum_row x[row,k] d_raw[row,j]
 // (rows added in index order, fp64 accumulators).  The last CTA sums grad_bias and grad_alpha over rows.
 constexpr int kRowTile = 32;
@@ -534,7 +605,14 @@ int weights_bwd_impl(const float* x, const float* phi, BiasPtrs bias, const floa
     }
     return check_launch("dynamic_weights_bwd(fused)");
   }
-  if (batch) {
+  if (batch >= kManyRows && !part20) {
+    {
+      ProfScope ps("k_dw_bwd_rows_thread", st);
+      launch_k(k_dw_bwd_rows_thread, (unsigned)((batch + 127) / 128), 128, 0, st, saved, bias, alpha_pre, alpha_post, alpha_res,
+               (const float*)dH_pre, dH_post, (const float*)dH_res, buf, batch, K, iters, eps, sign0);
+    }
+    if (int e = check_launch("dynamic_weights_bwd(rows)")) return e;
+  } else if (batch) {
     {
       ProfScope ps("k_dw_bwd_rows", st);
       launch_k(k_dw_bwd_rows, (unsigned)batch, part20 ? 256 : 32, 0, st, saved, bias, alpha_pre, alpha_post, alpha_res, part20, slots,

@@ -386,6 +386,331 @@ k_dw_rows_fwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
   }
 }
 
+// ======================================================================================
+// Backward pass over x:  grad_x[r,k] = sum_j d_raw[r,j] phi[k,j] + coef[r] x[r,k]   and the per-group
+// partial sums of  grad_phi[k,j] = sum_r x[r,k] d_raw[r,j],  reading x once.
+//
+// One CTA owns a slab of 128 k and walks a group of rows in sub-tiles of 128 rows.  Both products
+// run on tcgen05 with 3xTF32 splits:
+//   product 1 (grad_x):   A = d_raw hi/lo [128 rows x 32 j] in tensor memory, B = the slab of phi hi/lo
+//                         [128 k x 32 j] in shared memory (loaded once per CTA), D1 [128 rows x 128 k].
+//   product 2 (grad_phi): A = x^T hi/lo [128 k x 64 rows] per half sub-tile in tensor memory (thread t of
+//                         warps 4-7 owns k = t: it reads its column of the x tile from shared memory,
+//                         splits it and writes lane t), B = d_raw^T hi/lo [32 j x 128 rows] written to
+//                         shared memory by the row threads in the swizzled K-major layout, D2 [128 k x 32 j]
+//                         per half, drained into fp32 registers after every half.
+//   warps 0-3 (row threads)     d_raw / coef of their row -> A of product 1 and B of product 2; later
+//                               the epilogue: D1 + coef * x, written over the x tile in place and
+//                               stored by TMA.
+//   warps 4-7 (column threads)  x^T halves -> tensor memory; running sums of grad_phi.
+//   warp 8 (one lane)           TMA loads: phi slab once, x sub-tiles (two stages of 64 KiB).
+//   warp 9 (one lane)           all tcgen05.mma and tcgen05.commit.
+// Tensor memory: A1 64 + D1 128 + A2 2 x 128 + D2 2 x 32 = 512 columns (one CTA per SM).
+// ======================================================================================
+namespace bw {
+constexpr int kSlab = 128;                         // k per CTA
+constexpr uint32_t kXStage = 4 * kXBytes;          // 64 KiB: four [128 rows x 32 k] tiles
+constexpr uint32_t kOffB1 = 2 * kXStage;           // phi slab hi, lo: 2 x 16 KiB
+constexpr uint32_t kB1Bytes = kSlab * 32 * 4;
+constexpr uint32_t kOffB2 = kOffB1 + 2 * kB1Bytes; // d_raw^T hi, lo: 2 x 16 KiB (4 blocks of [32 j x 32 rows])
+constexpr uint32_t kB2Bytes = 32 * 128 * 4;
+constexpr uint32_t kOffBars = kOffB2 + 2 * kB2Bytes;
+constexpr size_t kSmem = 1024 + kOffBars + 256;
+constexpr int kThreadsBwd = 320;
+constexpr uint32_t kColA1 = 0, kColD1 = 64, kColA2 = 192, kColD2 = 448;   // A2 half h at kColA2 + 128 h (hi 64, lo 64)
+constexpr uint32_t kIdescN128 = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+enum { kErrPhi = 2001, kErrXFull = 2002, kErrXFree = 2003, kErrXRead = 2004, kErrA1 = 2005, kErrAbFree = 2006,
+       kErrA2Ready = 2007, kErrA2Free = 2008, kErrD1Full = 2009, kErrD1Empty = 2010, kErrD2Full = 2011, kErrD2Empty = 2012 };
+}  // namespace bw
+
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int y, uint32_t src) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+               ::"l"(map), "r"(x), "r"(y), "r"(src)
+               : "memory");
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// phi_hi / phi_lo [Kp, 32] from phi [K, 24] (columns 24..31 and rows K..Kp-1 zero); clears the status word.
+__global__ void __launch_bounds__(256)
+k_phi_split_rows(const float* __restrict__ phi, float* __restrict__ hi, float* __restrict__ lo, int64_t K, int64_t Kp,
+                 int* __restrict__ status) {
+  pdl_prologue();
+  if (blockIdx.x == 0 && threadIdx.x == 0) *status = kOk;
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= 32 * Kp) return;
+  const int64_t k = i >> 5;
+  const int j = (int)(i & 31);
+  float h = 0.f, l = 0.f;
+  if (j < 24 && k < K) {
+    const float v = __ldg(phi + k * 24 + j);
+    h = __uint_as_float(tf32_rn(v));
+    l = __uint_as_float(tf32_rn(v - h));
+  }
+  hi[i] = h;
+  lo[i] = l;
+}
+
+__global__ void __launch_bounds__(bw::kThreadsBwd, 1)
+k_dw_rows_bwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_gx,
+                 const __grid_constant__ CUtensorMap map_phi_hi, const __grid_constant__ CUtensorMap map_phi_lo,
+                 const float* __restrict__ buf, float* __restrict__ phi_part, int64_t rows, int64_t K,
+                 int64_t rows_per_group, int* status) {
+  using namespace bw;
+  pdl_prologue();
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bars = base + kOffBars;
+  // barriers (8 bytes each)
+  const uint32_t b_phi = bars;
+  auto b_xfull = [&](int s) { return bars + 8u * (1 + s); };
+  auto b_xfree = [&](int s) { return bars + 8u * (3 + s); };
+  auto b_xread = [&](int s) { return bars + 8u * (5 + s); };
+  const uint32_t b_a1 = bars + 8u * 7, b_abfree = bars + 8u * 8;
+  auto b_a2ready = [&](int h) { return bars + 8u * (9 + h); };
+  auto b_a2free = [&](int h) { return bars + 8u * (11 + h); };
+  const uint32_t b_d1full = bars + 8u * 13, b_d1empty = bars + 8u * 14;
+  auto b_d2full = [&](int h) { return bars + 8u * (15 + h); };
+  auto b_d2empty = [&](int h) { return bars + 8u * (17 + h); };
+  const uint32_t holder = bars + 8u * 19;
+  __shared__ int s_abort;
+  volatile int* abort_flag = &s_abort;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t k0 = (int64_t)blockIdx.x * kSlab;
+  const int64_t g0 = (int64_t)blockIdx.y * rows_per_group;
+  const int64_t g1 = min(g0 + rows_per_group, rows);
+  const int nsub = (int)((g1 - g0 + kBM - 1) / kBM);
+
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    mbar_init(b_phi, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(b_xfull(s), 1);
+      mbar_init(b_xfree(s), 1);
+      mbar_init(b_xread(s), 128);
+      mbar_init(b_a2ready(s), 128);
+      mbar_init(b_a2free(s), 1);
+      mbar_init(b_d2full(s), 1);
+      mbar_init(b_d2empty(s), 128);
+    }
+    mbar_init(b_a1, 128);
+    mbar_init(b_abfree, 1);
+    mbar_init(b_d1full, 1);
+    mbar_init(b_d1empty, 128);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 9) tmem_alloc(holder, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  uint32_t tmem_base;
+  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(holder) : "memory");
+
+  if (warp == 8) {
+    // ---------------------------------------------------------------- TMA loads
+    if (lane == 0) {
+      mbar_expect_tx(b_phi, 2 * kB1Bytes);
+      tma_load_2d(base + kOffB1, &map_phi_hi, 0, (int)k0, b_phi);
+      tma_load_2d(base + kOffB1 + kB1Bytes, &map_phi_lo, 0, (int)k0, b_phi);
+      for (int it = 0; it < nsub; ++it) {
+        const int s = it & 1;
+        if (it >= 2 && !mbar_wait(b_xfree(s), ((it >> 1) - 1) & 1, abort_flag, status, kErrXFree)) break;
+        mbar_expect_tx(b_xfull(s), kXStage);
+        const int r0 = (int)(g0 + (int64_t)it * kBM);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          tma_load_2d(base + s * kXStage + kk * kXBytes, &map_x, (int)k0 + 32 * kk, r0, b_xfull(s));
+      }
+    }
+  } else if (warp == 9) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      bool ok = mbar_wait(b_phi, 0, abort_flag, status, kErrPhi);
+      const uint64_t b1_hi = make_kmajor_sw128_desc(base + kOffB1), b1_lo = make_kmajor_sw128_desc(base + kOffB1 + kB1Bytes);
+      for (int it = 0; it < nsub && ok; ++it) {
+        const uint32_t ph = it & 1;
+        if (!mbar_wait(b_a1, ph, abort_flag, status, kErrA1)) break;
+        if (it >= 1 && !mbar_wait(b_d1empty, (it - 1) & 1, abort_flag, status, kErrD1Empty)) break;
+        tc_fence_after();
+        const uint32_t a1_hi = tmem_base + kColA1, a1_lo = a1_hi + 32, d1 = tmem_base + kColD1;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {   // product 1: K = 32 (24 used) in steps of 8
+          mma_tf32_ts(d1, a1_hi + 8 * j, b1_hi + 2 * j, kIdescN128, j > 0);
+          mma_tf32_ts(d1, a1_hi + 8 * j, b1_lo + 2 * j, kIdescN128, 1);
+          mma_tf32_ts(d1, a1_lo + 8 * j, b1_hi + 2 * j, kIdescN128, 1);
+        }
+        tc_commit(b_d1full);
+        for (int h = 0; h < 2 && ok; ++h) {
+          if (!mbar_wait(b_a2ready(h), ph, abort_flag, status, kErrA2Ready)) { ok = false; break; }
+          if (it >= 1 && !mbar_wait(b_d2empty(h), (it - 1) & 1, abort_flag, status, kErrD2Empty)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a2_hi = tmem_base + kColA2 + 128 * h, a2_lo = a2_hi + 64, d2 = tmem_base + kColD2 + 32 * h;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {   // product 2: K = 64 rows of this half in steps of 8
+            const int r = 64 * h + 8 * j;                         // first row of the step
+            const uint32_t off = (uint32_t)(r >> 5) * 4096u + (uint32_t)(r & 31) * 4u;
+            const uint64_t b2_hi = make_kmajor_sw128_desc(base + kOffB2 + off);
+            const uint64_t b2_lo = make_kmajor_sw128_desc(base + kOffB2 + kB2Bytes + off);
+            mma_tf32_ts(d2, a2_hi + 8 * j, b2_hi, kIdesc, j > 0);
+            mma_tf32_ts(d2, a2_hi + 8 * j, b2_lo, kIdesc, 1);
+            mma_tf32_ts(d2, a2_lo + 8 * j, b2_hi, kIdesc, 1);
+          }
+          tc_commit(b_a2free(h));
+          tc_commit(b_d2full(h));
+        }
+        if (ok) tc_commit(b_abfree);
+      }
+    }
+  } else if (warp < 4) {
+    // ---------------------------------------------------------------- row threads
+    const int t = threadIdx.x;
+    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    // rows j = 24..31 of d_raw^T stay zero for the whole kernel
+    for (uint32_t i = t; i < 2 * kB2Bytes / 16; i += 128)
+      asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(base + kOffB2 + i * 16), "r"(0u) : "memory");
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    bool ok = true;
+    for (int it = 0; it < nsub && ok; ++it) {
+      const int s = it & 1;
+      const int64_t row = g0 + (int64_t)it * kBM + t;
+      if (it >= 1 && !mbar_wait(b_abfree, (it - 1) & 1, abort_flag, status, kErrAbFree)) { ok = false; break; }
+      // ---- this row's d_raw (24 values) and coef
+      float dr[24], coef = 0.f;
+      if (row < g1) {
+        const float* q = buf + row * 56 + 24;
+#pragma unroll
+        for (int j = 0; j < 24; ++j) dr[j] = __ldg(q + j);
+        coef = __ldg(q + 24);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 24; ++j) dr[j] = 0.f;
+      }
+      uint32_t hi[32], lo[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        hi[j] = j < 24 ? tf32_rn(dr[j]) : 0u;
+        lo[j] = j < 24 ? tf32_rn(dr[j] - __uint_as_float(hi[j])) : 0u;
+      }
+      tmem_st32(tmem_base + lane_addr + kColA1, hi);
+      tmem_st32(tmem_base + lane_addr + kColA1 + 32, lo);
+      {   // d_raw^T: element (j, r = t) of block t / 32, 128-byte swizzle (16-byte chunk index ^ (j & 7))
+        const uint32_t blk = base + kOffB2 + (uint32_t)(t >> 5) * 4096u + (uint32_t)(t & 3) * 4u;
+        const uint32_t chunk = (uint32_t)(t & 31) >> 2;
+#pragma unroll
+        for (int j = 0; j < 24; ++j) {
+          const uint32_t a = blk + (uint32_t)j * 128u + ((chunk ^ (uint32_t)(j & 7)) << 4);
+          asm volatile("st.shared.b32 [%0], %1;" ::"r"(a), "r"(hi[j]) : "memory");
+          asm volatile("st.shared.b32 [%0], %1;" ::"r"(a + kB2Bytes), "r"(lo[j]) : "memory");
+        }
+      }
+      fence_async_smem();
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(b_a1);
+      // ---- epilogue of product 1: grad_x = D1 + coef * x, written over the x tile and stored by TMA
+      if (!mbar_wait(b_xfull(s), (it >> 1) & 1, abort_flag, status, kErrXFull)) { ok = false; break; }
+      if (!mbar_wait(b_xread(s), (it >> 1) & 1, abort_flag, status, kErrXRead)) { ok = false; break; }
+      if (!mbar_wait(b_d1full, it & 1, abort_flag, status, kErrD1Full)) { ok = false; break; }
+      tc_fence_after();
+#pragma unroll 1
+      for (int kk = 0; kk < 4; ++kk) {
+        uint32_t v[32];
+        tmem_ld32(tmem_base + lane_addr + kColD1 + 32 * kk, v);
+        tmem_wait_ld();
+        const uint32_t rowp = base + s * kXStage + kk * kXBytes + (uint32_t)t * 128u;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint32_t a = rowp + (uint32_t)((c ^ (t & 7)) << 4);
+          float4 xv;
+          asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(xv.x), "=f"(xv.y), "=f"(xv.z), "=f"(xv.w) : "r"(a) : "memory");
+          xv.x = fmaf(coef, xv.x, __uint_as_float(v[4 * c]));
+          xv.y = fmaf(coef, xv.y, __uint_as_float(v[4 * c + 1]));
+          xv.z = fmaf(coef, xv.z, __uint_as_float(v[4 * c + 2]));
+          xv.w = fmaf(coef, xv.w, __uint_as_float(v[4 * c + 3]));
+          asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(a), "f"(xv.x), "f"(xv.y), "f"(xv.z), "f"(xv.w) : "memory");
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(b_d1empty);
+      fence_async_smem();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (t == 0) {
+        const int r0 = (int)(g0 + (int64_t)it * kBM);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          tma_store_2d(&map_gx, (int)k0 + 32 * kk, r0, base + s * kXStage + kk * kXBytes);
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        mbar_arrive(b_xfree(s));
+      }
+    }
+    if (t == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  } else {
+    // ---------------------------------------------------------------- column threads (warps 4-7)
+    const int t = threadIdx.x - 128;           // k within the slab = lane of tensor memory
+    const int kk = t >> 5, c = t & 31;
+    const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t colp = (uint32_t)kk * kXBytes + (uint32_t)(c & 3) * 4u;
+    const uint32_t chunk = (uint32_t)c >> 2;
+    float acc[24];
+#pragma unroll
+    for (int j = 0; j < 24; ++j) acc[j] = 0.f;
+    bool ok = true;
+    for (int it = 0; it < nsub && ok; ++it) {
+      const int s = it & 1;
+      if (!mbar_wait(b_xfull(s), (it >> 1) & 1, abort_flag, status, kErrXFull)) { ok = false; break; }
+      const uint32_t tile = base + s * kXStage + colp;
+      for (int h = 0; h < 2 && ok; ++h) {
+        if (it >= 1 && !mbar_wait(b_a2free(h), (it - 1) & 1, abort_flag, status, kErrA2Free)) { ok = false; break; }
+#pragma unroll 1
+        for (int q = 0; q < 2; ++q) {            // 32 rows at a time
+          uint32_t hi[32], lo[32];
+#pragma unroll
+          for (int u = 0; u < 32; ++u) {
+            const uint32_t r = (uint32_t)(64 * h + 32 * q + u);
+            float xv;
+            asm volatile("ld.shared.f32 %0, [%1];" : "=f"(xv) : "r"(tile + r * 128u + ((chunk ^ (r & 7u)) << 4)) : "memory");
+            hi[u] = tf32_rn(xv);
+            lo[u] = tf32_rn(xv - __uint_as_float(hi[u]));
+          }
+          const uint32_t a2 = tmem_base + lane_addr + kColA2 + 128 * h + 32 * q;
+          tmem_st32(a2, hi);
+          tmem_st32(a2 + 64, lo);
+        }
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(b_a2ready(h));
+      }
+      if (!ok) break;
+      mbar_arrive(b_xread(s));                   // this thread no longer reads the x tile
+      for (int h = 0; h < 2 && ok; ++h) {        // grad_phi sums of this sub-tile's halves -> fp32 registers
+        if (!mbar_wait(b_d2full(h), it & 1, abort_flag, status, kErrD2Full)) { ok = false; break; }
+        tc_fence_after();
+        uint32_t v[32];
+        tmem_ld32(tmem_base + lane_addr + kColD2 + 32 * h, v);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 24; ++j) acc[j] += __uint_as_float(v[j]);
+        tc_fence_before();
+        mbar_arrive(b_d2empty(h));
+      }
+    }
+    const int64_t k = k0 + t;
+    if (k < K) {
+      float* o = phi_part + ((int64_t)blockIdx.y * K + k) * 24;
+      const float nanv = __int_as_float(0x7fc00000);
+#pragma unroll
+      for (int j = 0; j < 24; ++j) o[j] = ok ? acc[j] : nanv;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
 // ------------------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
