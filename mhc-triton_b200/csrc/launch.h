@@ -109,6 +109,10 @@ int rows_fwd_tc_launch(const float* x, const float* phi, BiasPtrs bias, const fl
                        const float* alpha_res, float* H_pre, float* H_post, float* H_res, float* saved, void* scratch,
                        int64_t batch, int64_t K, int iters, float eps, cudaStream_t st);
 
+int64_t rows_tc_bwd_scratch_floats(int64_t K);
+int rows_bwd_tc_launch(const float* x, const float* phi, const float* buf, float* phi_part, float* grad_x,
+                       float* scratch, int64_t batch, int64_t K, int max_groups, cudaStream_t st, int* groups_used);
+
 int64_t weights_fwd_scratch_bytes(int64_t batch, int64_t K);
 int64_t weights_bwd_scratch_bytes(int64_t batch, int64_t K);
 

@@ -548,8 +548,9 @@ k_dw_bwd_param_finish(const double* __restrict__ psum, int nctas, float* __restr
 
 // ------------------------------------------------------------------------------ host side
 int64_t rows_bwd_extra_floats(int64_t batch, int64_t K) {
-  // grad_phi partial sums per row tile, then the 27 fp64 column sums of each summing CTA (+ alignment slack)
-  return (int64_t)phi_row_tiles(batch) * K * 24 + (int64_t)kSumCtas * 27 * 2 + 2;
+  // grad_phi partial sums per row tile, then the 27 fp64 column sums of each summing CTA (+ alignment slack),
+  // then the tensor-core pass's split copy of phi (+ slack to align it to 256 bytes)
+  return (int64_t)phi_row_tiles(batch) * K * 24 + (int64_t)kSumCtas * 27 * 2 + 2 + 64 + rows_tc_bwd_scratch_floats(K);
 }
 
 // K slices per 128-row block for the tensor-core projection: the smallest count whose CTAs fill whole
@@ -599,8 +600,13 @@ int project_rows_launch(const float* x, const float* phi, float* part, int64_t b
 
 int bwd_rows_launch(const float* x, const float* phi, const float* buf, float* phi_part, float* grad_x, float* grad_phi,
                     float* grad_bias, float* grad_alpha, int64_t batch, int64_t K, int accumulate, cudaStream_t st) {
-  const int tiles = phi_row_tiles(batch);
-  if (K % 4 == 0 && is_aligned16(x)) {
+  int tiles = phi_row_tiles(batch);
+  const int64_t n_part = (int64_t)tiles * K * 24;
+  if (rows_tc_usable(x, batch, K) && is_aligned16(grad_x)) {   // tcgen05 pass; its scratch follows the column sums
+    float* tc_scratch = reinterpret_cast<float*>(
+        (reinterpret_cast<uintptr_t>(phi_part + n_part + (int64_t)kSumCtas * 27 * 2 + 2) + 255) & ~(uintptr_t)255);
+    if (int e = rows_bwd_tc_launch(x, phi, buf, phi_part, grad_x, tc_scratch, batch, K, tiles, st, &tiles)) return e;
+  } else if (K % 4 == 0 && is_aligned16(x)) {
     ProfScope ps("k_dw_bwd_x_rows_mma", st);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)((K + kTK - 1) / kTK), (unsigned)tiles);
@@ -617,14 +623,14 @@ int bwd_rows_launch(const float* x, const float* phi, const float* buf, float* p
     (void)cudaLaunchKernelEx(&cfg, k_dw_bwd_x_rows, x, phi, buf, grad_x, phi_part, batch, K, phi_rows_per_tile(batch));
   }
   if (int e = check_launch("dynamic_weights_bwd(x rows)")) return e;
-  const int64_t n = K * 24;
+  const int64_t n = K * 24;   // `tiles` sets of partial sums were written
   {
     ProfScope ps("k_dw_bwd_phi_finish", st);
     launch_k(k_dw_bwd_phi_finish, (unsigned)((n + 255) / 256), 256, 0, st, (const float*)phi_part, grad_phi, n, tiles,
              accumulate);
   }
   if (int e = check_launch("dynamic_weights_bwd(grad_phi finish)")) return e;
-  double* psum = reinterpret_cast<double*>((reinterpret_cast<uintptr_t>(phi_part + (int64_t)tiles * n) + 7) & ~(uintptr_t)7);
+  double* psum = reinterpret_cast<double*>((reinterpret_cast<uintptr_t>(phi_part + n_part) + 7) & ~(uintptr_t)7);
   int64_t nctas = (batch + 255) / 256;
   if (nctas > kSumCtas) nctas = kSumCtas;
   const int64_t rows_per_cta = (batch + nctas - 1) / nctas;

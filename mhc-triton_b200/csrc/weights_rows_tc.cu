@@ -10,7 +10,8 @@
 // triple the shared-memory traffic of an HBM-bound kernel, so the rows take the tensor-memory road:
 //
 //   warp 4 (one lane)   TMA producer: x tile [128 rows x 32 k] + the pre-split phi^T tiles (hi, lo)
-//                       [32 outputs x 32 k] per stage, three stages.
+//                       [32 outputs x 32 k] per stage, four stages (the x part of a stage is free again as
+//                       soon as the row threads hold it in registers, the phi part when its MMAs are done).
 //   warps 0-3           thread t owns row t: reads its 128 bytes of the x tile from shared memory,
 //                       splits them into hi / lo in registers, adds up x^2, and writes both halves to
 //                       tensor memory (tcgen05.st), lane t, as the A operand [128 x 32].
@@ -39,18 +40,18 @@ namespace tc {
 constexpr int kBM = 128;   // rows per CTA = lanes of tensor memory
 constexpr int kBK = 32;    // k per tile: 128 bytes of fp32, one swizzle span
 constexpr int kBN = 32;    // the 24 outputs, padded
-constexpr int kStages = 3;
+constexpr int kStages = 4;   // shared-memory stages in flight (TMA latency x HBM rate needs ~32 KiB of x per SM)
 constexpr uint32_t kXBytes = kBM * kBK * 4;          // 16 KiB
 constexpr uint32_t kPBytes = kBN * kBK * 4;          // 4 KiB
 constexpr uint32_t kStageBytes = kXBytes + 2 * kPBytes;
-constexpr uint32_t kTmemCols = 256;                  // A: 3 stages x (32 hi + 32 lo); D: 2 x 32
-constexpr uint32_t kColA = 0, kColD = kStages * 64;
+constexpr uint32_t kTmemCols = 256;                  // A: 2 buffers x (32 hi + 32 lo); D: 2 x 32  (two CTAs per SM)
+constexpr uint32_t kColA = 0, kColD = 128;
 constexpr int kThreads = 192;
 constexpr size_t kSmemBytes = 1024 + kStages * kStageBytes + 256;
 constexpr long long kWaitCycles = 2000000000LL;      // about one second
 
 // status word values (first int of the scratch): which wait ran out
-enum { kOk = 0, kErrFull = 1001, kErrAReady = 1002, kErrStageFree = 1003, kErrDFull = 1004, kErrDEmpty = 1005 };
+enum { kOk = 0, kErrFull = 1001, kErrAReady = 1002, kErrStageFree = 1003, kErrDFull = 1004, kErrDEmpty = 1005, kErrXReleased = 1006 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -208,13 +209,14 @@ k_dw_rows_fwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;   // tiles need 1024-byte alignment for the swizzle
   const uint32_t bars = base + kStages * kStageBytes;
-  // barriers: full[3] a_ready[3] stage_free[3] d_full[2] d_empty[2]
+  // barriers: full[S] x_free[S] b_free[S] a_ready[2] d_full[2] d_empty[2]
   auto bar_full = [&](int s) { return bars + 8u * s; };
-  auto bar_aready = [&](int s) { return bars + 8u * (kStages + s); };
+  auto bar_xfree = [&](int s) { return bars + 8u * (kStages + s); };
   auto bar_free = [&](int s) { return bars + 8u * (2 * kStages + s); };
-  auto bar_dfull = [&](int d) { return bars + 8u * (3 * kStages + d); };
-  auto bar_dempty = [&](int d) { return bars + 8u * (3 * kStages + 2 + d); };
-  const uint32_t holder = bars + 8u * (3 * kStages + 4);
+  auto bar_aready = [&](int a) { return bars + 8u * (3 * kStages + a); };
+  auto bar_dfull = [&](int d) { return bars + 8u * (3 * kStages + 2 + d); };
+  auto bar_dempty = [&](int d) { return bars + 8u * (3 * kStages + 4 + d); };
+  const uint32_t holder = bars + 8u * (3 * kStages + 6);
   __shared__ int s_abort;
   volatile int* abort_flag = &s_abort;
 
@@ -226,10 +228,11 @@ k_dw_rows_fwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     s_abort = 0;
     for (int s = 0; s < kStages; ++s) {
       mbar_init(bar_full(s), 1);
-      mbar_init(bar_aready(s), kBM);
+      mbar_init(bar_xfree(s), kBM);
       mbar_init(bar_free(s), 1);
     }
     for (int d = 0; d < 2; ++d) {
+      mbar_init(bar_aready(d), kBM);
       mbar_init(bar_dfull(d), 1);
       mbar_init(bar_dempty(d), kBM);
     }
@@ -247,7 +250,9 @@ k_dw_rows_fwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     if (lane == 0) {
       for (int i = 0; i < nk; ++i) {
         const int s = i % kStages;
-        if (i >= kStages && !mbar_wait(bar_free(s), ((i / kStages) - 1) & 1, abort_flag, status, kErrStageFree)) break;
+        if (i >= kStages && (!mbar_wait(bar_xfree(s), ((i / kStages) - 1) & 1, abort_flag, status, kErrXReleased) ||
+                             !mbar_wait(bar_free(s), ((i / kStages) - 1) & 1, abort_flag, status, kErrStageFree)))
+          break;
         const uint32_t dst = base + s * kStageBytes;
         mbar_expect_tx(bar_full(s), kStageBytes);
         tma_load_2d(dst, &map_x, i * kBK, (int)row0, bar_full(s));
@@ -259,24 +264,23 @@ k_dw_rows_fwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       for (int i = 0; i < nk; ++i) {
-        const int s = i % kStages, d = i & 1;
-        const uint32_t ph = (i / kStages) & 1;
-        if (!mbar_wait(bar_full(s), ph, abort_flag, status, kErrFull)) break;
-        if (!mbar_wait(bar_aready(s), ph, abort_flag, status, kErrAReady)) break;
+        const int s = i % kStages, d = i & 1;   // d: the A buffer and the accumulator of this tile
+        if (!mbar_wait(bar_full(s), (i / kStages) & 1, abort_flag, status, kErrFull)) break;
+        if (!mbar_wait(bar_aready(d), (i >> 1) & 1, abort_flag, status, kErrAReady)) break;
         if (i >= 2 && !mbar_wait(bar_dempty(d), ((i >> 1) - 1) & 1, abort_flag, status, kErrDEmpty)) break;
         tc_fence_after();
         const uint32_t stage = base + s * kStageBytes;
         const uint64_t b_hi = make_kmajor_sw128_desc(stage + kXBytes);
         const uint64_t b_lo = make_kmajor_sw128_desc(stage + kXBytes + kPBytes);
-        const uint32_t a_hi = tmem_base + kColA + s * 64, a_lo = a_hi + 32, dd = tmem_base + kColD + d * 32;
+        const uint32_t a_hi = tmem_base + kColA + d * 64, a_lo = a_hi + 32, dd = tmem_base + kColD + d * 32;
 #pragma unroll
         for (int j = 0; j < kBK / 8; ++j) {   // a k-step of 8 is 32 bytes of a swizzled row: descriptor address + 2
           mma_tf32_ts(dd, a_hi + 8 * j, b_hi + 2 * j, kIdesc, j > 0);
           mma_tf32_ts(dd, a_hi + 8 * j, b_lo + 2 * j, kIdesc, 1);
           mma_tf32_ts(dd, a_lo + 8 * j, b_hi + 2 * j, kIdesc, 1);
         }
-        tc_commit(bar_free(s));    // stage s (shared memory and its A columns) may be refilled
-        tc_commit(bar_dfull(d));   // accumulator d holds this tile's sums
+        tc_commit(bar_free(s));    // the phi tiles of stage s may be overwritten
+        tc_commit(bar_dfull(d));   // accumulator d holds this tile's sums (and A buffer d has been read)
       }
     }
   } else {
@@ -324,12 +328,14 @@ k_dw_rows_fwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         }
       }
       q += qt;
-      const uint32_t a_hi = tmem_base + lane_addr + kColA + s * 64;
+      mbar_arrive(bar_xfree(s));   // the tile is in registers
+      // A buffer i & 1 was last read by the MMAs of tile i - 2, whose accumulator this thread has already drained
+      const uint32_t a_hi = tmem_base + lane_addr + kColA + (i & 1) * 64;
       tmem_st32(a_hi, hi);
       tmem_st32(a_hi + 32, lo);
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(bar_aready(s));
+      mbar_arrive(bar_aready(i & 1));
       if (i >= 1) ok = drain(i - 1);
     }
     if (ok && nk > 0) ok = drain(nk - 1);
@@ -569,71 +575,78 @@ k_dw_rows_bwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     for (uint32_t i = t; i < 2 * kB2Bytes / 16; i += 128)
       asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(base + kOffB2 + i * 16), "r"(0u) : "memory");
     asm volatile("bar.sync 1, 128;" ::: "memory");
-    bool ok = true;
-    for (int it = 0; it < nsub && ok; ++it) {
+    for (int it = 0; it < nsub; ++it) {
       const int s = it & 1;
       const int64_t row = g0 + (int64_t)it * kBM + t;
-      if (it >= 1 && !mbar_wait(b_abfree, (it - 1) & 1, abort_flag, status, kErrAbFree)) { ok = false; break; }
-      // ---- this row's d_raw (24 values) and coef
-      float dr[24], coef = 0.f;
-      if (row < g1) {
-        const float* q = buf + row * 56 + 24;
+      // A failed (timed-out) wait must not leave the other row threads alone at the CTA-level barrier
+      // below: every thread reaches that barrier in every iteration, and all leave together after it.
+      bool good = it < 1 || mbar_wait(b_abfree, (it - 1) & 1, abort_flag, status, kErrAbFree);
+      float coef = 0.f;
+      if (good) {
+        // ---- this row's d_raw (24 values) and coef
+        float dr[24];
+        if (row < g1) {
+          const float* q = buf + row * 56 + 24;
 #pragma unroll
-        for (int j = 0; j < 24; ++j) dr[j] = __ldg(q + j);
-        coef = __ldg(q + 24);
-      } else {
+          for (int j = 0; j < 24; ++j) dr[j] = __ldg(q + j);
+          coef = __ldg(q + 24);
+        } else {
 #pragma unroll
-        for (int j = 0; j < 24; ++j) dr[j] = 0.f;
-      }
-      uint32_t hi[32], lo[32];
-#pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        hi[j] = j < 24 ? tf32_rn(dr[j]) : 0u;
-        lo[j] = j < 24 ? tf32_rn(dr[j] - __uint_as_float(hi[j])) : 0u;
-      }
-      tmem_st32(tmem_base + lane_addr + kColA1, hi);
-      tmem_st32(tmem_base + lane_addr + kColA1 + 32, lo);
-      {   // d_raw^T: element (j, r = t) of block t / 32, 128-byte swizzle (16-byte chunk index ^ (j & 7))
-        const uint32_t blk = base + kOffB2 + (uint32_t)(t >> 5) * 4096u + (uint32_t)(t & 3) * 4u;
-        const uint32_t chunk = (uint32_t)(t & 31) >> 2;
-#pragma unroll
-        for (int j = 0; j < 24; ++j) {
-          const uint32_t a = blk + (uint32_t)j * 128u + ((chunk ^ (uint32_t)(j & 7)) << 4);
-          asm volatile("st.shared.b32 [%0], %1;" ::"r"(a), "r"(hi[j]) : "memory");
-          asm volatile("st.shared.b32 [%0], %1;" ::"r"(a + kB2Bytes), "r"(lo[j]) : "memory");
+          for (int j = 0; j < 24; ++j) dr[j] = 0.f;
         }
+        uint32_t hi[32], lo[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          hi[j] = j < 24 ? tf32_rn(dr[j]) : 0u;
+          lo[j] = j < 24 ? tf32_rn(dr[j] - __uint_as_float(hi[j])) : 0u;
+        }
+        tmem_st32(tmem_base + lane_addr + kColA1, hi);
+        tmem_st32(tmem_base + lane_addr + kColA1 + 32, lo);
+        {   // d_raw^T: element (j, r = t) of block t / 32, 128-byte swizzle (16-byte chunk index ^ (j & 7))
+          const uint32_t blk = base + kOffB2 + (uint32_t)(t >> 5) * 4096u + (uint32_t)(t & 3) * 4u;
+          const uint32_t chunk = (uint32_t)(t & 31) >> 2;
+#pragma unroll
+          for (int j = 0; j < 24; ++j) {
+            const uint32_t a = blk + (uint32_t)j * 128u + ((chunk ^ (uint32_t)(j & 7)) << 4);
+            asm volatile("st.shared.b32 [%0], %1;" ::"r"(a), "r"(hi[j]) : "memory");
+            asm volatile("st.shared.b32 [%0], %1;" ::"r"(a + kB2Bytes), "r"(lo[j]) : "memory");
+          }
+        }
+        fence_async_smem();
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(b_a1);
       }
-      fence_async_smem();
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(b_a1);
       // ---- epilogue of product 1: grad_x = D1 + coef * x, written over the x tile and stored by TMA
-      if (!mbar_wait(b_xfull(s), (it >> 1) & 1, abort_flag, status, kErrXFull)) { ok = false; break; }
-      if (!mbar_wait(b_xread(s), (it >> 1) & 1, abort_flag, status, kErrXRead)) { ok = false; break; }
-      if (!mbar_wait(b_d1full, it & 1, abort_flag, status, kErrD1Full)) { ok = false; break; }
-      tc_fence_after();
+      good = good && mbar_wait(b_xfull(s), (it >> 1) & 1, abort_flag, status, kErrXFull) &&
+             mbar_wait(b_xread(s), (it >> 1) & 1, abort_flag, status, kErrXRead) &&
+             mbar_wait(b_d1full, it & 1, abort_flag, status, kErrD1Full);
+      if (good) {
+        tc_fence_after();
 #pragma unroll 1
-      for (int kk = 0; kk < 4; ++kk) {
-        uint32_t v[32];
-        tmem_ld32(tmem_base + lane_addr + kColD1 + 32 * kk, v);
-        tmem_wait_ld();
-        const uint32_t rowp = base + s * kXStage + kk * kXBytes + (uint32_t)t * 128u;
+        for (int kk = 0; kk < 4; ++kk) {
+          uint32_t v[32];
+          tmem_ld32(tmem_base + lane_addr + kColD1 + 32 * kk, v);
+          tmem_wait_ld();
+          const uint32_t rowp = base + s * kXStage + kk * kXBytes + (uint32_t)t * 128u;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          const uint32_t a = rowp + (uint32_t)((c ^ (t & 7)) << 4);
-          float4 xv;
-          asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(xv.x), "=f"(xv.y), "=f"(xv.z), "=f"(xv.w) : "r"(a) : "memory");
-          xv.x = fmaf(coef, xv.x, __uint_as_float(v[4 * c]));
-          xv.y = fmaf(coef, xv.y, __uint_as_float(v[4 * c + 1]));
-          xv.z = fmaf(coef, xv.z, __uint_as_float(v[4 * c + 2]));
-          xv.w = fmaf(coef, xv.w, __uint_as_float(v[4 * c + 3]));
-          asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(a), "f"(xv.x), "f"(xv.y), "f"(xv.z), "f"(xv.w) : "memory");
+          for (int c = 0; c < 8; ++c) {
+            const uint32_t a = rowp + (uint32_t)((c ^ (t & 7)) << 4);
+            float4 xv;
+            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(xv.x), "=f"(xv.y), "=f"(xv.z), "=f"(xv.w) : "r"(a) : "memory");
+            xv.x = fmaf(coef, xv.x, __uint_as_float(v[4 * c]));
+            xv.y = fmaf(coef, xv.y, __uint_as_float(v[4 * c + 1]));
+            xv.z = fmaf(coef, xv.z, __uint_as_float(v[4 * c + 2]));
+            xv.w = fmaf(coef, xv.w, __uint_as_float(v[4 * c + 3]));
+            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(a), "f"(xv.x), "f"(xv.y), "f"(xv.z), "f"(xv.w) : "memory");
+          }
         }
+        tc_fence_before();
+        mbar_arrive(b_d1empty);
+        fence_async_smem();
       }
-      tc_fence_before();
-      mbar_arrive(b_d1empty);
-      fence_async_smem();
       asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (*abort_flag) break;   // the same answer for all 128 threads: set before the barrier or not at all
       if (t == 0) {
         const int r0 = (int)(g0 + (int64_t)it * kBM);
 #pragma unroll
@@ -764,6 +777,58 @@ int64_t rows_tc_fwd_scratch_bytes(int64_t K) { return 256 + 2 * 32 * round_up(K,
 bool rows_tc_usable(const float* x, int64_t batch, int64_t K) {
   return tc::enabled() && batch >= kManyRows && K % 4 == 0 && K >= 4 && is_aligned16(x) && batch < (1LL << 31) &&
          K < (1LL << 31) && tc::encode_fn() != nullptr;
+}
+
+// Scratch of the tensor-core backward, in floats: a 256-byte header (status word) + phi hi and lo [Kp, 32]
+// with Kp = K rounded up to the slab of 128.
+int64_t rows_tc_bwd_scratch_floats(int64_t K) { return 64 + 2 * 32 * round_up(K, tc::bw::kSlab); }
+
+// The pass over x of the many-rows backward on tcgen05.  Row groups (one set of grad_phi partial sums each)
+// are multiples of 128 rows so that no two CTAs ever store to the same rows of grad_x; *groups_used tells
+// the caller how many sets to add up.
+int rows_bwd_tc_launch(const float* x, const float* phi, const float* buf, float* phi_part, float* grad_x,
+                       float* scratch, int64_t batch, int64_t K, int max_groups, cudaStream_t st, int* groups_used) {
+  using namespace tc;
+  if (!is_aligned16(scratch) || !is_aligned16(grad_x))
+    return fail(MHC_ERR_MISALIGNED, "dynamic_weights_bwd: scratch and grad_x must be 16-byte aligned");
+  const int64_t Kp = round_up(K, bw::kSlab);
+  int* status = (int*)scratch;
+  float* phi_hi = scratch + 64;
+  float* phi_lo = phi_hi + 32 * Kp;
+  if (max_groups < 1) max_groups = 1;
+  const int64_t rows_per_group = round_up((batch + max_groups - 1) / max_groups, kBM);
+  const int64_t groups = (batch + rows_per_group - 1) / rows_per_group;
+  CUtensorMap mx, mg, mh, ml;
+  if (!make_map_2d(&mx, x, batch, K, kBM) || !make_map_2d(&mg, grad_x, batch, K, kBM) ||
+      !make_map_2d(&mh, phi_hi, Kp, 32, bw::kSlab) || !make_map_2d(&ml, phi_lo, Kp, 32, bw::kSlab))
+    return fail(MHC_ERR_CUDA, "dynamic_weights_bwd: cuTensorMapEncodeTiled failed");
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(k_dw_rows_bwd_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bw::kSmem) != cudaSuccess)
+      return check_launch("dynamic_weights_bwd(tc attribute)");
+    attr_set = true;
+  }
+  {
+    ProfScope ps("k_phi_split_rows", st);
+    launch_k(k_phi_split_rows, (unsigned)((32 * Kp + 255) / 256), 256, 0, st, phi, phi_hi, phi_lo, K, Kp, status);
+  }
+  if (int e = check_launch("dynamic_weights_bwd(phi split)")) return e;
+  {
+    ProfScope ps("k_dw_rows_bwd_tc", st);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(Kp / bw::kSlab), (unsigned)groups);
+    cfg.blockDim = dim3(bw::kThreadsBwd);
+    cfg.dynamicSmemBytes = bw::kSmem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    (void)cudaLaunchKernelEx(&cfg, k_dw_rows_bwd_tc, mx, mg, mh, ml, buf, phi_part, batch, K, rows_per_group, status);
+  }
+  *groups_used = (int)groups;
+  return check_launch("dynamic_weights_bwd(tc)");
 }
 
 int rows_fwd_tc_launch(const float* x, const float* phi, BiasPtrs bias, const float* alpha_pre, const float* alpha_post,

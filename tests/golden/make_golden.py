@@ -188,7 +188,7 @@ def gen_layer_small(ref):
 
 
 def c1_inputs():
-    """BASELINE config 1 inputs: seed 0, H then the upstream gradient."""
+    """Config 1 inputs (fp32 H of shape (2, 128, 4, 512)): seed 0, H then the upstream gradient."""
     torch.manual_seed(0)
     H = torch.randn(2, 128, 4, 512)
     g = torch.randn(2, 128, 4, 512)

@@ -692,7 +692,7 @@ def test_per_token_weights_through_reshape():
 
 
 @pytest.mark.parametrize("B,K", [(64, 4 * 64), (200, 4 * 100 + 4), (1000, 4 * 256), (130, 4 * 33 + 2), (300, 4 * 1100),
-                                 (2500, 4 * 128)])
+                                 (2500, 4 * 128), (4096 + 17, 2048), (129, 128)])
 def test_dynamic_weights_many_rows(B, K):
     """From 64 rows on the op switches to kernels tiled over rows (per-token use); same results.
     Covers the register-tiled projection (K % 4 == 0) with one and with several K slices, the scalar

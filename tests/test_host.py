@@ -69,10 +69,13 @@ def test_scratch_sizes():
     few = lib.mhc_scratch_bytes(_lib.OP_DYNAMIC_WEIGHTS_BWD, 16, 0, D, 0)
     assert few == 16 * 56 * 4
     many = lib.mhc_scratch_bytes(_lib.OP_DYNAMIC_WEIGHTS_BWD, 32768, 0, D, 0)
-    assert many == 4 * (32768 * 56 + 32 * K * 24 + 64 * 27 * 2 + 2)
+    tc = 64 + 64 + 2 * 32 * K     # the tensor-core pass: alignment slack, status header, phi split in two [K, 32]
+    assert many == 4 * (32768 * 56 + 32 * K * 24 + 64 * 27 * 2 + 2 + tc)
     one_tile = lib.mhc_scratch_bytes(_lib.OP_DYNAMIC_WEIGHTS_BWD, 100, 0, D, 0)
-    assert one_tile == 4 * (100 * 56 + 1 * K * 24 + 64 * 27 * 2 + 2)
-    # forward: [row, K slice, 25] partial sums with at most 128 slices of at least 256 k
+    assert one_tile == 4 * (100 * 56 + 1 * K * 24 + 64 * 27 * 2 + 2 + tc)
+    # forward: [row, K slice, 25] partial sums with at most 128 slices of at least 256 k (few rows); from 64 rows on
+    # at least the tensor-core projection's split copy of phi (256-byte header + two [32, K] arrays)
+    assert lib.mhc_scratch_bytes(_lib.OP_DYNAMIC_WEIGHTS_FWD, 64, 0, D, 0) == 256 + 2 * 32 * K * 4
     assert lib.mhc_scratch_bytes(_lib.OP_DYNAMIC_WEIGHTS_FWD, 8, 0, D, 0) == 8 * 64 * 25 * 4
 
 
