@@ -5,7 +5,7 @@
 // so one kernel goes from x to (H_pre, H_post, H_res, saved).
 //
 // fp32 parity needs more than one TF32 product: x = hi + lo and phi = hi + lo (each half rounded to
-// TF32), and x * phi ~ hi*hi + hi*lo + lo*hi.  The tensor core reads its B operand from shared
+// TF32), and x * phi = hi*hi + hi*lo + lo*hi (+ lo*lo, which comes for free here).  The tensor core reads its B operand from shared
 // memory and its A operand from shared OR tensor memory; splitting x inside shared memory would
 // triple the shared-memory traffic of an HBM-bound kernel, so the rows take the tensor-memory road:
 //
@@ -15,8 +15,9 @@
 //   warps 0-3           thread t owns row t: reads its 128 bytes of the x tile from shared memory,
 //                       splits them into hi / lo in registers, adds up x^2, and writes both halves to
 //                       tensor memory (tcgen05.st), lane t, as the A operand [128 x 32].
-//   warp 5 (one lane)   issues 4 k-steps x 3 products of tcgen05.mma (M 128, N 32, K 8) per tile into
-//                       one of two accumulators [128 x 32] in tensor memory, then tcgen05.commit.
+//   warp 5 (one lane)   issues 4 k-steps x 2 products of tcgen05.mma (M 128, N 64, K 8) per tile: x_hi and
+//                       x_lo, each against [phi_hi | phi_lo] side by side, into one of two accumulators
+//                       [128 x 64] in tensor memory (the two halves are added when drained), then tcgen05.commit.
 //   warps 0-3 again     drain the accumulator of the previous tile (tcgen05.ld) into fp32 registers:
 //                       the tensor core starts every 32-deep tile from zero and the running sums are
 //                       ordinary round-to-nearest fp32 adds, which keeps its truncating adds out of
@@ -34,6 +35,18 @@
 #include "common.cuh"
 #include "launch.h"
 
+// Build with -DMHC_TC_TIMING to make one thread of each role of CTA 0 add up the cycles it spends in each phase
+// of its loop into the scratch header (ints 8.. of the status block); a development aid, off by default.
+#ifdef MHC_TC_TIMING
+#define TC_TIMING_DECL(n) long long tc_t_[n] = {}; long long tc_last_ = clock64(); const bool tc_on_ = blockIdx.x == 0 && blockIdx.y == 0
+#define TC_T(i) do { if (tc_on_) { const long long now_ = clock64(); tc_t_[i] += now_ - tc_last_; tc_last_ = now_; } } while (0)
+#define TC_TIMING_FLUSH(status, off, n) do { if (tc_on_) for (int i_ = 0; i_ < (n); ++i_) (status)[8 + (off) + i_] = (int)(tc_t_[i_] >> 4); } while (0)
+#else
+#define TC_TIMING_DECL(n)
+#define TC_T(i)
+#define TC_TIMING_FLUSH(status, off, n)
+#endif
+
 namespace mhc {
 namespace tc {
 
@@ -44,8 +57,9 @@ constexpr int kStages = 4;   // shared-memory stages in flight (TMA latency x HB
 constexpr uint32_t kXBytes = kBM * kBK * 4;          // 16 KiB
 constexpr uint32_t kPBytes = kBN * kBK * 4;          // 4 KiB
 constexpr uint32_t kStageBytes = kXBytes + 2 * kPBytes;
-constexpr uint32_t kTmemCols = 256;                  // A: 2 buffers x (32 hi + 32 lo); D: 2 x 32  (two CTAs per SM)
+constexpr uint32_t kTmemCols = 256;                  // A: 2 buffers x (32 hi + 32 lo); D: 2 x 64  (two CTAs per SM)
 constexpr uint32_t kColA = 0, kColD = 128;
+constexpr int kDCols = 64;                           // an accumulator holds A * [phi_hi | phi_lo]
 constexpr int kThreads = 192;
 constexpr size_t kSmemBytes = 1024 + kStages * kStageBytes + 256;
 constexpr long long kWaitCycles = 2000000000LL;      // about one second
@@ -63,6 +77,13 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 }
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// One arrival per WARP (barriers that count warps are initialised with the number of warps): the
+// lanes' earlier writes and tensor-memory operations are ordered before lane 0's arrive by the warp
+// barrier.  128 single-thread arrivals per tile on one shared-memory word cost more than the tile's math.
+__device__ __forceinline__ void mbar_arrive_warp(uint32_t bar) {
+  __syncwarp();
+  if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
 }
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
@@ -94,6 +115,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// The same for a whole warp waiting on one barrier: the answer is made warp-uniform, so that the lanes of a
+// warp never part ways at a wait that ran out (they arrive on barriers together, see mbar_arrive_warp).
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+  const bool ok = mbar_wait(bar, parity, abort_flag, status, code);
+  return __all_sync(0xffffffffu, ok);
+}
+
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
@@ -114,7 +142,10 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
-// D[128 x 32] (+)= A[128 x 8] (tensor memory) * B[32 x 8]^T (shared memory, K-major), TF32 inputs, fp32 sums.
+// D[128 x N] (+)= A[128 x 8] (tensor memory) * B[N x 8]^T (shared memory, K-major), TF32 inputs, fp32 sums.
+// One such instruction occupies the tensor core for roughly 85 cycles whether N is 32 or 64 (measured),
+// so the kernels below concatenate the hi and lo halves of B along N and issue two products per k-step
+// instead of three.
 __device__ __forceinline__ void mma_tf32_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
@@ -141,6 +172,7 @@ __device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
 // Instruction descriptor: fp32 accumulator (bits [4,6) = 1), A and B TF32 (bits [7,10) = [10,13) = 2),
 // both K-major (bits 15, 16 = 0), N >> 3 in bits [17,23), M >> 4 in bits [24,29).
 constexpr uint32_t kIdesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+constexpr uint32_t kIdescN64 = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(64 >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
 
 #define MHC_R32(a) a[0], a[1], a[2], a[3], a[4], a[5], a[6], a[7], a[8], a[9], a[10], a[11], a[12], a[13], a[14], a[15], \
                    a[16], a[17], a[18], a[19], a[20], a[21], a[22], a[23], a[24], a[25], a[26], a[27], a[28], a[29], a[30], a[31]
@@ -228,13 +260,13 @@ k_dw_rows_fwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     s_abort = 0;
     for (int s = 0; s < kStages; ++s) {
       mbar_init(bar_full(s), 1);
-      mbar_init(bar_xfree(s), kBM);
+      mbar_init(bar_xfree(s), kBM / 32);
       mbar_init(bar_free(s), 1);
     }
     for (int d = 0; d < 2; ++d) {
-      mbar_init(bar_aready(d), kBM);
+      mbar_init(bar_aready(d), kBM / 32);
       mbar_init(bar_dfull(d), 1);
-      mbar_init(bar_dempty(d), kBM);
+      mbar_init(bar_dempty(d), kBM / 32);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -248,40 +280,49 @@ k_dw_rows_fwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
   if (warp == 4) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
+      TC_TIMING_DECL(3);
       for (int i = 0; i < nk; ++i) {
         const int s = i % kStages;
-        if (i >= kStages && (!mbar_wait(bar_xfree(s), ((i / kStages) - 1) & 1, abort_flag, status, kErrXReleased) ||
-                             !mbar_wait(bar_free(s), ((i / kStages) - 1) & 1, abort_flag, status, kErrStageFree)))
-          break;
+        if (i >= kStages && !mbar_wait(bar_xfree(s), ((i / kStages) - 1) & 1, abort_flag, status, kErrXReleased)) break;
+        TC_T(0);
+        if (i >= kStages && !mbar_wait(bar_free(s), ((i / kStages) - 1) & 1, abort_flag, status, kErrStageFree)) break;
+        TC_T(1);
         const uint32_t dst = base + s * kStageBytes;
         mbar_expect_tx(bar_full(s), kStageBytes);
         tma_load_2d(dst, &map_x, i * kBK, (int)row0, bar_full(s));
         tma_load_2d(dst + kXBytes, &map_phi_hi, i * kBK, 0, bar_full(s));
         tma_load_2d(dst + kXBytes + kPBytes, &map_phi_lo, i * kBK, 0, bar_full(s));
+        TC_T(2);
       }
+      TC_TIMING_FLUSH(status, 0, 3);
     }
   } else if (warp == 5) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
+      TC_TIMING_DECL(4);
       for (int i = 0; i < nk; ++i) {
         const int s = i % kStages, d = i & 1;   // d: the A buffer and the accumulator of this tile
         if (!mbar_wait(bar_full(s), (i / kStages) & 1, abort_flag, status, kErrFull)) break;
+        TC_T(0);
         if (!mbar_wait(bar_aready(d), (i >> 1) & 1, abort_flag, status, kErrAReady)) break;
+        TC_T(1);
         if (i >= 2 && !mbar_wait(bar_dempty(d), ((i >> 1) - 1) & 1, abort_flag, status, kErrDEmpty)) break;
+        TC_T(2);
         tc_fence_after();
         const uint32_t stage = base + s * kStageBytes;
-        const uint64_t b_hi = make_kmajor_sw128_desc(stage + kXBytes);
-        const uint64_t b_lo = make_kmajor_sw128_desc(stage + kXBytes + kPBytes);
-        const uint32_t a_hi = tmem_base + kColA + d * 64, a_lo = a_hi + 32, dd = tmem_base + kColD + d * 32;
+        // phi_hi (32 rows) and phi_lo (32 rows) lie back to back: one K-major tile of 64 rows
+        const uint64_t b_cat = make_kmajor_sw128_desc(stage + kXBytes);
+        const uint32_t a_hi = tmem_base + kColA + d * 64, a_lo = a_hi + 32, dd = tmem_base + kColD + d * kDCols;
 #pragma unroll
         for (int j = 0; j < kBK / 8; ++j) {   // a k-step of 8 is 32 bytes of a swizzled row: descriptor address + 2
-          mma_tf32_ts(dd, a_hi + 8 * j, b_hi + 2 * j, kIdesc, j > 0);
-          mma_tf32_ts(dd, a_hi + 8 * j, b_lo + 2 * j, kIdesc, 1);
-          mma_tf32_ts(dd, a_lo + 8 * j, b_hi + 2 * j, kIdesc, 1);
+          mma_tf32_ts(dd, a_hi + 8 * j, b_cat + 2 * j, kIdescN64, j > 0);   // columns 0..31: hi*hi, 32..63: hi*lo
+          mma_tf32_ts(dd, a_lo + 8 * j, b_cat + 2 * j, kIdescN64, 1);       //                lo*hi,          lo*lo
         }
         tc_commit(bar_free(s));    // the phi tiles of stage s may be overwritten
         tc_commit(bar_dfull(d));   // accumulator d holds this tile's sums (and A buffer d has been read)
+        TC_T(3);
       }
+      TC_TIMING_FLUSH(status, 4, 4);
     }
   } else {
     // ------------------------------------------------------------------ rows: split, accumulate, finish
@@ -292,22 +333,28 @@ k_dw_rows_fwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     for (int j = 0; j < 24; ++j) acc[j] = 0.f;
     float q = 0.f;
     bool ok = true;
+    TC_TIMING_DECL(8);
     auto drain = [&](int i) {   // add tile i's accumulator to the running sums
       const int d = i & 1;
-      if (!mbar_wait(bar_dfull(d), (i >> 1) & 1, abort_flag, status, kErrDFull)) return false;
+      if (!mbar_wait_warp(bar_dfull(d), (i >> 1) & 1, abort_flag, status, kErrDFull)) return false;
+      TC_T(4);
       tc_fence_after();
-      uint32_t v[32];
-      tmem_ld32(tmem_base + lane_addr + kColD + d * 32, v);
+      uint32_t v[32], w[32];
+      tmem_ld32(tmem_base + lane_addr + kColD + d * kDCols, v);
+      tmem_ld32(tmem_base + lane_addr + kColD + d * kDCols + 32, w);
       tmem_wait_ld();
+      TC_T(5);
 #pragma unroll
-      for (int j = 0; j < 24; ++j) acc[j] += __uint_as_float(v[j]);
+      for (int j = 0; j < 24; ++j) acc[j] += __uint_as_float(v[j]) + __uint_as_float(w[j]);
       tc_fence_before();
-      mbar_arrive(bar_dempty(d));
+      mbar_arrive_warp(bar_dempty(d));
+      TC_T(6);
       return true;
     };
     for (int i = 0; i < nk && ok; ++i) {
       const int s = i % kStages;
-      if (!mbar_wait(bar_full(s), (i / kStages) & 1, abort_flag, status, kErrFull)) { ok = false; break; }
+      if (!mbar_wait_warp(bar_full(s), (i / kStages) & 1, abort_flag, status, kErrFull)) { ok = false; break; }
+      TC_T(0);
       const uint32_t rowp = base + s * kStageBytes + (uint32_t)t * 128u;
       uint32_t hi[32], lo[32];
       float qt = 0.f;
@@ -328,17 +375,21 @@ k_dw_rows_fwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         }
       }
       q += qt;
-      mbar_arrive(bar_xfree(s));   // the tile is in registers
+      TC_T(1);
+      mbar_arrive_warp(bar_xfree(s));   // the tile is in registers
       // A buffer i & 1 was last read by the MMAs of tile i - 2, whose accumulator this thread has already drained
       const uint32_t a_hi = tmem_base + lane_addr + kColA + (i & 1) * 64;
       tmem_st32(a_hi, hi);
       tmem_st32(a_hi + 32, lo);
       tmem_wait_st();
+      TC_T(2);
       tc_fence_before();
-      mbar_arrive(bar_aready(i & 1));
+      mbar_arrive_warp(bar_aready(i & 1));
+      TC_T(3);
       if (i >= 1) ok = drain(i - 1);
     }
     if (ok && nk > 0) ok = drain(nk - 1);
+    TC_TIMING_FLUSH(status, 8, 7);
     const int64_t row = row0 + t;
     if (row < rows) {
       const float nanv = __int_as_float(0x7fc00000);
@@ -402,30 +453,31 @@ k_dw_rows_fwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 //                         [128 k x 32 j] in shared memory (loaded once per CTA), D1 [128 rows x 128 k].
 //   product 2 (grad_phi): A = x^T hi/lo [128 k x 64 rows] per half sub-tile in tensor memory (thread t of
 //                         warps 4-7 owns k = t: it reads its column of the x tile from shared memory,
-//                         splits it and writes lane t), B = d_raw^T hi/lo [32 j x 128 rows] written to
-//                         shared memory by the row threads in the swizzled K-major layout, D2 [128 k x 32 j]
-//                         per half, drained into fp32 registers after every half.
-//   warps 0-3 (row threads)     d_raw / coef of their row -> A of product 1 and B of product 2; later
-//                               the epilogue: D1 + coef * x, written over the x tile in place and
-//                               stored by TMA.
+//                         splits it and writes lane t), B = [d_raw^T hi | d_raw^T lo] (N = 64) written to
+//                         shared memory by the row threads in the swizzled K-major layout, D2 [128 k x 64]
+//                         per sub-tile (two products per k-step instead of three), drained into fp32
+//                         registers after every sub-tile.
+//   warps 0-3 (row threads)     d_raw / coef of their row (fetched one sub-tile ahead) -> A of product 1 and
+//                               B of product 2; later the epilogue: D1 + coef * x written over the x tile.
 //   warps 4-7 (column threads)  x^T halves -> tensor memory; running sums of grad_phi.
-//   warp 8 (one lane)           TMA loads: phi slab once, x sub-tiles (two stages of 64 KiB).
+//   warp 8 (one lane)           TMA: phi slab once, x sub-tiles (two stages of 64 KiB), and the stores of the
+//                               finished grad_x tiles; a stage is reloaded as soon as its store has read it.
 //   warp 9 (one lane)           all tcgen05.mma and tcgen05.commit.
-// Tensor memory: A1 64 + D1 128 + A2 2 x 128 + D2 2 x 32 = 512 columns (one CTA per SM).
+// Tensor memory: A1 64 + D1 128 + A2 2 x 128 + D2 64 = 512 columns (one CTA per SM).
 // ======================================================================================
 namespace bw {
 constexpr int kSlab = 128;                         // k per CTA
 constexpr uint32_t kXStage = 4 * kXBytes;          // 64 KiB: four [128 rows x 32 k] tiles
 constexpr uint32_t kOffB1 = 2 * kXStage;           // phi slab hi, lo: 2 x 16 KiB
 constexpr uint32_t kB1Bytes = kSlab * 32 * 4;
-constexpr uint32_t kOffB2 = kOffB1 + 2 * kB1Bytes; // d_raw^T hi, lo: 2 x 16 KiB (4 blocks of [32 j x 32 rows])
+constexpr uint32_t kOffB2 = kOffB1 + 2 * kB1Bytes; // d_raw^T: 4 blocks (32 rows of x each) of [hi 32 j-rows | lo 32 j-rows] x 128 bytes
 constexpr uint32_t kB2Bytes = 32 * 128 * 4;
 constexpr uint32_t kOffBars = kOffB2 + 2 * kB2Bytes;
 constexpr size_t kSmem = 1024 + kOffBars + 256;
 constexpr int kThreadsBwd = 320;
-constexpr uint32_t kColA1 = 0, kColD1 = 64, kColA2 = 192, kColD2 = 448;   // A2 half h at kColA2 + 128 h (hi 64, lo 64)
+constexpr uint32_t kColA1 = 0, kColD1 = 64, kColA2 = 192, kColD2 = 448;   // A2 half h at kColA2 + 128 h (hi 64, lo 64); D2 64
 constexpr uint32_t kIdescN128 = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-enum { kErrPhi = 2001, kErrXFull = 2002, kErrXFree = 2003, kErrXRead = 2004, kErrA1 = 2005, kErrAbFree = 2006,
+enum { kErrPhi = 2001, kErrXFull = 2002, kErrStore = 2003, kErrXRead = 2004, kErrA1 = 2005, kErrAbFree = 2006,
        kErrA2Ready = 2007, kErrA2Free = 2008, kErrD1Full = 2009, kErrD1Empty = 2010, kErrD2Full = 2011, kErrD2Empty = 2012 };
 }  // namespace bw
 
@@ -466,17 +518,16 @@ k_dw_rows_bwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bars = base + kOffBars;
-  // barriers (8 bytes each)
+  // barriers (8 bytes each); those the row / column threads arrive on count warps (4)
   const uint32_t b_phi = bars;
   auto b_xfull = [&](int s) { return bars + 8u * (1 + s); };
-  auto b_xfree = [&](int s) { return bars + 8u * (3 + s); };
-  auto b_xread = [&](int s) { return bars + 8u * (5 + s); };
+  auto b_store = [&](int s) { return bars + 8u * (3 + s); };    // the row threads have written grad_x over stage s
+  auto b_xread = [&](int s) { return bars + 8u * (5 + s); };    // the column threads have read stage s
   const uint32_t b_a1 = bars + 8u * 7, b_abfree = bars + 8u * 8;
   auto b_a2ready = [&](int h) { return bars + 8u * (9 + h); };
   auto b_a2free = [&](int h) { return bars + 8u * (11 + h); };
   const uint32_t b_d1full = bars + 8u * 13, b_d1empty = bars + 8u * 14;
-  auto b_d2full = [&](int h) { return bars + 8u * (15 + h); };
-  auto b_d2empty = [&](int h) { return bars + 8u * (17 + h); };
+  const uint32_t b_d2full = bars + 8u * 15, b_d2empty = bars + 8u * 16;
   const uint32_t holder = bars + 8u * 19;
   __shared__ int s_abort;
   volatile int* abort_flag = &s_abort;
@@ -492,17 +543,17 @@ k_dw_rows_bwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     mbar_init(b_phi, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(b_xfull(s), 1);
-      mbar_init(b_xfree(s), 1);
-      mbar_init(b_xread(s), 128);
-      mbar_init(b_a2ready(s), 128);
+      mbar_init(b_store(s), 4);
+      mbar_init(b_xread(s), 4);
+      mbar_init(b_a2ready(s), 4);
       mbar_init(b_a2free(s), 1);
-      mbar_init(b_d2full(s), 1);
-      mbar_init(b_d2empty(s), 128);
     }
-    mbar_init(b_a1, 128);
+    mbar_init(b_a1, 4);
     mbar_init(b_abfree, 1);
     mbar_init(b_d1full, 1);
-    mbar_init(b_d1empty, 128);
+    mbar_init(b_d1empty, 4);
+    mbar_init(b_d2full, 1);
+    mbar_init(b_d2empty, 4);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 9) tmem_alloc(holder, 512);
@@ -513,30 +564,55 @@ k_dw_rows_bwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
   asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(holder) : "memory");
 
   if (warp == 8) {
-    // ---------------------------------------------------------------- TMA loads
+    // ---------------------------------------------------------------- TMA: loads, and the stores of grad_x
     if (lane == 0) {
-      mbar_expect_tx(b_phi, 2 * kB1Bytes);
-      tma_load_2d(base + kOffB1, &map_phi_hi, 0, (int)k0, b_phi);
-      tma_load_2d(base + kOffB1 + kB1Bytes, &map_phi_lo, 0, (int)k0, b_phi);
-      for (int it = 0; it < nsub; ++it) {
+      TC_TIMING_DECL(4);
+      auto load_x = [&](int it) {
         const int s = it & 1;
-        if (it >= 2 && !mbar_wait(b_xfree(s), ((it >> 1) - 1) & 1, abort_flag, status, kErrXFree)) break;
         mbar_expect_tx(b_xfull(s), kXStage);
         const int r0 = (int)(g0 + (int64_t)it * kBM);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
           tma_load_2d(base + s * kXStage + kk * kXBytes, &map_x, (int)k0 + 32 * kk, r0, b_xfull(s));
+      };
+      mbar_expect_tx(b_phi, 2 * kB1Bytes);
+      tma_load_2d(base + kOffB1, &map_phi_hi, 0, (int)k0, b_phi);
+      tma_load_2d(base + kOffB1 + kB1Bytes, &map_phi_lo, 0, (int)k0, b_phi);
+      load_x(0);
+      if (nsub > 1) load_x(1);
+      for (int it = 0; it < nsub; ++it) {
+        const int s = it & 1;
+        TC_T(3);
+        if (!mbar_wait(b_store(s), (it >> 1) & 1, abort_flag, status, kErrStore)) break;
+        TC_T(0);
+        const int r0 = (int)(g0 + (int64_t)it * kBM);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          tma_store_2d(&map_gx, (int)k0 + 32 * kk, r0, base + s * kXStage + kk * kXBytes);
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        TC_T(1);
+        if (it + 2 < nsub) {   // the stage is refilled as soon as the stores have read it
+          asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          load_x(it + 2);
+        }
+        TC_T(2);
       }
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+      TC_TIMING_FLUSH(status, 24, 4);
     }
   } else if (warp == 9) {
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0) {
+      TC_TIMING_DECL(8);
       bool ok = mbar_wait(b_phi, 0, abort_flag, status, kErrPhi);
       const uint64_t b1_hi = make_kmajor_sw128_desc(base + kOffB1), b1_lo = make_kmajor_sw128_desc(base + kOffB1 + kB1Bytes);
       for (int it = 0; it < nsub && ok; ++it) {
         const uint32_t ph = it & 1;
+        TC_T(7);
         if (!mbar_wait(b_a1, ph, abort_flag, status, kErrA1)) break;
+        TC_T(0);
         if (it >= 1 && !mbar_wait(b_d1empty, (it - 1) & 1, abort_flag, status, kErrD1Empty)) break;
+        TC_T(1);
         tc_fence_after();
         const uint32_t a1_hi = tmem_base + kColA1, a1_lo = a1_hi + 32, d1 = tmem_base + kColD1;
 #pragma unroll
@@ -546,118 +622,132 @@ k_dw_rows_bwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
           mma_tf32_ts(d1, a1_lo + 8 * j, b1_hi + 2 * j, kIdescN128, 1);
         }
         tc_commit(b_d1full);
+        TC_T(2);
+        const uint32_t d2 = tmem_base + kColD2;
         for (int h = 0; h < 2 && ok; ++h) {
           if (!mbar_wait(b_a2ready(h), ph, abort_flag, status, kErrA2Ready)) { ok = false; break; }
-          if (it >= 1 && !mbar_wait(b_d2empty(h), (it - 1) & 1, abort_flag, status, kErrD2Empty)) { ok = false; break; }
+          TC_T(3);
+          if (h == 0 && it >= 1 && !mbar_wait(b_d2empty, (it - 1) & 1, abort_flag, status, kErrD2Empty)) { ok = false; break; }
+          TC_T(4);
           tc_fence_after();
-          const uint32_t a2_hi = tmem_base + kColA2 + 128 * h, a2_lo = a2_hi + 64, d2 = tmem_base + kColD2 + 32 * h;
+          const uint32_t a2_hi = tmem_base + kColA2 + 128 * h, a2_lo = a2_hi + 64;
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {   // product 2: K = 64 rows of this half in steps of 8
+          for (int j = 0; j < 8; ++j) {   // product 2: K = 64 rows of this half in steps of 8, B = [d_hi | d_lo] (N = 64)
             const int r = 64 * h + 8 * j;                         // first row of the step
-            const uint32_t off = (uint32_t)(r >> 5) * 4096u + (uint32_t)(r & 31) * 4u;
-            const uint64_t b2_hi = make_kmajor_sw128_desc(base + kOffB2 + off);
-            const uint64_t b2_lo = make_kmajor_sw128_desc(base + kOffB2 + kB2Bytes + off);
-            mma_tf32_ts(d2, a2_hi + 8 * j, b2_hi, kIdesc, j > 0);
-            mma_tf32_ts(d2, a2_hi + 8 * j, b2_lo, kIdesc, 1);
-            mma_tf32_ts(d2, a2_lo + 8 * j, b2_hi, kIdesc, 1);
+            const uint64_t b2 = make_kmajor_sw128_desc(base + kOffB2 + (uint32_t)(r >> 5) * 8192u + (uint32_t)(r & 31) * 4u);
+            mma_tf32_ts(d2, a2_hi + 8 * j, b2, kIdescN64, (h | j) > 0);
+            mma_tf32_ts(d2, a2_lo + 8 * j, b2, kIdescN64, 1);
           }
           tc_commit(b_a2free(h));
-          tc_commit(b_d2full(h));
+          TC_T(5);
         }
-        if (ok) tc_commit(b_abfree);
+        if (ok) {
+          tc_commit(b_d2full);
+          tc_commit(b_abfree);
+        }
+        TC_T(6);
       }
+      TC_TIMING_FLUSH(status, 0, 8);
     }
   } else if (warp < 4) {
     // ---------------------------------------------------------------- row threads
     const int t = threadIdx.x;
     const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
-    // rows j = 24..31 of d_raw^T stay zero for the whole kernel
+    // rows j = 24..31 of both halves of d_raw^T stay zero for the whole kernel
     for (uint32_t i = t; i < 2 * kB2Bytes / 16; i += 128)
       asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(base + kOffB2 + i * 16), "r"(0u) : "memory");
     asm volatile("bar.sync 1, 128;" ::: "memory");
-    for (int it = 0; it < nsub; ++it) {
-      const int s = it & 1;
+    TC_TIMING_DECL(8);
+    // this row's d_raw (24 values) and coef, fetched one sub-tile ahead
+    float4 dq[6];
+    float coef_next = 0.f;
+    auto fetch = [&](int it) {
       const int64_t row = g0 + (int64_t)it * kBM + t;
-      // A failed (timed-out) wait must not leave the other row threads alone at the CTA-level barrier
-      // below: every thread reaches that barrier in every iteration, and all leave together after it.
-      bool good = it < 1 || mbar_wait(b_abfree, (it - 1) & 1, abort_flag, status, kErrAbFree);
-      float coef = 0.f;
-      if (good) {
-        // ---- this row's d_raw (24 values) and coef
-        float dr[24];
-        if (row < g1) {
-          const float* q = buf + row * 56 + 24;
+      if (it < nsub && row < g1) {
+        const float* q = buf + row * 56 + 24;   // 16-byte aligned: rows are 224 bytes, the offset 96
 #pragma unroll
-          for (int j = 0; j < 24; ++j) dr[j] = __ldg(q + j);
-          coef = __ldg(q + 24);
-        } else {
+        for (int i = 0; i < 6; ++i) dq[i] = __ldg(reinterpret_cast<const float4*>(q) + i);
+        coef_next = __ldg(q + 24);
+      } else {
 #pragma unroll
-          for (int j = 0; j < 24; ++j) dr[j] = 0.f;
-        }
+        for (int i = 0; i < 6; ++i) dq[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        coef_next = 0.f;
+      }
+    };
+    fetch(0);
+    bool good = true;
+    for (int it = 0; it < nsub && good; ++it) {
+      const int s = it & 1;
+      TC_T(7);
+      if (it >= 1 && !mbar_wait_warp(b_abfree, (it - 1) & 1, abort_flag, status, kErrAbFree)) break;
+      TC_T(0);
+      const float coef = coef_next;
+      {
         uint32_t hi[32], lo[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          hi[j] = j < 24 ? tf32_rn(dr[j]) : 0u;
-          lo[j] = j < 24 ? tf32_rn(dr[j] - __uint_as_float(hi[j])) : 0u;
+        for (int i = 0; i < 6; ++i) {
+          const float e[4] = {dq[i].x, dq[i].y, dq[i].z, dq[i].w};
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            hi[4 * i + u] = tf32_rn(e[u]);
+            lo[4 * i + u] = tf32_rn(e[u] - __uint_as_float(hi[4 * i + u]));
+          }
         }
+#pragma unroll
+        for (int j = 24; j < 32; ++j) { hi[j] = 0u; lo[j] = 0u; }
         tmem_st32(tmem_base + lane_addr + kColA1, hi);
         tmem_st32(tmem_base + lane_addr + kColA1 + 32, lo);
-        {   // d_raw^T: element (j, r = t) of block t / 32, 128-byte swizzle (16-byte chunk index ^ (j & 7))
-          const uint32_t blk = base + kOffB2 + (uint32_t)(t >> 5) * 4096u + (uint32_t)(t & 3) * 4u;
-          const uint32_t chunk = (uint32_t)(t & 31) >> 2;
+        // d_raw^T: element (j, r = t) of block t / 32 = [hi: 32 j-rows x 128 bytes][lo: the same], 128-byte
+        // swizzle (16-byte chunk index ^ (j & 7)): one K-major tile of 64 rows per block of 32 rows of x
+        const uint32_t blk = base + kOffB2 + (uint32_t)(t >> 5) * 8192u + (uint32_t)(t & 3) * 4u;
+        const uint32_t chunk = (uint32_t)(t & 31) >> 2;
 #pragma unroll
-          for (int j = 0; j < 24; ++j) {
-            const uint32_t a = blk + (uint32_t)j * 128u + ((chunk ^ (uint32_t)(j & 7)) << 4);
-            asm volatile("st.shared.b32 [%0], %1;" ::"r"(a), "r"(hi[j]) : "memory");
-            asm volatile("st.shared.b32 [%0], %1;" ::"r"(a + kB2Bytes), "r"(lo[j]) : "memory");
-          }
+        for (int j = 0; j < 24; ++j) {
+          const uint32_t a = blk + (uint32_t)j * 128u + ((chunk ^ (uint32_t)(j & 7)) << 4);
+          asm volatile("st.shared.b32 [%0], %1;" ::"r"(a), "r"(hi[j]) : "memory");
+          asm volatile("st.shared.b32 [%0], %1;" ::"r"(a + 4096u), "r"(lo[j]) : "memory");
         }
-        fence_async_smem();
-        tmem_wait_st();
-        tc_fence_before();
-        mbar_arrive(b_a1);
       }
-      // ---- epilogue of product 1: grad_x = D1 + coef * x, written over the x tile and stored by TMA
-      good = good && mbar_wait(b_xfull(s), (it >> 1) & 1, abort_flag, status, kErrXFull) &&
-             mbar_wait(b_xread(s), (it >> 1) & 1, abort_flag, status, kErrXRead) &&
-             mbar_wait(b_d1full, it & 1, abort_flag, status, kErrD1Full);
-      if (good) {
-        tc_fence_after();
-#pragma unroll 1
-        for (int kk = 0; kk < 4; ++kk) {
-          uint32_t v[32];
-          tmem_ld32(tmem_base + lane_addr + kColD1 + 32 * kk, v);
-          tmem_wait_ld();
-          const uint32_t rowp = base + s * kXStage + kk * kXBytes + (uint32_t)t * 128u;
+      fence_async_smem();
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive_warp(b_a1);
+      fetch(it + 1);   // in flight during the waits and the epilogue below
+      TC_T(1);
+      // ---- epilogue of product 1: grad_x = D1 + coef * x, written over the x tile; the TMA warp stores it
+      if (!mbar_wait_warp(b_xfull(s), (it >> 1) & 1, abort_flag, status, kErrXFull)) break;
+      TC_T(2);
+      if (!mbar_wait_warp(b_xread(s), (it >> 1) & 1, abort_flag, status, kErrXRead)) break;
+      TC_T(3);
+      if (!mbar_wait_warp(b_d1full, it & 1, abort_flag, status, kErrD1Full)) break;
+      TC_T(4);
+      tc_fence_after();
+      uint32_t v[2][32];
+      tmem_ld32(tmem_base + lane_addr + kColD1, v[0]);
 #pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            const uint32_t a = rowp + (uint32_t)((c ^ (t & 7)) << 4);
-            float4 xv;
-            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(xv.x), "=f"(xv.y), "=f"(xv.z), "=f"(xv.w) : "r"(a) : "memory");
-            xv.x = fmaf(coef, xv.x, __uint_as_float(v[4 * c]));
-            xv.y = fmaf(coef, xv.y, __uint_as_float(v[4 * c + 1]));
-            xv.z = fmaf(coef, xv.z, __uint_as_float(v[4 * c + 2]));
-            xv.w = fmaf(coef, xv.w, __uint_as_float(v[4 * c + 3]));
-            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(a), "f"(xv.x), "f"(xv.y), "f"(xv.z), "f"(xv.w) : "memory");
-          }
+      for (int kk = 0; kk < 4; ++kk) {
+        tmem_wait_ld();
+        if (kk + 1 < 4) tmem_ld32(tmem_base + lane_addr + kColD1 + 32 * (kk + 1), v[(kk + 1) & 1]);   // next quarter in flight
+        const uint32_t rowp = base + s * kXStage + kk * kXBytes + (uint32_t)t * 128u;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint32_t a = rowp + (uint32_t)((c ^ (t & 7)) << 4);
+          float4 xv;
+          asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(xv.x), "=f"(xv.y), "=f"(xv.z), "=f"(xv.w) : "r"(a) : "memory");
+          xv.x = fmaf(coef, xv.x, __uint_as_float(v[kk & 1][4 * c]));
+          xv.y = fmaf(coef, xv.y, __uint_as_float(v[kk & 1][4 * c + 1]));
+          xv.z = fmaf(coef, xv.z, __uint_as_float(v[kk & 1][4 * c + 2]));
+          xv.w = fmaf(coef, xv.w, __uint_as_float(v[kk & 1][4 * c + 3]));
+          asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(a), "f"(xv.x), "f"(xv.y), "f"(xv.z), "f"(xv.w) : "memory");
         }
-        tc_fence_before();
-        mbar_arrive(b_d1empty);
-        fence_async_smem();
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (*abort_flag) break;   // the same answer for all 128 threads: set before the barrier or not at all
-      if (t == 0) {
-        const int r0 = (int)(g0 + (int64_t)it * kBM);
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          tma_store_2d(&map_gx, (int)k0 + 32 * kk, r0, base + s * kXStage + kk * kXBytes);
-        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-        mbar_arrive(b_xfree(s));
-      }
+      tc_fence_before();
+      mbar_arrive_warp(b_d1empty);
+      fence_async_smem();
+      mbar_arrive_warp(b_store(s));
+      TC_T(5);
     }
-    if (t == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    if (t == 0) TC_TIMING_FLUSH(status, 8, 8);
   } else {
     // ---------------------------------------------------------------- column threads (warps 4-7)
     const int t = threadIdx.x - 128;           // k within the slab = lane of tensor memory
@@ -669,12 +759,15 @@ k_dw_rows_bwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 #pragma unroll
     for (int j = 0; j < 24; ++j) acc[j] = 0.f;
     bool ok = true;
+    TC_TIMING_DECL(6);
     for (int it = 0; it < nsub && ok; ++it) {
       const int s = it & 1;
-      if (!mbar_wait(b_xfull(s), (it >> 1) & 1, abort_flag, status, kErrXFull)) { ok = false; break; }
+      if (!mbar_wait_warp(b_xfull(s), (it >> 1) & 1, abort_flag, status, kErrXFull)) { ok = false; break; }
+      TC_T(0);
       const uint32_t tile = base + s * kXStage + colp;
       for (int h = 0; h < 2 && ok; ++h) {
-        if (it >= 1 && !mbar_wait(b_a2free(h), (it - 1) & 1, abort_flag, status, kErrA2Free)) { ok = false; break; }
+        if (it >= 1 && !mbar_wait_warp(b_a2free(h), (it - 1) & 1, abort_flag, status, kErrA2Free)) { ok = false; break; }
+        TC_T(1);
 #pragma unroll 1
         for (int q = 0; q < 2; ++q) {            // 32 rows at a time
           uint32_t hi[32], lo[32];
@@ -692,22 +785,26 @@ k_dw_rows_bwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         }
         tmem_wait_st();
         tc_fence_before();
-        mbar_arrive(b_a2ready(h));
+        mbar_arrive_warp(b_a2ready(h));
+        TC_T(2);
       }
       if (!ok) break;
-      mbar_arrive(b_xread(s));                   // this thread no longer reads the x tile
-      for (int h = 0; h < 2 && ok; ++h) {        // grad_phi sums of this sub-tile's halves -> fp32 registers
-        if (!mbar_wait(b_d2full(h), it & 1, abort_flag, status, kErrD2Full)) { ok = false; break; }
-        tc_fence_after();
-        uint32_t v[32];
-        tmem_ld32(tmem_base + lane_addr + kColD2 + 32 * h, v);
-        tmem_wait_ld();
+      mbar_arrive_warp(b_xread(s));              // this warp no longer reads the x tile
+      // grad_phi sums of this sub-tile -> fp32 registers (columns 0..31: x_hi*d_hi + x_lo*d_hi, 32..63: the d_lo terms)
+      if (!mbar_wait_warp(b_d2full, it & 1, abort_flag, status, kErrD2Full)) { ok = false; break; }
+      TC_T(3);
+      tc_fence_after();
+      uint32_t v[32], w[32];
+      tmem_ld32(tmem_base + lane_addr + kColD2, v);
+      tmem_ld32(tmem_base + lane_addr + kColD2 + 32, w);
+      tmem_wait_ld();
 #pragma unroll
-        for (int j = 0; j < 24; ++j) acc[j] += __uint_as_float(v[j]);
-        tc_fence_before();
-        mbar_arrive(b_d2empty(h));
-      }
+      for (int j = 0; j < 24; ++j) acc[j] += __uint_as_float(v[j]) + __uint_as_float(w[j]);
+      tc_fence_before();
+      mbar_arrive_warp(b_d2empty);
+      TC_T(4);
     }
+    if (t == 0) TC_TIMING_FLUSH(status, 16, 5);
     const int64_t k = k0 + t;
     if (k < K) {
       float* o = phi_part + ((int64_t)blockIdx.y * K + k) * 24;
