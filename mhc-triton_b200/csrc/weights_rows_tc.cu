@@ -358,14 +358,16 @@ k_dw_rows_fwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       const uint32_t rowp = base + s * kStageBytes + (uint32_t)t * 128u;
       uint32_t hi[32], lo[32];
       float qt = 0.f;
+      float4 xr[8];
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {   // 16-byte chunk c of row t sits at chunk position c ^ (t & 7)
-        float4 v;
+      for (int c = 0; c < 8; ++c)   // 16-byte chunk c of row t sits at chunk position c ^ (t & 7); all loads first
         asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
-                     : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                     : "=f"(xr[c].x), "=f"(xr[c].y), "=f"(xr[c].z), "=f"(xr[c].w)
                      : "r"(rowp + (uint32_t)((c ^ (t & 7)) << 4))
                      : "memory");
-        const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const float e[4] = {xr[c].x, xr[c].y, xr[c].z, xr[c].w};
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
           const uint32_t h = tf32_rn(e[u]);
@@ -457,9 +459,9 @@ k_dw_rows_fwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 //                         shared memory by the row threads in the swizzled K-major layout, D2 [128 k x 64]
 //                         per sub-tile (two products per k-step instead of three), drained into fp32
 //                         registers after every sub-tile.
-//   warps 0-3 (row threads)     d_raw / coef of their row (fetched one sub-tile ahead) -> A of product 1 and
-//                               B of product 2; later the epilogue: D1 + coef * x written over the x tile.
+//   warps 0-3 (row threads)     d_raw of their row (fetched one sub-tile ahead) -> A of product 1 and B of product 2.
 //   warps 4-7 (column threads)  x^T halves -> tensor memory; running sums of grad_phi.
+//   warps 10-13 (epilogue)      thread = row: D1 + coef * x written over the x tile in place.
 //   warp 8 (one lane)           TMA: phi slab once, x sub-tiles (two stages of 64 KiB), and the stores of the
 //                               finished grad_x tiles; a stage is reloaded as soon as its store has read it.
 //   warp 9 (one lane)           all tcgen05.mma and tcgen05.commit.
@@ -474,7 +476,7 @@ constexpr uint32_t kOffB2 = kOffB1 + 2 * kB1Bytes; // d_raw^T: 4 blocks (32 rows
 constexpr uint32_t kB2Bytes = 32 * 128 * 4;
 constexpr uint32_t kOffBars = kOffB2 + 2 * kB2Bytes;
 constexpr size_t kSmem = 1024 + kOffBars + 256;
-constexpr int kThreadsBwd = 320;
+constexpr int kThreadsBwd = 448;
 constexpr uint32_t kColA1 = 0, kColD1 = 64, kColA2 = 192, kColD2 = 448;   // A2 half h at kColA2 + 128 h (hi 64, lo 64); D2 64
 constexpr uint32_t kIdescN128 = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 enum { kErrPhi = 2001, kErrXFull = 2002, kErrStore = 2003, kErrXRead = 2004, kErrA1 = 2005, kErrAbFree = 2006,
@@ -650,7 +652,7 @@ k_dw_rows_bwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       TC_TIMING_FLUSH(status, 0, 8);
     }
   } else if (warp < 4) {
-    // ---------------------------------------------------------------- row threads
+    // ---------------------------------------------------------------- row threads: operands from d_raw
     const int t = threadIdx.x;
     const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
     // rows j = 24..31 of both halves of d_raw^T stay zero for the whole kernel
@@ -658,20 +660,17 @@ k_dw_rows_bwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(base + kOffB2 + i * 16), "r"(0u) : "memory");
     asm volatile("bar.sync 1, 128;" ::: "memory");
     TC_TIMING_DECL(8);
-    // this row's d_raw (24 values) and coef, fetched one sub-tile ahead
+    // this row's d_raw (24 values), fetched one sub-tile ahead
     float4 dq[6];
-    float coef_next = 0.f;
     auto fetch = [&](int it) {
       const int64_t row = g0 + (int64_t)it * kBM + t;
       if (it < nsub && row < g1) {
         const float* q = buf + row * 56 + 24;   // 16-byte aligned: rows are 224 bytes, the offset 96
 #pragma unroll
         for (int i = 0; i < 6; ++i) dq[i] = __ldg(reinterpret_cast<const float4*>(q) + i);
-        coef_next = __ldg(q + 24);
       } else {
 #pragma unroll
         for (int i = 0; i < 6; ++i) dq[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-        coef_next = 0.f;
       }
     };
     fetch(0);
@@ -681,7 +680,6 @@ k_dw_rows_bwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       TC_T(7);
       if (it >= 1 && !mbar_wait_warp(b_abfree, (it - 1) & 1, abort_flag, status, kErrAbFree)) break;
       TC_T(0);
-      const float coef = coef_next;
       {
         uint32_t hi[32], lo[32];
 #pragma unroll
@@ -697,6 +695,7 @@ k_dw_rows_bwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         for (int j = 24; j < 32; ++j) { hi[j] = 0u; lo[j] = 0u; }
         tmem_st32(tmem_base + lane_addr + kColA1, hi);
         tmem_st32(tmem_base + lane_addr + kColA1 + 32, lo);
+        TC_T(6);
         // d_raw^T: element (j, r = t) of block t / 32 = [hi: 32 j-rows x 128 bytes][lo: the same], 128-byte
         // swizzle (16-byte chunk index ^ (j & 7)): one K-major tile of 64 rows per block of 32 rows of x
         const uint32_t blk = base + kOffB2 + (uint32_t)(t >> 5) * 8192u + (uint32_t)(t & 3) * 4u;
@@ -712,9 +711,27 @@ k_dw_rows_bwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive_warp(b_a1);
-      fetch(it + 1);   // in flight during the waits and the epilogue below
+      fetch(it + 1);   // in flight while the products of this sub-tile run
       TC_T(1);
-      // ---- epilogue of product 1: grad_x = D1 + coef * x, written over the x tile; the TMA warp stores it
+    }
+    if (t == 0) TC_TIMING_FLUSH(status, 8, 8);
+  } else if (warp >= 10) {
+    // ---------------------------------------------------------------- epilogue threads (warps 10-13)
+    // grad_x = D1 + coef * x, written over the x tile in place; the TMA warp stores it.  A warp reaches the
+    // lanes 32 * (warp % 4) .. + 31 of tensor memory, and the lane is the row.
+    const int t = (warp & 3) * 32 + lane;
+    const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+    TC_TIMING_DECL(8);
+    auto coef_of = [&](int it) {
+      const int64_t row = g0 + (int64_t)it * kBM + t;
+      return (it < nsub && row < g1) ? __ldg(buf + row * 56 + 48) : 0.f;
+    };
+    float coef_next = coef_of(0);
+    for (int it = 0; it < nsub; ++it) {
+      const int s = it & 1;
+      const float coef = coef_next;
+      coef_next = coef_of(it + 1);
+      TC_T(7);
       if (!mbar_wait_warp(b_xfull(s), (it >> 1) & 1, abort_flag, status, kErrXFull)) break;
       TC_T(2);
       if (!mbar_wait_warp(b_xread(s), (it >> 1) & 1, abort_flag, status, kErrXRead)) break;
@@ -729,17 +746,25 @@ k_dw_rows_bwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         tmem_wait_ld();
         if (kk + 1 < 4) tmem_ld32(tmem_base + lane_addr + kColD1 + 32 * (kk + 1), v[(kk + 1) & 1]);   // next quarter in flight
         const uint32_t rowp = base + s * kXStage + kk * kXBytes + (uint32_t)t * 128u;
+        float4 xv[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c)   // all loads first, then the arithmetic, then the stores
+          asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                       : "=f"(xv[c].x), "=f"(xv[c].y), "=f"(xv[c].z), "=f"(xv[c].w)
+                       : "r"(rowp + (uint32_t)((c ^ (t & 7)) << 4))
+                       : "memory");
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
-          const uint32_t a = rowp + (uint32_t)((c ^ (t & 7)) << 4);
-          float4 xv;
-          asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(xv.x), "=f"(xv.y), "=f"(xv.z), "=f"(xv.w) : "r"(a) : "memory");
-          xv.x = fmaf(coef, xv.x, __uint_as_float(v[kk & 1][4 * c]));
-          xv.y = fmaf(coef, xv.y, __uint_as_float(v[kk & 1][4 * c + 1]));
-          xv.z = fmaf(coef, xv.z, __uint_as_float(v[kk & 1][4 * c + 2]));
-          xv.w = fmaf(coef, xv.w, __uint_as_float(v[kk & 1][4 * c + 3]));
-          asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(a), "f"(xv.x), "f"(xv.y), "f"(xv.z), "f"(xv.w) : "memory");
+          xv[c].x = fmaf(coef, xv[c].x, __uint_as_float(v[kk & 1][4 * c]));
+          xv[c].y = fmaf(coef, xv[c].y, __uint_as_float(v[kk & 1][4 * c + 1]));
+          xv[c].z = fmaf(coef, xv[c].z, __uint_as_float(v[kk & 1][4 * c + 2]));
+          xv[c].w = fmaf(coef, xv[c].w, __uint_as_float(v[kk & 1][4 * c + 3]));
         }
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};"
+                       ::"r"(rowp + (uint32_t)((c ^ (t & 7)) << 4)), "f"(xv[c].x), "f"(xv[c].y), "f"(xv[c].z), "f"(xv[c].w)
+                       : "memory");
       }
       tc_fence_before();
       mbar_arrive_warp(b_d1empty);
@@ -747,8 +772,8 @@ k_dw_rows_bwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       mbar_arrive_warp(b_store(s));
       TC_T(5);
     }
-    if (t == 0) TC_TIMING_FLUSH(status, 8, 8);
-  } else {
+    if (t == 0) TC_TIMING_FLUSH(status, 28, 8);
+  } else if (warp < 8) {
     // ---------------------------------------------------------------- column threads (warps 4-7)
     const int t = threadIdx.x - 128;           // k within the slab = lane of tensor memory
     const int kk = t >> 5, c = t & 31;
@@ -771,13 +796,16 @@ k_dw_rows_bwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 #pragma unroll 1
         for (int q = 0; q < 2; ++q) {            // 32 rows at a time
           uint32_t hi[32], lo[32];
+          float xc[32];
+#pragma unroll
+          for (int u = 0; u < 32; ++u) {   // all loads first
+            const uint32_t r = (uint32_t)(64 * h + 32 * q + u);
+            asm volatile("ld.shared.f32 %0, [%1];" : "=f"(xc[u]) : "r"(tile + r * 128u + ((chunk ^ (r & 7u)) << 4)) : "memory");
+          }
 #pragma unroll
           for (int u = 0; u < 32; ++u) {
-            const uint32_t r = (uint32_t)(64 * h + 32 * q + u);
-            float xv;
-            asm volatile("ld.shared.f32 %0, [%1];" : "=f"(xv) : "r"(tile + r * 128u + ((chunk ^ (r & 7u)) << 4)) : "memory");
-            hi[u] = tf32_rn(xv);
-            lo[u] = tf32_rn(xv - __uint_as_float(hi[u]));
+            hi[u] = tf32_rn(xc[u]);
+            lo[u] = tf32_rn(xc[u] - __uint_as_float(hi[u]));
           }
           const uint32_t a2 = tmem_base + lane_addr + kColA2 + 128 * h + 32 * q;
           tmem_st32(a2, hi);
