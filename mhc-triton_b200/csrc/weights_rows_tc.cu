@@ -480,7 +480,8 @@ constexpr int kThreadsBwd = 448;
 constexpr uint32_t kColA1 = 0, kColD1 = 64, kColA2 = 192, kColD2 = 448;   // A2 half h at kColA2 + 128 h (hi 64, lo 64); D2 64
 constexpr uint32_t kIdescN128 = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 enum { kErrPhi = 2001, kErrXFull = 2002, kErrStore = 2003, kErrXRead = 2004, kErrA1 = 2005, kErrAbFree = 2006,
-       kErrA2Ready = 2007, kErrA2Free = 2008, kErrD1Full = 2009, kErrD1Empty = 2010, kErrD2Full = 2011, kErrD2Empty = 2012 };
+       kErrA2Ready = 2007, kErrA2Free = 2008, kErrD1Full = 2009, kErrD1Empty = 2010, kErrD2Full = 2011, kErrD2Empty = 2012,
+       kErrB2 = 2013 };
 }  // namespace bw
 
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int y, uint32_t src) {
@@ -525,7 +526,8 @@ k_dw_rows_bwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
   auto b_xfull = [&](int s) { return bars + 8u * (1 + s); };
   auto b_store = [&](int s) { return bars + 8u * (3 + s); };    // the row threads have written grad_x over stage s
   auto b_xread = [&](int s) { return bars + 8u * (5 + s); };    // the column threads have read stage s
-  const uint32_t b_a1 = bars + 8u * 7, b_abfree = bars + 8u * 8;
+  const uint32_t b_a1 = bars + 8u * 7, b_b2free = bars + 8u * 8;   // A1 written / the products have read d_raw^T
+  const uint32_t b_a1free = bars + 8u * 17, b_b2 = bars + 8u * 18;    // product 1 has read A1 / d_raw^T written
   auto b_a2ready = [&](int h) { return bars + 8u * (9 + h); };
   auto b_a2free = [&](int h) { return bars + 8u * (11 + h); };
   const uint32_t b_d1full = bars + 8u * 13, b_d1empty = bars + 8u * 14;
@@ -551,7 +553,9 @@ k_dw_rows_bwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       mbar_init(b_a2free(s), 1);
     }
     mbar_init(b_a1, 4);
-    mbar_init(b_abfree, 1);
+    mbar_init(b_b2, 4);
+    mbar_init(b_a1free, 1);
+    mbar_init(b_b2free, 1);
     mbar_init(b_d1full, 1);
     mbar_init(b_d1empty, 4);
     mbar_init(b_d2full, 1);
@@ -624,7 +628,9 @@ k_dw_rows_bwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
           mma_tf32_ts(d1, a1_lo + 8 * j, b1_hi + 2 * j, kIdescN128, 1);
         }
         tc_commit(b_d1full);
+        tc_commit(b_a1free);       // the row threads may write the next sub-tile's A1 while product 2 runs
         TC_T(2);
+        if (!mbar_wait(b_b2, ph, abort_flag, status, kErrB2)) break;
         const uint32_t d2 = tmem_base + kColD2;
         for (int h = 0; h < 2 && ok; ++h) {
           if (!mbar_wait(b_a2ready(h), ph, abort_flag, status, kErrA2Ready)) { ok = false; break; }
@@ -645,7 +651,7 @@ k_dw_rows_bwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         }
         if (ok) {
           tc_commit(b_d2full);
-          tc_commit(b_abfree);
+          tc_commit(b_b2free);
         }
         TC_T(6);
       }
@@ -678,26 +684,32 @@ k_dw_rows_bwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     for (int it = 0; it < nsub && good; ++it) {
       const int s = it & 1;
       TC_T(7);
-      if (it >= 1 && !mbar_wait_warp(b_abfree, (it - 1) & 1, abort_flag, status, kErrAbFree)) break;
+      if (it >= 1 && !mbar_wait_warp(b_a1free, (it - 1) & 1, abort_flag, status, kErrAbFree)) break;
       TC_T(0);
-      {
-        uint32_t hi[32], lo[32];
+      uint32_t hi[32], lo[32];
 #pragma unroll
-        for (int i = 0; i < 6; ++i) {
-          const float e[4] = {dq[i].x, dq[i].y, dq[i].z, dq[i].w};
+      for (int i = 0; i < 6; ++i) {
+        const float e[4] = {dq[i].x, dq[i].y, dq[i].z, dq[i].w};
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            hi[4 * i + u] = tf32_rn(e[u]);
-            lo[4 * i + u] = tf32_rn(e[u] - __uint_as_float(hi[4 * i + u]));
-          }
+        for (int u = 0; u < 4; ++u) {
+          hi[4 * i + u] = tf32_rn(e[u]);
+          lo[4 * i + u] = tf32_rn(e[u] - __uint_as_float(hi[4 * i + u]));
         }
+      }
 #pragma unroll
-        for (int j = 24; j < 32; ++j) { hi[j] = 0u; lo[j] = 0u; }
-        tmem_st32(tmem_base + lane_addr + kColA1, hi);
-        tmem_st32(tmem_base + lane_addr + kColA1 + 32, lo);
-        TC_T(6);
-        // d_raw^T: element (j, r = t) of block t / 32 = [hi: 32 j-rows x 128 bytes][lo: the same], 128-byte
-        // swizzle (16-byte chunk index ^ (j & 7)): one K-major tile of 64 rows per block of 32 rows of x
+      for (int j = 24; j < 32; ++j) { hi[j] = 0u; lo[j] = 0u; }
+      tmem_st32(tmem_base + lane_addr + kColA1, hi);
+      tmem_st32(tmem_base + lane_addr + kColA1 + 32, lo);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive_warp(b_a1);
+      TC_T(6);
+      // d_raw^T is still being read by product 2 of the previous sub-tile
+      if (it >= 1 && !mbar_wait_warp(b_b2free, (it - 1) & 1, abort_flag, status, kErrAbFree)) break;
+      TC_T(2);
+      {
+        // element (j, r = t) of block t / 32 = [hi: 32 j-rows x 128 bytes][lo: the same], 128-byte swizzle
+        // (16-byte chunk index ^ (j & 7)): one K-major tile of 64 rows per block of 32 rows of x
         const uint32_t blk = base + kOffB2 + (uint32_t)(t >> 5) * 8192u + (uint32_t)(t & 3) * 4u;
         const uint32_t chunk = (uint32_t)(t & 31) >> 2;
 #pragma unroll
@@ -708,9 +720,7 @@ k_dw_rows_bwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         }
       }
       fence_async_smem();
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive_warp(b_a1);
+      mbar_arrive_warp(b_b2);
       fetch(it + 1);   // in flight while the products of this sub-tile run
       TC_T(1);
     }
