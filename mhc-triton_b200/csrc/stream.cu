@@ -720,18 +720,6 @@ Geo make_geo(int64_t S, int64_t D, int vec, GeoKind kind, int tpc, int occ) {
   const int max_cols = pool ? MHC_POOL_COLS : MHC_MAX_COLS;
   int cols = 32;
   while (cols < max_cols && cols < g.DV) cols <<= 1;
-  // Rows that are not a multiple of the widest group (e.g. 896 packs: 3.5 groups of 256) would leave part of
-  // the last group's threads idle in every CTA: take the widest power of two that wastes the fewest threads
-  // (896 = 7 x 128; the CTA then walks two tokens abreast).
-  if (!pool) {
-    int best = cols;
-    int64_t best_pad = ((g.DV + cols - 1) / cols) * (int64_t)cols;
-    for (int c = cols >> 1; c >= 64; c >>= 1) {
-      const int64_t pad = ((g.DV + c - 1) / c) * (int64_t)c;
-      if (pad < best_pad) { best = c; best_pad = pad; }
-    }
-    cols = best;
-  }
   g.cols = cols;
   g.CG = (g.DV + cols - 1) / cols;
   if (pool) {
