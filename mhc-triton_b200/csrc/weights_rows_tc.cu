@@ -9,9 +9,10 @@
 // memory and its A operand from shared OR tensor memory; splitting x inside shared memory would
 // triple the shared-memory traffic of an HBM-bound kernel, so the rows take the tensor-memory road:
 //
-//   warp 4 (one lane)   TMA producer: x tile [128 rows x 32 k] + the pre-split phi^T tiles (hi, lo)
-//                       [32 outputs x 32 k] per stage, four stages (the x part of a stage is free again as
-//                       soon as the row threads hold it in registers, the phi part when its MMAs are done).
+//   warp 4 (two lanes)  TMA producers: x tiles [128 rows x 32 k] through a ring of five stages (a stage is
+//                       free again as soon as the row threads hold it in registers) and the pre-split
+//                       phi^T tiles (hi, lo) [32 outputs x 32 k] through a ring of three (free when their
+//                       MMAs are done).
 //   warps 0-3           thread t owns row t: reads its 128 bytes of the x tile from shared memory,
 //                       splits them into hi / lo in registers, adds up x^2, and writes both halves to
 //                       tensor memory (tcgen05.st), lane t, as the A operand [128 x 32].
@@ -53,19 +54,24 @@ namespace tc {
 constexpr int kBM = 128;   // rows per CTA = lanes of tensor memory
 constexpr int kBK = 32;    // k per tile: 128 bytes of fp32, one swizzle span
 constexpr int kBN = 32;    // the 24 outputs, padded
-constexpr int kStages = 4;   // shared-memory stages in flight (TMA latency x HBM rate needs ~32 KiB of x per SM)
+// Two rings of shared-memory stages: x tiles (free again as soon as the row threads hold them in
+// registers) and phi tiles (free when their MMAs are done).  A TMA load takes 3000-4000 cycles to land, so
+// what counts is the x in flight per SM: 2 CTAs x 5 stages x 16 KiB.
+constexpr int kXStages = 5, kPStages = 3;
 constexpr uint32_t kXBytes = kBM * kBK * 4;          // 16 KiB
 constexpr uint32_t kPBytes = kBN * kBK * 4;          // 4 KiB
-constexpr uint32_t kStageBytes = kXBytes + 2 * kPBytes;
+constexpr uint32_t kPStageBytes = 2 * kPBytes;       // phi_hi, phi_lo back to back
+constexpr uint32_t kOffP = kXStages * kXBytes;
 constexpr uint32_t kTmemCols = 256;                  // A: 2 buffers x (32 hi + 32 lo); D: 2 x 64  (two CTAs per SM)
 constexpr uint32_t kColA = 0, kColD = 128;
 constexpr int kDCols = 64;                           // an accumulator holds A * [phi_hi | phi_lo]
 constexpr int kThreads = 192;
-constexpr size_t kSmemBytes = 1024 + kStages * kStageBytes + 256;
+constexpr size_t kSmemBytes = 1024 + kXStages * kXBytes + kPStages * kPStageBytes + 256;
 constexpr long long kWaitCycles = 2000000000LL;      // about one second
 
 // status word values (first int of the scratch): which wait ran out
-enum { kOk = 0, kErrFull = 1001, kErrAReady = 1002, kErrStageFree = 1003, kErrDFull = 1004, kErrDEmpty = 1005, kErrXReleased = 1006 };
+enum { kOk = 0, kErrFull = 1001, kErrAReady = 1002, kErrStageFree = 1003, kErrDFull = 1004, kErrDEmpty = 1005, kErrXReleased = 1006,
+       kErrPFull = 1007 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -240,15 +246,16 @@ k_dw_rows_fwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
   pdl_prologue();
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;   // tiles need 1024-byte alignment for the swizzle
-  const uint32_t bars = base + kStages * kStageBytes;
-  // barriers: full[S] x_free[S] b_free[S] a_ready[2] d_full[2] d_empty[2]
+  const uint32_t bars = base + kOffP + kPStages * kPStageBytes;
+  // barriers: x_full[X] x_free[X] p_full[P] p_free[P] a_ready[2] d_full[2] d_empty[2]
   auto bar_full = [&](int s) { return bars + 8u * s; };
-  auto bar_xfree = [&](int s) { return bars + 8u * (kStages + s); };
-  auto bar_free = [&](int s) { return bars + 8u * (2 * kStages + s); };
-  auto bar_aready = [&](int a) { return bars + 8u * (3 * kStages + a); };
-  auto bar_dfull = [&](int d) { return bars + 8u * (3 * kStages + 2 + d); };
-  auto bar_dempty = [&](int d) { return bars + 8u * (3 * kStages + 4 + d); };
-  const uint32_t holder = bars + 8u * (3 * kStages + 6);
+  auto bar_xfree = [&](int s) { return bars + 8u * (kXStages + s); };
+  auto bar_pfull = [&](int s) { return bars + 8u * (2 * kXStages + s); };
+  auto bar_free = [&](int s) { return bars + 8u * (2 * kXStages + kPStages + s); };
+  auto bar_aready = [&](int a) { return bars + 8u * (2 * kXStages + 2 * kPStages + a); };
+  auto bar_dfull = [&](int d) { return bars + 8u * (2 * kXStages + 2 * kPStages + 2 + d); };
+  auto bar_dempty = [&](int d) { return bars + 8u * (2 * kXStages + 2 * kPStages + 4 + d); };
+  const uint32_t holder = bars + 8u * (2 * kXStages + 2 * kPStages + 6);
   __shared__ int s_abort;
   volatile int* abort_flag = &s_abort;
 
@@ -258,9 +265,12 @@ k_dw_rows_fwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 
   if (threadIdx.x == 0) {
     s_abort = 0;
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < kXStages; ++s) {
       mbar_init(bar_full(s), 1);
       mbar_init(bar_xfree(s), kBM / 32);
+    }
+    for (int s = 0; s < kPStages; ++s) {
+      mbar_init(bar_pfull(s), 1);
       mbar_init(bar_free(s), 1);
     }
     for (int d = 0; d < 2; ++d) {
@@ -278,40 +288,43 @@ k_dw_rows_fwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
   asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(holder) : "memory");
 
   if (warp == 4) {
-    // ------------------------------------------------------------------ TMA producer
+    // ------------------------------------------------------------------ TMA producers: lane 0 x, lane 1 phi
     if (lane == 0) {
       TC_TIMING_DECL(3);
       for (int i = 0; i < nk; ++i) {
-        const int s = i % kStages;
-        if (i >= kStages && !mbar_wait(bar_xfree(s), ((i / kStages) - 1) & 1, abort_flag, status, kErrXReleased)) break;
+        const int s = i % kXStages;
+        if (i >= kXStages && !mbar_wait(bar_xfree(s), ((i / kXStages) - 1) & 1, abort_flag, status, kErrXReleased)) break;
         TC_T(0);
-        if (i >= kStages && !mbar_wait(bar_free(s), ((i / kStages) - 1) & 1, abort_flag, status, kErrStageFree)) break;
-        TC_T(1);
-        const uint32_t dst = base + s * kStageBytes;
-        mbar_expect_tx(bar_full(s), kStageBytes);
-        tma_load_2d(dst, &map_x, i * kBK, (int)row0, bar_full(s));
-        tma_load_2d(dst + kXBytes, &map_phi_hi, i * kBK, 0, bar_full(s));
-        tma_load_2d(dst + kXBytes + kPBytes, &map_phi_lo, i * kBK, 0, bar_full(s));
+        mbar_expect_tx(bar_full(s), kXBytes);
+        tma_load_2d(base + s * kXBytes, &map_x, i * kBK, (int)row0, bar_full(s));
         TC_T(2);
       }
       TC_TIMING_FLUSH(status, 0, 3);
+    } else if (lane == 1) {
+      for (int i = 0; i < nk; ++i) {
+        const int s = i % kPStages;
+        if (i >= kPStages && !mbar_wait(bar_free(s), ((i / kPStages) - 1) & 1, abort_flag, status, kErrStageFree)) break;
+        const uint32_t dst = base + kOffP + s * kPStageBytes;
+        mbar_expect_tx(bar_pfull(s), kPStageBytes);
+        tma_load_2d(dst, &map_phi_hi, i * kBK, 0, bar_pfull(s));
+        tma_load_2d(dst + kPBytes, &map_phi_lo, i * kBK, 0, bar_pfull(s));
+      }
     }
   } else if (warp == 5) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       TC_TIMING_DECL(4);
       for (int i = 0; i < nk; ++i) {
-        const int s = i % kStages, d = i & 1;   // d: the A buffer and the accumulator of this tile
-        if (!mbar_wait(bar_full(s), (i / kStages) & 1, abort_flag, status, kErrFull)) break;
+        const int s = i % kPStages, d = i & 1;   // d: the A buffer and the accumulator of this tile
+        if (!mbar_wait(bar_pfull(s), (i / kPStages) & 1, abort_flag, status, kErrPFull)) break;
         TC_T(0);
         if (!mbar_wait(bar_aready(d), (i >> 1) & 1, abort_flag, status, kErrAReady)) break;
         TC_T(1);
         if (i >= 2 && !mbar_wait(bar_dempty(d), ((i >> 1) - 1) & 1, abort_flag, status, kErrDEmpty)) break;
         TC_T(2);
         tc_fence_after();
-        const uint32_t stage = base + s * kStageBytes;
         // phi_hi (32 rows) and phi_lo (32 rows) lie back to back: one K-major tile of 64 rows
-        const uint64_t b_cat = make_kmajor_sw128_desc(stage + kXBytes);
+        const uint64_t b_cat = make_kmajor_sw128_desc(base + kOffP + s * kPStageBytes);
         const uint32_t a_hi = tmem_base + kColA + d * 64, a_lo = a_hi + 32, dd = tmem_base + kColD + d * kDCols;
 #pragma unroll
         for (int j = 0; j < kBK / 8; ++j) {   // a k-step of 8 is 32 bytes of a swizzled row: descriptor address + 2
@@ -340,8 +353,8 @@ k_dw_rows_fwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       TC_T(4);
       tc_fence_after();
       uint32_t v[32], w[32];
-      tmem_ld32(tmem_base + lane_addr + kColD + d * kDCols, v);
-      tmem_ld32(tmem_base + lane_addr + kColD + d * kDCols + 32, w);
+      tmem_ld32(tmem_base + lane_addr + kColD + d * kDCols, v);          // the x * phi_hi terms
+      tmem_ld32(tmem_base + lane_addr + kColD + d * kDCols + 32, w);     // the x * phi_lo terms
       tmem_wait_ld();
       TC_T(5);
 #pragma unroll
@@ -352,10 +365,10 @@ k_dw_rows_fwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       return true;
     };
     for (int i = 0; i < nk && ok; ++i) {
-      const int s = i % kStages;
-      if (!mbar_wait_warp(bar_full(s), (i / kStages) & 1, abort_flag, status, kErrFull)) { ok = false; break; }
+      const int s = i % kXStages;
+      if (!mbar_wait_warp(bar_full(s), (i / kXStages) & 1, abort_flag, status, kErrFull)) { ok = false; break; }
       TC_T(0);
-      const uint32_t rowp = base + s * kStageBytes + (uint32_t)t * 128u;
+      const uint32_t rowp = base + s * kXBytes + (uint32_t)t * 128u;
       uint32_t hi[32], lo[32];
       float qt = 0.f;
       float4 xr[8];
@@ -388,6 +401,8 @@ k_dw_rows_fwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       tc_fence_before();
       mbar_arrive_warp(bar_aready(i & 1));
       TC_T(3);
+      // (collecting tile i - 1's sums before the stores above was tried: the products then start later and
+      // the wait here only grows)
       if (i >= 1) ok = drain(i - 1);
     }
     if (ok && nk > 0) ok = drain(nk - 1);
