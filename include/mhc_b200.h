@@ -187,7 +187,7 @@ int mhc_add_residual_bwd(const void* dH_new, const void* branch_output, const fl
  * loop must not call cudaMalloc, or a plugin that only receives input and output buffers).  The
  * partial sums go to a fixed 1 MiB array inside the library image, which every GPU that loads the
  * library holds until the process exits; shapes whose partial sums need more than
- * mhc_add_residual_bwd_noalloc_max_bytes() (16 bytes per 4 tokens per group of 256 16-byte packs
+ * mhc_add_residual_bwd_noalloc_max_bytes() (16 bytes per 3 to 5 tokens per group of 256 16-byte packs
  * along D, per batch element: 256 KiB for bf16 B=8, S=4096, D=4096) are rejected with
  * MHC_ERR_SCRATCH_TOO_SMALL.  The call allocates and frees nothing.  The first
  * call on each device looks up the array's device address (with that device current) and should
@@ -214,10 +214,14 @@ int mhc_meanpool_fwd(const void* H, float* x, void* scratch, int64_t scratch_byt
  * (no host read of the scales).  saved [batch, 32] fp32 receives raw (24 values), sum(x^2),
  * inv_rms and padding for the backward; it may be NULL.
  * Any batch is accepted.  Below 64 rows every row gets its own CTAs (the sequence-pooled use, batch =
- * number of sequences); from 64 rows on (per-token use, batch = number of tokens) both directions tile
- * over rows and, when K % 4 == 0 and x / phi are 16-byte aligned, compute x phi, grad_x and grad_phi
- * with TF32 tensor-core MMAs on hi/lo splits of both operands (3xTF32) and fp32 running sums: same
- * results as the fp32 FMA path to within the fp32 parity band, not bit-identical to it.
+ * number of sequences).  From 64 rows on (per-token use, batch = number of tokens), when K % 4 == 0
+ * and x is 16-byte aligned, both directions run on the fifth-generation tensor cores: tcgen05.mma
+ * kind::tf32 on hi/lo splits of both operands (3xTF32) with fp32 running sums, x tiles by TMA, and in
+ * the forward the whole finish of a row as the kernel's epilogue; same results as the fp32 FMA path
+ * to within the fp32 parity band, not bit-identical to it.  Other shapes use mma.sync / FMA kernels
+ * (also with MHC_ROWS_TC=0 in the environment).  On the tensor-core path scratch must be 16-byte
+ * aligned, and its first int is a status word: 0, or the code of an mbarrier wait that ran out
+ * (every wait in those kernels is bounded; the affected outputs are then NaN).
  * Replaces fused_dynamic_weights_forward, src/mhc/_kernels.py:690-752 (kernel :318-590). */
 int mhc_dynamic_weights_fwd(const float* x, const float* phi, const float* bias,
                             const float* alpha_pre, const float* alpha_post,
@@ -228,7 +232,8 @@ int mhc_dynamic_weights_fwd(const float* x, const float* phi, const float* bias,
 /* Gradients of the above: grad_x [batch,K], grad_phi [K,24], grad_bias [24], grad_alpha [3]
  * (pre, post, res), all fp32, written (not accumulated) unless `accumulate_params` is non-zero,
  * in which case grad_phi / grad_bias / grad_alpha are added to.  `saved` is the buffer the
- * forward filled.  Replaces _FusedDynamicWeights.backward, src/mhc/ops.py:109-228, including its
+ * forward filled.  On the tensor-core path (see above) grad_x and scratch must be 16-byte aligned.
+ * Replaces _FusedDynamicWeights.backward, src/mhc/ops.py:109-228, including its
  * call of sinkhorn_backward (:161-166). */
 int mhc_dynamic_weights_bwd(const float* x, const float* phi, const float* bias,
                             const float* alpha_pre, const float* alpha_post,

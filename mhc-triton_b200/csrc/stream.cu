@@ -929,6 +929,22 @@ extern "C" int mhc_add_residual_fwd(const void* H_residual, const void* branch_o
   return check_launch("add_residual_fwd");
 }
 
+// Tokens per chunk of the add-residual kernels that also pool: MHC_TPC_ADDPOOL adjusted so that one batch
+// element's CTAs fill whole waves (two resident CTAs per SM; column groups counted for 16-byte packs of
+// 2-byte elements, the common case; other layouts get the same chunk length, only a less even fill).
+// A function of S, D and the device only, shared by the launch and by mhc_add_residual_pool_chunks.
+static int addpool_tpc(int64_t S, int64_t D) {
+  const int64_t dv = D >= 8 ? D / 8 : 1;
+  const int cg = (int)((dv + MHC_MAX_COLS - 1) / MHC_MAX_COLS);
+  return wave_tpc(S, cg, 1, MHC_TPC_ADDPOOL, MHC_ADDMIXPOOL_MINB);
+}
+
+extern "C" int64_t mhc_add_residual_pool_chunks(int64_t S, int64_t D) {
+  if (S <= 0) return 0;
+  const int tpc = addpool_tpc(S, D);
+  return (S + tpc - 1) / tpc;
+}
+
 extern "C" int mhc_add_residual_mix_fwd(const void* H, const float* H_res, const void* branch_output,
                                         const float* H_post, void* H_new, float* pool_partials, int64_t B, int64_t S,
                                         int64_t D, int dtype, mhc_stream_t stream) {
@@ -940,8 +956,9 @@ extern "C" int mhc_add_residual_mix_fwd(const void* H, const float* H_res, const
   cudaStream_t st = (cudaStream_t)stream;
   if (pool_partials) {
     Geo g = make_geo(S, D, vec, GeoKind::Reduce, MHC_TPC_ADDPOOL);
-    g.tpc = (int32_t)(S < MHC_TPC_ADDPOOL ? S : MHC_TPC_ADDPOOL);
-    g.nchunk = (int32_t)((S + MHC_TPC_ADDPOOL - 1) / MHC_TPC_ADDPOOL);
+    const int ptpc = addpool_tpc(S, D);
+    g.tpc = (int32_t)(S < ptpc ? S : ptpc);
+    g.nchunk = (int32_t)mhc_add_residual_pool_chunks(S, D);
     g.reverse = (MHC_REV_MASK >> 2) & 1;
     const int64_t items = B * geo_slots(g);
     if (int e = check_grid("add_residual_mix_fwd", items)) return e;
@@ -962,11 +979,6 @@ extern "C" int mhc_add_residual_mix_fwd(const void* H, const float* H_res, const
   return check_launch("add_residual_mix_fwd");
 }
 
-extern "C" int64_t mhc_add_residual_pool_chunks(int64_t S, int64_t D) {
-  (void)D;
-  if (S <= 0) return 0;
-  return (S + MHC_TPC_ADDPOOL - 1) / MHC_TPC_ADDPOOL;  // a function of S only
-}
 
 extern "C" int mhc_add_residual_pool_fwd(const void* H_residual, const void* branch_output, const float* H_post,
                                          void* H_new, float* pool_partials, int64_t B, int64_t S, int64_t D, int dtype,
@@ -977,9 +989,10 @@ extern "C" int mhc_add_residual_pool_fwd(const void* H_residual, const void* bra
     return fail(MHC_ERR_NULL_POINTER, "add_residual_pool_fwd: null pointer");
   const int vec = pick_vec(dtype, D, {H_residual, branch_output, H_new});
   Geo g = make_geo(S, D, vec, GeoKind::Reduce, MHC_TPC_ADDPOOL);
-  // Chunks are MHC_TPC_ADDPOOL tokens whatever the row width (token sub-groups share a chunk), so the
-  // number of partial rows is a function of S only.
-  g.tpc = (int32_t)(S < MHC_TPC_ADDPOOL ? S : MHC_TPC_ADDPOOL);
+  // Chunks are addpool_tpc tokens whatever the pack width (token sub-groups share a chunk), so the
+  // number of partial rows is a function of S and D only.
+  const int ptpc = addpool_tpc(S, D);
+  g.tpc = (int32_t)(S < ptpc ? S : ptpc);
   g.nchunk = (int32_t)mhc_add_residual_pool_chunks(S, D);
   g.reverse = (MHC_REV_MASK >> 2) & 1;
   const int64_t items = B * geo_slots(g);
