@@ -810,6 +810,22 @@ k_dw_rows_bwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     for (int j = 0; j < 24; ++j) acc[j] = 0.f;
     bool ok = true;
     TC_TIMING_DECL(6);
+    // grad_phi sums of sub-tile `it` -> fp32 registers (columns 0..31: the d_hi terms, 32..63: the d_lo terms)
+    auto drain = [&](int it) {
+      if (!mbar_wait_warp(b_d2full, it & 1, abort_flag, status, kErrD2Full)) return false;
+      TC_T(3);
+      tc_fence_after();
+      uint32_t v[32], w[32];
+      tmem_ld32(tmem_base + lane_addr + kColD2, v);
+      tmem_ld32(tmem_base + lane_addr + kColD2 + 32, w);
+      tmem_wait_ld();
+#pragma unroll
+      for (int j = 0; j < 24; ++j) acc[j] += __uint_as_float(v[j]) + __uint_as_float(w[j]);
+      tc_fence_before();
+      mbar_arrive_warp(b_d2empty);
+      TC_T(4);
+      return true;
+    };
     for (int it = 0; it < nsub && ok; ++it) {
       const int s = it & 1;
       if (!mbar_wait_warp(b_xfull(s), (it >> 1) & 1, abort_flag, status, kErrXFull)) { ok = false; break; }
@@ -840,23 +856,15 @@ k_dw_rows_bwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         tc_fence_before();
         mbar_arrive_warp(b_a2ready(h));
         TC_T(2);
+        // The previous sub-tile's sums are collected here, after the first half of this one is on its way: the
+        // tensor core needs a while to finish them, and the first product of this sub-tile cannot start before
+        // they are out of the accumulator anyway.
+        if (h == 0 && it >= 1) ok = drain(it - 1);
       }
       if (!ok) break;
       mbar_arrive_warp(b_xread(s));              // this warp no longer reads the x tile
-      // grad_phi sums of this sub-tile -> fp32 registers (columns 0..31: x_hi*d_hi + x_lo*d_hi, 32..63: the d_lo terms)
-      if (!mbar_wait_warp(b_d2full, it & 1, abort_flag, status, kErrD2Full)) { ok = false; break; }
-      TC_T(3);
-      tc_fence_after();
-      uint32_t v[32], w[32];
-      tmem_ld32(tmem_base + lane_addr + kColD2, v);
-      tmem_ld32(tmem_base + lane_addr + kColD2 + 32, w);
-      tmem_wait_ld();
-#pragma unroll
-      for (int j = 0; j < 24; ++j) acc[j] += __uint_as_float(v[j]) + __uint_as_float(w[j]);
-      tc_fence_before();
-      mbar_arrive_warp(b_d2empty);
-      TC_T(4);
     }
+    if (ok && nsub > 0) ok = drain(nsub - 1);
     if (t == 0) TC_TIMING_FLUSH(status, 16, 5);
     const int64_t k = k0 + t;
     if (k < K) {
