@@ -490,7 +490,7 @@ constexpr uint32_t kB1Bytes = kSlab * 32 * 4;
 constexpr uint32_t kOffB2 = kOffB1 + 2 * kB1Bytes; // d_raw^T: 4 blocks (32 rows of x each) of [hi 32 j-rows | lo 32 j-rows] x 128 bytes
 constexpr uint32_t kB2Bytes = 32 * 128 * 4;
 constexpr uint32_t kOffBars = kOffB2 + 2 * kB2Bytes;
-constexpr size_t kSmem = 1024 + kOffBars + 256;
+constexpr size_t kSmem = 1024 + kOffBars + 512;
 constexpr int kThreadsBwd = 448;
 constexpr uint32_t kColA1 = 0, kColD1 = 64, kColA2 = 192, kColD2 = 448;   // A2 half h at kColA2 + 128 h (hi 64, lo 64); D2 64
 constexpr uint32_t kIdescN128 = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
@@ -536,18 +536,20 @@ k_dw_rows_bwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bars = base + kOffBars;
-  // barriers (8 bytes each); those the row / column threads arrive on count warps (4)
+  // barriers (8 bytes each).  The x tile of a sub-tile is four quarters [128 rows x 32 k] of 16 KiB, each with
+  // its own load / read / store barriers (buffer q = 4 * (sub-tile & 1) + quarter), so that loading, splitting,
+  // the epilogue and the store of different quarters overlap.
   const uint32_t b_phi = bars;
-  auto b_xfull = [&](int s) { return bars + 8u * (1 + s); };
-  auto b_store = [&](int s) { return bars + 8u * (3 + s); };    // the row threads have written grad_x over stage s
-  auto b_xread = [&](int s) { return bars + 8u * (5 + s); };    // the column threads have read stage s
-  const uint32_t b_a1 = bars + 8u * 7, b_b2free = bars + 8u * 8;   // A1 written / the products have read d_raw^T
-  const uint32_t b_a1free = bars + 8u * 17, b_b2 = bars + 8u * 18;    // product 1 has read A1 / d_raw^T written
-  auto b_a2ready = [&](int h) { return bars + 8u * (9 + h); };
-  auto b_a2free = [&](int h) { return bars + 8u * (11 + h); };
-  const uint32_t b_d1full = bars + 8u * 13, b_d1empty = bars + 8u * 14;
-  const uint32_t b_d2full = bars + 8u * 15, b_d2empty = bars + 8u * 16;
-  const uint32_t holder = bars + 8u * 19;
+  auto b_xfull = [&](int q) { return bars + 8u * (1 + q); };     // TMA has filled quarter buffer q
+  auto b_store = [&](int q) { return bars + 8u * (9 + q); };     // the epilogue warps (4) have written grad_x over it
+  auto b_xread = [&](int q) { return bars + 8u * (17 + q); };    // the column warp of this quarter has read it
+  const uint32_t b_a1 = bars + 8u * 25, b_b2free = bars + 8u * 26;   // A1 written / the products have read d_raw^T
+  auto b_a2ready = [&](int h) { return bars + 8u * (27 + h); };
+  auto b_a2free = [&](int h) { return bars + 8u * (29 + h); };
+  const uint32_t b_d1full = bars + 8u * 31, b_d1empty = bars + 8u * 32;
+  const uint32_t b_d2full = bars + 8u * 33, b_d2empty = bars + 8u * 34;
+  const uint32_t b_a1free = bars + 8u * 35, b_b2 = bars + 8u * 36;   // product 1 has read A1 / d_raw^T written
+  const uint32_t holder = bars + 8u * 38;
   __shared__ int s_abort;
   volatile int* abort_flag = &s_abort;
 
@@ -560,12 +562,14 @@ k_dw_rows_bwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
   if (threadIdx.x == 0) {
     s_abort = 0;
     mbar_init(b_phi, 1);
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(b_xfull(s), 1);
-      mbar_init(b_store(s), 4);
-      mbar_init(b_xread(s), 4);
-      mbar_init(b_a2ready(s), 4);
-      mbar_init(b_a2free(s), 1);
+    for (int q = 0; q < 8; ++q) {
+      mbar_init(b_xfull(q), 1);
+      mbar_init(b_store(q), 4);
+      mbar_init(b_xread(q), 1);
+    }
+    for (int h = 0; h < 2; ++h) {
+      mbar_init(b_a2ready(h), 4);
+      mbar_init(b_a2free(h), 1);
     }
     mbar_init(b_a1, 4);
     mbar_init(b_b2, 4);
@@ -588,35 +592,36 @@ k_dw_rows_bwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     // ---------------------------------------------------------------- TMA: loads, and the stores of grad_x
     if (lane == 0) {
       TC_TIMING_DECL(4);
-      auto load_x = [&](int it) {
-        const int s = it & 1;
-        mbar_expect_tx(b_xfull(s), kXStage);
-        const int r0 = (int)(g0 + (int64_t)it * kBM);
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          tma_load_2d(base + s * kXStage + kk * kXBytes, &map_x, (int)k0 + 32 * kk, r0, b_xfull(s));
+      auto load_q = [&](int it, int kk) {
+        const int q = 4 * (it & 1) + kk;
+        mbar_expect_tx(b_xfull(q), kXBytes);
+        tma_load_2d(base + q * kXBytes, &map_x, (int)k0 + 32 * kk, (int)(g0 + (int64_t)it * kBM), b_xfull(q));
       };
       mbar_expect_tx(b_phi, 2 * kB1Bytes);
       tma_load_2d(base + kOffB1, &map_phi_hi, 0, (int)k0, b_phi);
       tma_load_2d(base + kOffB1 + kB1Bytes, &map_phi_lo, 0, (int)k0, b_phi);
-      load_x(0);
-      if (nsub > 1) load_x(1);
-      for (int it = 0; it < nsub; ++it) {
-        const int s = it & 1;
-        TC_T(3);
-        if (!mbar_wait(b_store(s), (it >> 1) & 1, abort_flag, status, kErrStore)) break;
-        TC_T(0);
-        const int r0 = (int)(g0 + (int64_t)it * kBM);
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          tma_store_2d(&map_gx, (int)k0 + 32 * kk, r0, base + s * kXStage + kk * kXBytes);
-        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-        TC_T(1);
-        if (it + 2 < nsub) {   // the stage is refilled as soon as the stores have read it
-          asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-          load_x(it + 2);
+      for (int it = 0; it < 2 && it < nsub; ++it)
+        for (int kk = 0; kk < 4; ++kk) load_q(it, kk);
+      int prev_it = -1, prev_kk = 0;
+      bool ok = true;
+      for (int it = 0; it < nsub && ok; ++it) {
+        for (int kk = 0; kk < 4; ++kk) {
+          const int q = 4 * (it & 1) + kk;
+          TC_T(3);
+          if (!mbar_wait(b_store(q), (it >> 1) & 1, abort_flag, status, kErrStore)) { ok = false; break; }
+          TC_T(0);
+          tma_store_2d(&map_gx, (int)k0 + 32 * kk, (int)(g0 + (int64_t)it * kBM), base + q * kXBytes);
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          TC_T(1);
+          // the quarter stored one step earlier has been read out by now (all groups but the newest): refill it
+          if (prev_it >= 0 && prev_it + 2 < nsub) {
+            asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            load_q(prev_it + 2, prev_kk);
+          }
+          prev_it = it;
+          prev_kk = kk;
+          TC_T(2);
         }
-        TC_T(2);
       }
       asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
       TC_TIMING_FLUSH(status, 24, 4);
@@ -697,7 +702,6 @@ k_dw_rows_bwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     fetch(0);
     bool good = true;
     for (int it = 0; it < nsub && good; ++it) {
-      const int s = it & 1;
       TC_T(7);
       if (it >= 1 && !mbar_wait_warp(b_a1free, (it - 1) & 1, abort_flag, status, kErrAbFree)) break;
       TC_T(0);
@@ -757,20 +761,23 @@ k_dw_rows_bwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       const float coef = coef_next;
       coef_next = coef_of(it + 1);
       TC_T(7);
-      if (!mbar_wait_warp(b_xfull(s), (it >> 1) & 1, abort_flag, status, kErrXFull)) break;
-      TC_T(2);
-      if (!mbar_wait_warp(b_xread(s), (it >> 1) & 1, abort_flag, status, kErrXRead)) break;
-      TC_T(3);
       if (!mbar_wait_warp(b_d1full, it & 1, abort_flag, status, kErrD1Full)) break;
       TC_T(4);
       tc_fence_after();
       uint32_t v[2][32];
       tmem_ld32(tmem_base + lane_addr + kColD1, v[0]);
+      bool good = true;
 #pragma unroll
       for (int kk = 0; kk < 4; ++kk) {
+        const int q = 4 * s + kk;
+        // the quarter is loaded and its column warp has finished reading it
+        good = good && mbar_wait_warp(b_xfull(q), (it >> 1) & 1, abort_flag, status, kErrXFull) &&
+               mbar_wait_warp(b_xread(q), (it >> 1) & 1, abort_flag, status, kErrXRead);
+        if (!good) break;
+        TC_T(3);
         tmem_wait_ld();
         if (kk + 1 < 4) tmem_ld32(tmem_base + lane_addr + kColD1 + 32 * (kk + 1), v[(kk + 1) & 1]);   // next quarter in flight
-        const uint32_t rowp = base + s * kXStage + kk * kXBytes + (uint32_t)t * 128u;
+        const uint32_t rowp = base + q * kXBytes + (uint32_t)t * 128u;
         float4 xv[8];
 #pragma unroll
         for (int c = 0; c < 8; ++c)   // all loads first, then the arithmetic, then the stores
@@ -790,12 +797,15 @@ k_dw_rows_bwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
           asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};"
                        ::"r"(rowp + (uint32_t)((c ^ (t & 7)) << 4)), "f"(xv[c].x), "f"(xv[c].y), "f"(xv[c].z), "f"(xv[c].w)
                        : "memory");
+        if (kk == 3) {   // all of D1 is in registers: product 1 of the next sub-tile may overwrite it
+          tc_fence_before();
+          mbar_arrive_warp(b_d1empty);
+        }
+        fence_async_smem();
+        mbar_arrive_warp(b_store(q));   // the TMA lane stores this quarter
+        TC_T(5);
       }
-      tc_fence_before();
-      mbar_arrive_warp(b_d1empty);
-      fence_async_smem();
-      mbar_arrive_warp(b_store(s));
-      TC_T(5);
+      if (!good) break;
     }
     if (t == 0) TC_TIMING_FLUSH(status, 28, 8);
   } else if (warp < 8) {
@@ -827,20 +837,20 @@ k_dw_rows_bwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       return true;
     };
     for (int it = 0; it < nsub && ok; ++it) {
-      const int s = it & 1;
-      if (!mbar_wait_warp(b_xfull(s), (it >> 1) & 1, abort_flag, status, kErrXFull)) { ok = false; break; }
+      const int q = 4 * (it & 1) + kk;          // this warp's quarter of the sub-tile
+      if (!mbar_wait_warp(b_xfull(q), (it >> 1) & 1, abort_flag, status, kErrXFull)) { ok = false; break; }
       TC_T(0);
-      const uint32_t tile = base + s * kXStage + colp;
+      const uint32_t tile = base + (it & 1) * kXStage + colp;
       for (int h = 0; h < 2 && ok; ++h) {
         if (it >= 1 && !mbar_wait_warp(b_a2free(h), (it - 1) & 1, abort_flag, status, kErrA2Free)) { ok = false; break; }
         TC_T(1);
 #pragma unroll 1
-        for (int q = 0; q < 2; ++q) {            // 32 rows at a time
+        for (int rq = 0; rq < 2; ++rq) {         // 32 rows at a time
           uint32_t hi[32], lo[32];
           float xc[32];
 #pragma unroll
           for (int u = 0; u < 32; ++u) {   // all loads first
-            const uint32_t r = (uint32_t)(64 * h + 32 * q + u);
+            const uint32_t r = (uint32_t)(64 * h + 32 * rq + u);
             asm volatile("ld.shared.f32 %0, [%1];" : "=f"(xc[u]) : "r"(tile + r * 128u + ((chunk ^ (r & 7u)) << 4)) : "memory");
           }
 #pragma unroll
@@ -848,7 +858,7 @@ k_dw_rows_bwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             hi[u] = tf32_rn(xc[u]);
             lo[u] = tf32_rn(xc[u] - __uint_as_float(hi[u]));
           }
-          const uint32_t a2 = tmem_base + lane_addr + kColA2 + 128 * h + 32 * q;
+          const uint32_t a2 = tmem_base + lane_addr + kColA2 + 128 * h + 32 * rq;
           tmem_st32(a2, hi);
           tmem_st32(a2 + 64, lo);
         }
@@ -862,7 +872,7 @@ k_dw_rows_bwd_tc(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         if (h == 0 && it >= 1) ok = drain(it - 1);
       }
       if (!ok) break;
-      mbar_arrive_warp(b_xread(s));              // this warp no longer reads the x tile
+      mbar_arrive_warp(b_xread(q));              // this warp no longer reads its quarter of the x tile
     }
     if (ok && nsub > 0) ok = drain(nsub - 1);
     if (t == 0) TC_TIMING_FLUSH(status, 16, 5);
