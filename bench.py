@@ -884,7 +884,9 @@ def main():
                                             ("outside the graphs, beside the next forward" if use_graph else
                                              "started inside the backward beside the pass that writes dH"))
                                 if world > 1 else "none",
-                                **({"batch_overridden": B} if args.batch else {})),
+                                **({"batch_overridden": B} if args.batch else {}),
+                                **({"branch_overridden": "identity branches instead of the MLP"}
+                                   if name == "c5" and args.identity_branch else {})),
             "value_spread": {"regions": len(regions), "steps_per_region": args.steps, "median": value,
                              "min": min(vals), "max": max(vals)},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches) * world,

@@ -200,6 +200,9 @@ template <int V> __device__ __forceinline__ float raw_get(const RawPack<__half, 
   }
 }
 
+// The packs a thread holds for one token (N rows of 16 bytes, or N scalars).
+template <typename T, int V, int N> struct Bundle { RawPack<T, V> p[N]; };
+
 // Plain token loop: load, then compute (more resident CTAs cover the latency instead).
 template <class Bundle, class Load, class Compute>
 __device__ __forceinline__ void for_tokens_simple(int64_t s0, int64_t s1, int64_t step, Load load, Compute compute) {
@@ -226,6 +229,51 @@ __device__ __forceinline__ void for_tokens_pipelined(int64_t s0, int64_t s1, int
       compute(b, s + step);
     }
   }
+}
+
+// Token loop whose loads in flight live in shared memory instead of registers: every thread copies the N
+// packs of the next DEPTH-1 tokens with cp.async (16 bytes each, L2 only) into slots of its own and reads
+// a token's packs back when its copy group has landed.  A thread only ever reads what it copied itself,
+// so no barrier is involved, and a kernel whose accumulators leave no registers for packs in flight
+// still keeps (DEPTH-1) * N * 16 bytes per thread on the way.  Slot (stage d, pack n) of thread t is at
+// ring + ((d * N + n) * blockDim.x + t) * 16: conflict-free for the copies and for the reads.
+// `addr(s, n)` returns the global address of pack n of token s.  Needs 16-byte packs (V > 1).
+template <typename T, int V, int N, int DEPTH, class Addr, class Compute>
+__device__ __forceinline__ void for_tokens_staged(int64_t s0, int64_t s1, int64_t step, uint32_t ring, Addr addr,
+                                                  Compute compute) {
+  static_assert(DEPTH >= 2 && DEPTH <= 8, "ring depth");
+  const uint32_t mine = ring + threadIdx.x * 16u, pitch = blockDim.x * 16u;
+  auto issue = [&](int d, int64_t s) {
+#pragma unroll
+    for (int n = 0; n < N; ++n)
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(mine + (uint32_t)(d * N + n) * pitch), "l"(addr(s, n))
+                   : "memory");
+  };
+  int64_t next = s0;
+#pragma unroll
+  for (int d = 0; d < DEPTH - 1; ++d) {
+    if (next < s1) issue(d, next);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    next += step;
+  }
+  int d = 0;
+  for (int64_t s = s0; s < s1; s += step) {
+    const int dn = d == 0 ? DEPTH - 1 : d - 1;   // the stage read in the previous iteration
+    if (next < s1) issue(dn, next);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    next += step;
+    asm volatile("cp.async.wait_group %0;" ::"n"(DEPTH - 1) : "memory");
+    Bundle<T, V, N> a;
+#pragma unroll
+    for (int n = 0; n < N; ++n)
+      asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                   : "=r"(a.p[n].w.x), "=r"(a.p[n].w.y), "=r"(a.p[n].w.z), "=r"(a.p[n].w.w)
+                   : "r"(mine + (uint32_t)(d * N + n) * pitch)
+                   : "memory");
+    compute(a, s);
+    d = d + 1 == DEPTH ? 0 : d + 1;
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
 }
 
 template <bool PIPE, class Bundle, class Load, class Compute>

@@ -37,6 +37,7 @@ namespace mhc {
 #ifndef MHC_APPLY_MINB
 #define MHC_APPLY_MINB 3
 #endif
+
 // Mean-pool: tokens per CTA (adjusted to fill whole waves, see wave_tpc), packs along D per CTA (the CTA
 // has 4 x MHC_POOL_COLS threads, one per stream row and pack), loads in flight per thread, and
 // the resident CTAs per SM the chunking is sized for.
@@ -83,7 +84,6 @@ namespace mhc {
 #define MHC_ADDBWD_OCC 3
 #endif
 
-template <typename T, int V, int N> struct Bundle { RawPack<T, V> p[N]; };
 
 template <typename T, int V>
 __device__ __forceinline__ void unpack(const RawPack<T, V>& r, float (&o)[V]) {
@@ -209,6 +209,12 @@ k_add_residual_fwd(const T* __restrict__ Hr, const T* __restrict__ bo, const flo
 #ifndef MHC_ADDPOOL_PIPE
 #define MHC_ADDPOOL_PIPE 0
 #endif
+// Tokens' worth of loads the pooling add-residual kernels keep in a per-thread shared-memory ring (see
+// for_tokens_staged; 0: none, loads go straight to registers): stages * 5 packs * 16 bytes per thread.
+// Their 32 pooling sums leave too few registers to keep enough loads in flight otherwise.
+#ifndef MHC_ADDPOOL_STAGES
+#define MHC_ADDPOOL_STAGES 4
+#endif
 template <typename T, int V>
 __global__ void __launch_bounds__(MHC_MAX_COLS, 2)
 k_add_residual_pool_fwd(const T* __restrict__ Hr, const T* __restrict__ bo, const float* __restrict__ Hpost,
@@ -228,31 +234,40 @@ k_add_residual_pool_fwd(const T* __restrict__ Hr, const T* __restrict__ bo, cons
 #pragma unroll
     for (int n = 0; n < 4; ++n) p[n] = __ldg(Hpost + it.b * 4 + n);
     using B5 = Bundle<T, V, 5>;
-    for_tokens<MHC_ADDPOOL_PIPE != 0, B5>(
-        it.s0 + it.sub, it.s1, g.sub,
-        [&](B5& u, int64_t s) {
-          const T* r = Hr + (tok + s) * 4 * D + c0;
-          u.p[4] = ld_raw<T, V>(bo + (tok + s) * D + c0);
+    auto load = [&](B5& u, int64_t s) {
+      const T* r = Hr + (tok + s) * 4 * D + c0;
+      u.p[4] = ld_raw<T, V>(bo + (tok + s) * D + c0);
 #pragma unroll
-          for (int n = 0; n < 4; ++n) u.p[n] = ld_raw<T, V>(r + n * D);
-        },
-        [&](const B5& u, int64_t s) {
-          float y[V], x[V];
-          unpack<T, V>(u.p[4], y);
-          T* o = Hn + (tok + s) * 4 * D + c0;
+      for (int n = 0; n < 4; ++n) u.p[n] = ld_raw<T, V>(r + n * D);
+    };
+    auto compute = [&](const B5& u, int64_t s) {
+      float y[V], x[V];
+      unpack<T, V>(u.p[4], y);
+      T* o = Hn + (tok + s) * 4 * D + c0;
 #pragma unroll
-          for (int n = 0; n < 4; ++n) {
-            unpack<T, V>(u.p[n], x);
+      for (int n = 0; n < 4; ++n) {
+        unpack<T, V>(u.p[n], x);
 #pragma unroll
-            for (int e = 0; e < V; ++e) x[e] = x[e] + p[n] * y[e];
-            PackIO<T, V>::store_round(o + n * D, x);   // x now holds what a later read of H_new returns
+        for (int e = 0; e < V; ++e) x[e] = x[e] + p[n] * y[e];
+        PackIO<T, V>::store_round(o + n * D, x);   // x now holds what a later read of H_new returns
 #pragma unroll
-            for (int e = 0; e < V; ++e) acc[n][e] += x[e];
-          }
-        });
+        for (int e = 0; e < V; ++e) acc[n][e] += x[e];
+      }
+    };
+    if constexpr (V > 1 && MHC_ADDPOOL_STAGES > 0) {
+      for_tokens_staged<T, V, 5, MHC_ADDPOOL_STAGES>(
+          it.s0 + it.sub, it.s1, g.sub, (uint32_t)__cvta_generic_to_shared(sm),
+          [&](int64_t s, int n) -> const T* {
+            return n == 4 ? bo + (tok + s) * D + c0 : Hr + ((tok + s) * 4 + n) * D + c0;
+          },
+          compute);
+    } else {
+      for_tokens<MHC_ADDPOOL_PIPE != 0, B5>(it.s0 + it.sub, it.s1, g.sub, load, compute);
+    }
   }
   const int c = threadIdx.x % g.cols;
   if (g.sub > 1) {  // add the sub-groups in index order, two stream rows at a time (halves the shared memory)
+    if (V > 1 && MHC_ADDPOOL_STAGES > 0) __syncthreads();   // the sums below reuse the ring's shared memory
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
       if (half) __syncthreads();
@@ -302,6 +317,7 @@ k_add_residual_pool_fwd(const T* __restrict__ Hr, const T* __restrict__ bo, cons
 #ifndef MHC_ADDMIXPOOL_MINB
 #define MHC_ADDMIXPOOL_MINB 2
 #endif
+
 template <typename T, int V, bool POOL>
 __global__ void __launch_bounds__(MHC_MAX_COLS, POOL ? MHC_ADDMIXPOOL_MINB : MHC_ADDMIX_MINB)
 k_add_residual_mix_fwd(const T* __restrict__ H, const float* __restrict__ Hres, const T* __restrict__ bo,
@@ -326,39 +342,49 @@ k_add_residual_mix_fwd(const T* __restrict__ H, const float* __restrict__ Hres, 
 #pragma unroll
     for (int k = 0; k < 16; ++k) R[k] = __ldg(Hres + it.b * 16 + k);
     using B5 = Bundle<T, V, 5>;
-    for_tokens<(POOL ? MHC_ADDMIXPOOL_PIPE != 0 : MHC_ADDMIX_PIPE != 0), B5>(
-        it.s0 + it.sub, it.s1, g.sub,
-        [&](B5& u, int64_t s) {
-          const T* h = H + (tok + s) * 4 * D + c0;
-          u.p[4] = ld_raw<T, V>(bo + (tok + s) * D + c0);
+    auto load = [&](B5& u, int64_t s) {
+      const T* h = H + (tok + s) * 4 * D + c0;
+      u.p[4] = ld_raw<T, V>(bo + (tok + s) * D + c0);
 #pragma unroll
-          for (int n = 0; n < 4; ++n) u.p[n] = ld_raw<T, V>(h + n * D);
-        },
-        [&](const B5& u, int64_t s) {
-          float x[4][V], y[V], o[V];
-          unpack<T, V>(u.p[4], y);
+      for (int n = 0; n < 4; ++n) u.p[n] = ld_raw<T, V>(h + n * D);
+    };
+    auto compute = [&](const B5& u, int64_t s) {
+      float x[4][V], y[V], o[V];
+      unpack<T, V>(u.p[4], y);
 #pragma unroll
-          for (int n = 0; n < 4; ++n) unpack<T, V>(u.p[n], x[n]);
-          T* op = Hn + (tok + s) * 4 * D + c0;
+      for (int n = 0; n < 4; ++n) unpack<T, V>(u.p[n], x[n]);
+      T* op = Hn + (tok + s) * 4 * D + c0;
 #pragma unroll
-          for (int n = 0; n < 4; ++n) {
+      for (int n = 0; n < 4; ++n) {
 #pragma unroll
-            for (int e = 0; e < V; ++e)
-              o[e] = (((R[4 * n] * x[0][e] + R[4 * n + 1] * x[1][e]) + R[4 * n + 2] * x[2][e]) + R[4 * n + 3] * x[3][e]) +
-                     p[n] * y[e];
-            if (POOL) {
-              PackIO<T, V>::store_round(op + n * D, o);
+        for (int e = 0; e < V; ++e)
+          o[e] = (((R[4 * n] * x[0][e] + R[4 * n + 1] * x[1][e]) + R[4 * n + 2] * x[2][e]) + R[4 * n + 3] * x[3][e]) +
+                 p[n] * y[e];
+        if (POOL) {
+          PackIO<T, V>::store_round(op + n * D, o);
 #pragma unroll
-              for (int e = 0; e < V; ++e) acc[POOL ? n : 0][e] += o[e];
-            } else {
-              PackIO<T, V>::store(op + n * D, o);
-            }
-          }
-        });
+          for (int e = 0; e < V; ++e) acc[POOL ? n : 0][e] += o[e];
+        } else {
+          PackIO<T, V>::store(op + n * D, o);
+        }
+      }
+    };
+    if constexpr (POOL && V > 1 && MHC_ADDPOOL_STAGES > 0) {
+      // the pooling sums take the registers that would hold loads in flight: stage those in shared memory
+      for_tokens_staged<T, V, 5, MHC_ADDPOOL_STAGES>(
+          it.s0 + it.sub, it.s1, g.sub, (uint32_t)__cvta_generic_to_shared(sm),
+          [&](int64_t s, int n) -> const T* {
+            return n == 4 ? bo + (tok + s) * D + c0 : H + ((tok + s) * 4 + n) * D + c0;
+          },
+          compute);
+    } else {
+      for_tokens<(POOL ? MHC_ADDMIXPOOL_PIPE != 0 : MHC_ADDMIX_PIPE != 0), B5>(it.s0 + it.sub, it.s1, g.sub, load, compute);
+    }
   }
   if (POOL) {
     const int c = threadIdx.x % g.cols;
     if (g.sub > 1) {
+      if (V > 1 && MHC_ADDPOOL_STAGES > 0) __syncthreads();   // the sums below reuse the ring's shared memory
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         if (half) __syncthreads();
@@ -563,29 +589,28 @@ k_stream_mix_bwd_apply(const T* __restrict__ dbi, const T* __restrict__ dHr, con
     }
   }
   using B5 = Bundle<T, V, 5>;
-  for_tokens<MHC_APPLY_PIPE != 0, B5>(
-      it.s0 + it.sub, it.s1, g.sub,
-      [&](B5& u, int64_t s) {
-        const T* rp = dHr + (tok + s) * 4 * D + c0;
-        u.p[4] = ld_raw<T, V>(dbi + (tok + s) * D + c0);
+  auto load = [&](B5& u, int64_t s) {
+    const T* rp = dHr + (tok + s) * 4 * D + c0;
+    u.p[4] = ld_raw<T, V>(dbi + (tok + s) * D + c0);
 #pragma unroll
-        for (int n = 0; n < 4; ++n) u.p[n] = ld_raw<T, V>(rp + n * D);
-      },
-      [&](const B5& u, int64_t s) {
-        float r[4][V], q[V], y[V];
-        unpack<T, V>(u.p[4], q);
+    for (int n = 0; n < 4; ++n) u.p[n] = ld_raw<T, V>(rp + n * D);
+  };
+  auto compute = [&](const B5& u, int64_t s) {
+    float r[4][V], q[V], y[V];
+    unpack<T, V>(u.p[4], q);
 #pragma unroll
-        for (int n = 0; n < 4; ++n) unpack<T, V>(u.p[n], r[n]);
-        T* op = dH + (tok + s) * 4 * D + c0;
+    for (int n = 0; n < 4; ++n) unpack<T, V>(u.p[n], r[n]);
+    T* op = dH + (tok + s) * 4 * D + c0;
 #pragma unroll
-        for (int m = 0; m < 4; ++m) {
+    for (int m = 0; m < 4; ++m) {
 #pragma unroll
-          for (int e = 0; e < V; ++e)
-            y[e] = (w[m] * q[e] + (((R[m] * r[0][e] + R[4 + m] * r[1][e]) + R[8 + m] * r[2][e]) + R[12 + m] * r[3][e])) +
-                   c[m][e];
-          PackIO<T, V>::store(op + m * D, y);
-        }
-      });
+      for (int e = 0; e < V; ++e)
+        y[e] = (w[m] * q[e] + (((R[m] * r[0][e] + R[4 + m] * r[1][e]) + R[8 + m] * r[2][e]) + R[12 + m] * r[3][e])) +
+               c[m][e];
+      PackIO<T, V>::store(op + m * D, y);
+    }
+  };
+  for_tokens<MHC_APPLY_PIPE != 0, B5>(it.s0 + it.sub, it.s1, g.sub, load, compute);
 }
 
 // --------------------------------------------------------------------------------- mean-pool
@@ -663,6 +688,15 @@ k_reduce_partials(const float* __restrict__ part, int64_t slots, int W, int W0, 
 }
 
 // -------------------------------------------------------------------------------- host side
+// launch_k for kernels whose dynamic shared memory may exceed the 48 KiB a kernel gets without asking
+// (the attribute is per device and per kernel; setting it is a host-side call of about a microsecond).
+template <typename... KArgs, typename... Args>
+static inline void launch_pool_k(void (*kernel)(KArgs...), unsigned grid, unsigned block, size_t smem, cudaStream_t st,
+                                 Args&&... args) {
+  if (smem > 48 * 1024) (void)cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  launch_k(kernel, grid, block, smem, st, std::forward<Args>(args)...);
+}
+
 int sm_count() {
   static const int n = [] {
     int dev = 0, v = 0;
@@ -710,7 +744,7 @@ static int wave_tpc(int64_t S, int CG, int abreast, int base, int occ) {
 
 // occ > 0: adjust the tokens per CTA to the device's waves (wave_tpc); occ < 0: the smallest chunk
 // wave_tpc could choose, i.e. an upper bound of the number of chunks (scratch-size queries).
-Geo make_geo(int64_t S, int64_t D, int vec, GeoKind kind, int tpc, int occ) {
+Geo make_geo(int64_t S, int64_t D, int vec, GeoKind kind, int tpc, int occ, bool fit_cols) {
   Geo g;
   g.reverse = 0;
   g.S = S;
@@ -720,6 +754,15 @@ Geo make_geo(int64_t S, int64_t D, int vec, GeoKind kind, int tpc, int occ) {
   const int max_cols = pool ? MHC_POOL_COLS : MHC_MAX_COLS;
   int cols = 32;
   while (cols < max_cols && cols < g.DV) cols <<= 1;
+  // A row whose packs do not fill whole groups of `cols` leaves lanes of its last group idle (D = 7168 in
+  // bf16: 896 packs = 3.5 x 256, one lane in eight).  Take the widest narrower group that fits the row to
+  // within 1/32 instead; the CTA keeps its thread count by walking more tokens abreast.
+  if (fit_cols && !pool) {
+    auto waste = [&](int c) { return (g.DV + c - 1) / c * c - g.DV; };
+    if (waste(cols) * 32 > g.DV)
+      for (int c = cols >> 1; c >= 64; c >>= 1)
+        if (waste(c) * 32 <= g.DV) { cols = c; break; }
+  }
   g.cols = cols;
   g.CG = (g.DV + cols - 1) / cols;
   if (pool) {
@@ -962,10 +1005,11 @@ extern "C" int mhc_add_residual_mix_fwd(const void* H, const float* H_res, const
     g.reverse = (MHC_REV_MASK >> 2) & 1;
     const int64_t items = B * geo_slots(g);
     if (int e = check_grid("add_residual_mix_fwd", items)) return e;
-    const size_t smem = g.sub > 1 ? (size_t)2 * vec * geo_block(g) * sizeof(float) : 0;
+    size_t smem = g.sub > 1 ? (size_t)2 * vec * geo_block(g) * sizeof(float) : 0;
+    if (vec > 1 && MHC_ADDPOOL_STAGES > 0) smem = std::max(smem, (size_t)MHC_ADDPOOL_STAGES * 5 * 16 * geo_block(g));
     ProfScope ps("k_add_residual_mix_pool_fwd", st);
-    MHC_DISPATCH(dtype, vec, (launch_k(k_add_residual_mix_fwd<T, V, true>, (unsigned)items, geo_block(g), smem, st,
-                                       (const T*)H, H_res, (const T*)branch_output, H_post, (T*)H_new, pool_partials, g)));
+    MHC_DISPATCH(dtype, vec, (launch_pool_k(k_add_residual_mix_fwd<T, V, true>, (unsigned)items, geo_block(g), smem, st,
+                                            (const T*)H, H_res, (const T*)branch_output, H_post, (T*)H_new, pool_partials, g)));
   } else {
     Geo g = make_geo(S, D, vec, GeoKind::Stream, MHC_TPC_ADDMIX);
     g.reverse = (MHC_REV_MASK >> 2) & 1;
@@ -998,10 +1042,11 @@ extern "C" int mhc_add_residual_pool_fwd(const void* H_residual, const void* bra
   const int64_t items = B * geo_slots(g);
   if (int e = check_grid("add_residual_pool_fwd", items)) return e;
   cudaStream_t st = (cudaStream_t)stream;
-  const size_t smem = g.sub > 1 ? (size_t)2 * vec * geo_block(g) * sizeof(float) : 0;
+  size_t smem = g.sub > 1 ? (size_t)2 * vec * geo_block(g) * sizeof(float) : 0;
+  if (vec > 1 && MHC_ADDPOOL_STAGES > 0) smem = std::max(smem, (size_t)MHC_ADDPOOL_STAGES * 5 * 16 * geo_block(g));
   {
     ProfScope ps("k_add_residual_pool_fwd", st);
-    MHC_DISPATCH(dtype, vec, (launch_k(k_add_residual_pool_fwd<T, V>, (unsigned)items, geo_block(g), smem, st,
+    MHC_DISPATCH(dtype, vec, (launch_pool_k(k_add_residual_pool_fwd<T, V>, (unsigned)items, geo_block(g), smem, st,
                                        (const T*)H_residual, (const T*)branch_output, H_post, (T*)H_new, pool_partials, g)));
   }
   return check_launch("add_residual_pool_fwd");

@@ -162,7 +162,9 @@ def test_stream_ops_golden(golden):
     assert_close(lv[1].grad, a["dbo"], RT, 2 * AT, "dbo"); assert_close_norm(lv[2].grad, a["dH_post"], RT, AT, "dH_post")
 
 
-SHAPES = [(1, 1, 8), (2, 5, 24), (1, 33, 7), (3, 130, 100), (2, 64, 1024), (1, 257, 2056), (2, 40, 8 * 300)]
+# the last two: rows of 320 / 640 / 896 packs, which take column groups narrower than 256 (several tokens abreast)
+SHAPES = [(1, 1, 8), (2, 5, 24), (1, 33, 7), (3, 130, 100), (2, 64, 1024), (1, 257, 2056), (2, 40, 8 * 300),
+          (2, 37, 8 * 320), (1, 21, 7168)]
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
@@ -543,7 +545,8 @@ def test_sequence_sharded_wrapper_single_rank_equals_layer():
         assert_close_norm(b["dlayer." + n], a["d" + n], RT, AT, n)
 
 
-@pytest.mark.parametrize("dtype,B,S,D", [(torch.float32, 2, 150, 96), (torch.bfloat16, 2, 300, 512), (torch.float32, 1, 70, 20)])
+@pytest.mark.parametrize("dtype,B,S,D", [(torch.float32, 2, 150, 96), (torch.bfloat16, 2, 300, 512), (torch.float32, 1, 70, 20),
+                                           (torch.bfloat16, 2, 70, 2560)])
 def test_cross_layer_pooling_matches_separate_pooling(dtype, B, S, D):
     """add_residual(pool_for_next=True) hands the next layer the token sums of H_new: that layer
     launches no mean-pool kernel and gives the same results (the pooled state only differs in
