@@ -28,7 +28,8 @@ enum class GeoKind { Stream, Reduce, Pool };
 #ifndef MHC_FIT_COLS
 #define MHC_FIT_COLS 1
 #endif
-Geo make_geo(int64_t S, int64_t D, int vec, GeoKind kind, int tpc, int occ = 0, bool fit_cols = MHC_FIT_COLS != 0);
+Geo make_geo(int64_t S, int64_t D, int vec, GeoKind kind, int tpc, int occ = 0, bool fit_cols = MHC_FIT_COLS != 0,
+             int narrow_mult = 1);
 int sm_count();
 inline int geo_block(const Geo& g) { return g.cols * g.sub; }
 inline int64_t geo_slots(const Geo& g) { return (int64_t)g.nchunk * g.CG; }  // partial rows per batch element

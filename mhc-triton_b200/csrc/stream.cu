@@ -82,6 +82,16 @@ namespace mhc {
 #ifndef MHC_TPC_MIXBWD
 #define MHC_TPC_MIXBWD 28
 #endif
+// Add-residual backward and apply pass on rows that take narrow column groups (several tokens abreast, e.g.
+// D = 7168): tokens per thread = this x the constants above.  Every CTA of these two kernels has fixed work
+// (a block reduction and a ticket; 32 registers of grad_x columns to load) that short chunks repeat often.
+// At full SM clock the chunk length makes no difference at that width (111 / 172 us against 114 / 171 at
+// D = 7168, two sequences), but between the GEMMs of an MLP branch, where the power cap holds the SMs near
+// 1.4 GHz, 16 tokens per thread take 129 / 188 us against 156 / 202 for 4.  Wide rows (D = 4096, 2048)
+// keep the short chunks, which are 1-4 % faster there at full clock.
+#ifndef MHC_NARROW_MULT
+#define MHC_NARROW_MULT 4
+#endif
 // Resident CTAs per SM of the add-residual backward (80 registers x 256 threads), for wave_tpc.
 #ifndef MHC_ADDBWD_OCC
 #define MHC_ADDBWD_OCC 3
@@ -747,7 +757,7 @@ static int wave_tpc(int64_t S, int CG, int abreast, int base, int occ) {
 
 // occ > 0: adjust the tokens per CTA to the device's waves (wave_tpc); occ < 0: the smallest chunk
 // wave_tpc could choose, i.e. an upper bound of the number of chunks (scratch-size queries).
-Geo make_geo(int64_t S, int64_t D, int vec, GeoKind kind, int tpc, int occ, bool fit_cols) {
+Geo make_geo(int64_t S, int64_t D, int vec, GeoKind kind, int tpc, int occ, bool fit_cols, int narrow_mult) {
   Geo g;
   g.reverse = 0;
   g.S = S;
@@ -776,6 +786,7 @@ Geo make_geo(int64_t S, int64_t D, int vec, GeoKind kind, int tpc, int occ, bool
     // with it the layout of the per-CTA partial sums) depends on S and D only, never on the batch size.
     // Narrow rows (fewer than 256 packs): the CTA keeps 256 threads by walking 256/cols tokens abreast.
     g.sub = MHC_MAX_COLS / cols;
+    if (g.sub > 1) tpc *= narrow_mult;
     const int t = occ < 0 ? tpc_lo(tpc) : wave_tpc(S, g.CG, g.sub, tpc, occ);
     g.tpc = t * g.sub;
   }
@@ -894,7 +905,7 @@ int mix_bwd_partials_impl(int mode, const void* dbi, const void* dHr, const void
 int mix_bwd_apply_impl(const void* dbi, const void* dHr, const float* H_pre, const float* H_res, const float* gx,
                        float inv_S, void* dH, int64_t B, int64_t S, int64_t D, int dtype, cudaStream_t st) {
   const int vec = pick_vec(dtype, D, {dbi, dHr, dH});
-  Geo g = make_geo(S, D, vec, GeoKind::Stream, MHC_TPC_APPLY, MHC_APPLY_MINB);
+  Geo g = make_geo(S, D, vec, GeoKind::Stream, MHC_TPC_APPLY, MHC_APPLY_MINB, MHC_FIT_COLS != 0, MHC_NARROW_MULT);
   g.reverse = (MHC_REV_MASK >> 5) & 1;
   const int64_t items = B * geo_slots(g);
   if (int e = check_grid("stream_mix_bwd_apply", items)) return e;
@@ -912,7 +923,7 @@ int64_t add_residual_bwd_need_bytes(const void* dH_new, const void* bo, const vo
                                     int64_t D, int dtype) {
   if (B <= 0 || S <= 0 || D <= 0) return 0;
   const int vec = pick_vec(dtype, D, {dH_new, bo, dbo});
-  return B * geo_slots(make_geo(S, D, vec, GeoKind::Reduce, MHC_TPC_ADDBWD, MHC_ADDBWD_OCC)) * 4 * (int64_t)sizeof(float);
+  return B * geo_slots(make_geo(S, D, vec, GeoKind::Reduce, MHC_TPC_ADDBWD, MHC_ADDBWD_OCC, MHC_FIT_COLS != 0, MHC_NARROW_MULT)) * 4 * (int64_t)sizeof(float);
 }
 
 int check_bsd_pub(const char* what, int64_t B, int64_t S, int64_t D, int dtype) { return check_bsd(what, B, S, D, dtype); }
@@ -1069,7 +1080,7 @@ extern "C" int mhc_add_residual_bwd(const void* dH_new, const void* branch_outpu
   }
   // sizes first, pointers last: a call whose scratch is too small says so even with null pointers
   const int vec = pick_vec(dtype, D, {dH_new, branch_output, d_branch_output});
-  Geo g = make_geo(S, D, vec, GeoKind::Reduce, MHC_TPC_ADDBWD, MHC_ADDBWD_OCC);
+  Geo g = make_geo(S, D, vec, GeoKind::Reduce, MHC_TPC_ADDBWD, MHC_ADDBWD_OCC, MHC_FIT_COLS != 0, MHC_NARROW_MULT);
   g.reverse = (MHC_REV_MASK >> 3) & 1;
   const int64_t slots = geo_slots(g), items = B * slots;
   if (int e = check_grid("add_residual_bwd", items)) return e;
