@@ -217,7 +217,7 @@ k_add_residual_fwd(const T* __restrict__ Hr, const T* __restrict__ bo, const flo
 // i.e. after rounding to T).  Same layout as k_meanpool_partial's output, so the next layer's
 // projection kernel consumes it directly and that layer's pass over H for pooling disappears.
 #ifndef MHC_TPC_ADDPOOL
-#define MHC_TPC_ADDPOOL 32
+#define MHC_TPC_ADDPOOL 64
 #endif
 #ifndef MHC_ADDPOOL_PIPE
 #define MHC_ADDPOOL_PIPE 0
@@ -451,8 +451,14 @@ __device__ __forceinline__ void finish_partials(const float* __restrict__ part, 
 // d_branch_output[s,d] = sum_n H_post[n] g[s,n,d];  partial dH_post[n] = sum_{s,d} g[s,n,d] bo[s,d].
 // part: [B, slots, 4].  With tickets (one zeroed counter per batch element) the CTA of a batch
 // element that stores its partial last also adds them all up into dH_post[b].
+#ifndef MHC_ADDBWD_MINB
+#define MHC_ADDBWD_MINB 3
+#endif
+#ifndef MHC_ADDBWD_PIPE
+#define MHC_ADDBWD_PIPE 1
+#endif
 template <typename T, int V>
-__global__ void __launch_bounds__(MHC_MAX_COLS)
+__global__ void __launch_bounds__(MHC_MAX_COLS, MHC_ADDBWD_MINB)
 k_add_residual_bwd(const T* __restrict__ G, const T* __restrict__ bo, const float* __restrict__ Hpost,
                    T* __restrict__ dbo, float* __restrict__ part, Geo g, int* tickets, float* __restrict__ dH_post) {
   pdl_prologue();
@@ -465,7 +471,7 @@ k_add_residual_bwd(const T* __restrict__ G, const T* __restrict__ bo, const floa
     for (int n = 0; n < 4; ++n) p[n] = __ldg(Hpost + it.b * 4 + n);
     const int64_t D = g.D, c0 = (int64_t)it.col * V, tok = it.b * g.S;
     using B5 = Bundle<T, V, 5>;
-    for_tokens_pipelined<B5>(
+    for_tokens<MHC_ADDBWD_PIPE != 0, B5>(
         it.s0 + it.sub, it.s1, g.sub,
         [&](B5& u, int64_t s) {
           const T* gp = G + (tok + s) * 4 * D + c0;
