@@ -35,6 +35,7 @@ kernels from baseline/_ref on the same workload.
 per token (x [R, K] fp32), forward + backward, with the per-kernel times.
 `--workload c5` is the 16-layer D=7168 stack, 2 sequences per GPU, every layer wrapping a bf16 MLP
 branch (7168 -> 28672 -> 7168, SiLU); the hyper-connection kernels are timed apart from the MLP.
+`--workload c3` is bf16 H(8,4096,4,2048) around a bf16 Linear(2048 -> 2048) branch, reported the same way.
 """
 
 import argparse
@@ -176,7 +177,7 @@ def describe(name, world=1, scaling="strong"):
     B, S, D, dtype = WORKLOADS[name]
     nl = LAYERS.get(name, 1)
     stack = f"stack of {nl} layers, " if nl > 1 else ""
-    branch = "bf16 MLP branch (D -> 4D -> D, SiLU)" if name == "c5" else "identity branch"
+    branch = {"c5": "bf16 MLP branch (D -> 4D -> D, SiLU)", "c3": "bf16 Linear(D -> D) branch"}.get(name, "identity branch")
     if name in PER_GPU_BATCH or scaling == "weak":
         batch = f"H({B},{S},4,{D}) on every GPU"
     else:
@@ -540,6 +541,9 @@ class Bench:
             torch.manual_seed(100 + rank)
             self.branches = [torch.nn.Sequential(torch.nn.Linear(D, 4 * D), torch.nn.SiLU(), torch.nn.Linear(4 * D, D))
                              .to(dev).to(dtype) for _ in range(self.n_layers)]
+        elif name == "c3" and not args.identity_branch:
+            torch.manual_seed(100 + rank)
+            self.branches = [torch.nn.Linear(D, D).to(dev).to(dtype) for _ in range(self.n_layers)]
         if self.readme:
             for layer in self.layers:
                 layer.half()
@@ -667,7 +671,7 @@ def main():
     ap.add_argument("--scaling", default="strong", choices=["weak", "strong"],
                     help="strong: the workload's batch is split over the ranks; weak: every rank runs the whole batch")
     ap.add_argument("--layers", type=int, default=None, help="override the number of stacked layers")
-    ap.add_argument("--identity-branch", action="store_true", help="c5: identity branches instead of the MLP")
+    ap.add_argument("--identity-branch", action="store_true", help="c5 / c3: identity branches instead of the MLP / Linear")
     ap.add_argument("--no-cross-layer", action="store_true",
                     help="stacks: let every layer pool its own input instead of taking the sums from the layer before")
     ap.add_argument("--graph", dest="graph", action="store_true", default=None,
@@ -713,7 +717,8 @@ def main():
         if B0 % world:
             raise SystemExit(f"batch {B0} does not split over {world} ranks")
         B = B0 // world
-    use_graph = args.graph if args.graph is not None else (B < B0 and not readme and name != "c5")
+    branchy = name == "c5" or (name == "c3" and not args.identity_branch)   # steps with torch branch modules run eagerly
+    use_graph = args.graph if args.graph is not None else (B < B0 and not readme and not branchy)
     if readme:
         args.no_e2e = True
         use_graph = False
@@ -795,7 +800,7 @@ def main():
     e2e = None
     weak, streamed, e2e_step = None, None, None
     has_branches = bool(bench.branches)
-    if not args.no_e2e and n_layers == 1:   # the host-streamed step drives one layer
+    if not args.no_e2e and n_layers == 1 and not has_branches:   # the host-streamed step drives one layer, no branch
         Bh = bench.B
         H_host = bench.H.detach().cpu().pin_memory()
         g_host = bench.g.cpu().pin_memory()
@@ -885,8 +890,8 @@ def main():
                                              "started inside the backward beside the pass that writes dH"))
                                 if world > 1 else "none",
                                 **({"batch_overridden": B} if args.batch else {}),
-                                **({"branch_overridden": "identity branches instead of the MLP"}
-                                   if name == "c5" and args.identity_branch else {})),
+                                **({"branch_overridden": "identity branches instead of the MLP / Linear"}
+                                   if name in ("c5", "c3") and args.identity_branch else {})),
             "value_spread": {"regions": len(regions), "steps_per_region": args.steps, "median": value,
                              "min": min(vals), "max": max(vals)},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches) * world,
@@ -898,7 +903,7 @@ def main():
                                "mlp_and_rest_ms_per_step": ms_per_step - total_hc,
                                "what": "sum of the hyper-connection kernels' durations per step (CUDA events around "
                                        "every one of them, breakdown pass); `value` of the line is the whole step "
-                                       "including the MLP branches"}
+                                       "including the branch modules"}
         print(json.dumps(line))
     ok = parity is None or parity["ok"]
     if world > 1:
