@@ -232,7 +232,7 @@ template <typename T, int V>
 __global__ void __launch_bounds__(MHC_MAX_COLS, 2)
 k_add_residual_pool_fwd(const T* __restrict__ Hr, const T* __restrict__ bo, const float* __restrict__ Hpost,
                         T* __restrict__ Hn, float* __restrict__ pool, Geo g) {
-  extern __shared__ float sm[];  // [2*V][sub][cols], used when several tokens are walked abreast
+  extern __shared__ __align__(16) float sm[];  // [2*V][sub][cols], used when several tokens are walked abreast
   pdl_prologue();
   const Item it = decode_item(g);
   const int64_t D = g.D, c0 = (int64_t)it.col * V, tok = it.b * g.S;
@@ -335,7 +335,7 @@ template <typename T, int V, bool POOL>
 __global__ void __launch_bounds__(MHC_MAX_COLS, POOL ? MHC_ADDMIXPOOL_MINB : MHC_ADDMIX_MINB)
 k_add_residual_mix_fwd(const T* __restrict__ H, const float* __restrict__ Hres, const T* __restrict__ bo,
                        const float* __restrict__ Hpost, T* __restrict__ Hn, float* __restrict__ pool, Geo g) {
-  extern __shared__ float sm[];  // POOL: [2*V][sub][cols]
+  extern __shared__ __align__(16) float sm[];  // POOL: [2*V][sub][cols]
   pdl_prologue();
   const Item it = decode_item(g);
   const int64_t D = g.D, c0 = (int64_t)it.col * V, tok = it.b * g.S;
