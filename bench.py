@@ -90,12 +90,12 @@ MOVED_UNITS = 42
 # summarised under profiles/, per batch element of the c4 shape (traffic is proportional to the
 # batch; writes still dirty in L2 at kernel end are not counted); None = not captured.
 NCU_TRAFFIC_PER_SEQUENCE = {
-    ("c4", "k_stream_mix_bwd_apply"): (335.700992e6 + 212.415232e6) / 2,
-    ("c4", "k_add_residual_mix_fwd"): (335.574016e6 + 212.414720e6) / 2,
-    ("c4", "k_stream_mix_bwd_reduce"): (604.011008e6 + 3.462656e6) / 2,
-    ("c4", "k_add_residual_bwd"): (335.565824e6 + 13.202944e6) / 2,
-    ("c4", "k_stream_premix_fwd"): (268.446208e6 + 12.989696e6) / 2,
-    ("c4", "k_meanpool_partial"): (268.447232e6 + 3.391232e6) / 2,
+    ("c4", "k_stream_mix_bwd_apply"): (335.690752e6 + 212.552704e6) / 2,
+    ("c4", "k_add_residual_mix_fwd"): (335.570688e6 + 213.849856e6) / 2,
+    ("c4", "k_stream_mix_bwd_reduce"): (604.014592e6 + 3.558144e6) / 2,
+    ("c4", "k_add_residual_bwd"): (335.564800e6 + 13.082880e6) / 2,
+    ("c4", "k_stream_premix_fwd"): (268.446464e6 + 12.829440e6) / 2,
+    ("c4", "k_meanpool_partial"): (268.447488e6 + 4.223744e6) / 2,
 }
 
 
