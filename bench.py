@@ -173,11 +173,13 @@ def make_layer(D, device, seed=0, layer_idx=0):
     return hc.to(device)
 
 
-def describe(name, world=1, scaling="strong"):
+def describe(name, world=1, scaling="strong", identity=False, layers=None):
     B, S, D, dtype = WORKLOADS[name]
-    nl = LAYERS.get(name, 1)
+    nl = layers or LAYERS.get(name, 1)
     stack = f"stack of {nl} layers, " if nl > 1 else ""
     branch = {"c5": "bf16 MLP branch (D -> 4D -> D, SiLU)", "c3": "bf16 Linear(D -> D) branch"}.get(name, "identity branch")
+    if identity:
+        branch = "identity branch"
     if name in PER_GPU_BATCH or scaling == "weak":
         batch = f"H({B},{S},4,{D}) on every GPU"
     else:
@@ -186,11 +188,11 @@ def describe(name, world=1, scaling="strong"):
             f"fp32 phi[{4 * D},24], 20 Sinkhorn iters, {branch}")
 
 
-def config_of(name, world, scaling, per_gpu_batch, tokens, n_layers, **more):
+def config_of(name, world, scaling, per_gpu_batch, tokens, n_layers, identity=False, **more):
     """The `config` object of the JSON line; the reference arms use the same keys."""
     B, S, D, dtype = WORKLOADS[name]
     esz = torch.empty(0, dtype=dtype).element_size()
-    cfg = {"workload": describe(name, world, scaling), "global_tokens": tokens, "sharding": f"batch x{world}",
+    cfg = {"workload": describe(name, world, scaling, identity, n_layers), "global_tokens": tokens, "sharding": f"batch x{world}",
            "per_gpu_batch": per_gpu_batch, "layers": n_layers,
            "l2": "inputs larger than L2 (H alone is %.0f MiB per GPU)" % (per_gpu_batch * S * 4 * D * esz / 2 ** 20)}
     cfg.update(more)
@@ -289,7 +291,7 @@ def run_reference(args):
     sample = (f"{'whole batch' if whole else 'sample'}: {nseq} of {B} sequences per step ({nseq * S} tokens, D={D}), "
               f"fp32 math on {cores} threads, fwd+bwd; sequences are independent, so tokens/s of a sample is tokens/s "
               f"of the batch")
-    cfg = config_of(args.workload, 1, "strong", nseq, nseq * S, 1, collective="none", cuda_graph=False,
+    cfg = config_of(args.workload, 1, "strong", nseq, nseq * S, 1, identity=True, collective="none", cuda_graph=False,
                     timed="whole batch" if whole else f"sample of {nseq} of {B} sequences")
     line = {
         "impl": "reference", "metric": METRIC, "value": tps, "unit": "tokens/s", "n_gpus": args.gpus,
@@ -323,20 +325,25 @@ def run_reference_triton(args):
     gen = torch.Generator(device=dev).manual_seed(1234)
     H = torch.cat([torch.randn(1, S, 4, D, device=dev, generator=gen).to(dtype) for _ in range(B)]).requires_grad_(True)
     g = torch.cat([torch.randn(1, S, 4, D, device=dev, generator=gen).to(dtype) for _ in range(B)])
-    layer = ref_mhc.HyperConnection(dim=D, num_streams=4, dynamic=True, sinkhorn_iters=20, init_scale=0.1, layer_idx=0)
-    cpu_gen = torch.Generator().manual_seed(0)
-    with torch.no_grad():
-        layer.phi.copy_((torch.randn(24, 4 * D, generator=cpu_gen) * 0.02).T.contiguous())
-    layer = layer.to(dev)
-    if readme:
-        layer = layer.half()
+    # this arm times the hyper-connection layers alone: identity branches (0.5 x in the README protocol), --layers deep
+    n_layers = args.layers or 1
+    layers = []
+    for i in range(n_layers):
+        layer = ref_mhc.HyperConnection(dim=D, num_streams=4, dynamic=True, sinkhorn_iters=20, init_scale=0.1, layer_idx=i)
+        cpu_gen = torch.Generator().manual_seed(i)
+        with torch.no_grad():
+            layer.phi.copy_((torch.randn(24, 4 * D, generator=cpu_gen) * 0.02).T.contiguous())
+        layer = layer.to(dev)
+        layers.append(layer.half() if readme else layer)
 
     def step():
         H.grad = None
-        for q in layer.parameters():
-            q.grad = None
-        bi, add = layer(H)
-        h = add(bi * 0.5 if readme else bi)
+        h = H
+        for layer in layers:
+            for q in layer.parameters():
+                q.grad = None
+            bi, add = layer(h)
+            h = add(bi * 0.5 if readme else bi)
         if readme:
             h.sum().backward()
         else:
@@ -362,9 +369,9 @@ def run_reference_triton(args):
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": (tokens / (ms * 1e-3) / README_PUBLISHED_TOKENS_PER_S) if readme else None,
         "dtype": {torch.bfloat16: "bf16", torch.float16: "f16"}.get(dtype, "f32"), "data": "synthetic",
-        "config": config_of(args.workload, 1, "strong", B, tokens, 1, collective="none", cuda_graph=False),
+        "config": config_of(args.workload, 1, "strong", B, tokens, n_layers, identity=True, collective="none", cuda_graph=False),
         "value_spread": {"min_ms": min(vals), "max_ms": max(vals), "regions": REPEATS},
-        "hbm_gbs_on_algorithmic_bytes": TOTAL_UNITS * D * esz * tokens / (ms * 1e-3) / 1e9,
+        "hbm_gbs_on_algorithmic_bytes": TOTAL_UNITS * D * esz * tokens * n_layers / (ms * 1e-3) / 1e9,
     }))
 
 
@@ -889,9 +896,8 @@ def main():
                                             ("outside the graphs, beside the next forward" if use_graph else
                                              "started inside the backward beside the pass that writes dH"))
                                 if world > 1 else "none",
-                                **({"batch_overridden": B} if args.batch else {}),
-                                **({"branch_overridden": "identity branches instead of the MLP / Linear"}
-                                   if name in ("c5", "c3") and args.identity_branch else {})),
+                                identity=args.identity_branch,
+                                **({"batch_overridden": B} if args.batch else {})),
             "value_spread": {"regions": len(regions), "steps_per_region": args.steps, "median": value,
                              "min": min(vals), "max": max(vals)},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches) * world,
