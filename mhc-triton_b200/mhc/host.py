@@ -27,6 +27,8 @@ class HostStreamedStep:
         self.s_in = torch.cuda.Stream(device=self.dev)
         self.s_out = torch.cuda.Stream(device=self.dev)
         self._stage = None
+        self._free_ev = [None] * self.nslots   # per staging slot: the backward that last read it (kept across calls)
+        self._next = 0                         # running group count: consecutive calls rotate through the slots
 
     def _staging(self, shape, dtype):
         key = (tuple(shape), dtype)
@@ -34,6 +36,7 @@ class HostStreamedStep:
             bufs = [(torch.empty(shape, device=self.dev, dtype=dtype), torch.empty(shape, device=self.dev, dtype=dtype))
                     for _ in range(self.nslots)]
             self._stage = (key, bufs)
+            self._free_ev = [None] * self.nslots
         return self._stage[1]
 
     def __call__(self, H_host: torch.Tensor, g_host: torch.Tensor, out_H_new: torch.Tensor, out_dH: torch.Tensor,
@@ -47,17 +50,19 @@ class HostStreamedStep:
         G = self.group
         bufs = self._staging((G,) + tuple(H_host.shape[1:]), H_host.dtype)
         comp = torch.cuda.current_stream(self.dev)
-        free_ev = [None] * self.nslots
+        free_ev = self._free_ev
+        first = self._next
         hook = layer.grads_ready_hook
         n_groups = (B + G - 1) // G
         keep = []
         for i in range(n_groups):
             lo, hi = i * G, min(B, (i + 1) * G)
             n = hi - lo
-            Hd, gd = bufs[i % self.nslots]
+            slot = (first + i) % self.nslots
+            Hd, gd = bufs[slot]
             with torch.cuda.stream(self.s_in):
-                if free_ev[i % self.nslots] is not None:
-                    self.s_in.wait_event(free_ev[i % self.nslots])
+                if free_ev[slot] is not None:   # also holds across calls: the previous call's kernels may still read it
+                    self.s_in.wait_event(free_ev[slot])
                 Hd[:n].copy_(H_host[lo:hi], non_blocking=True)
                 ev_in = torch.cuda.Event()
                 ev_in.record(self.s_in)          # the forward needs only H ...
@@ -76,7 +81,7 @@ class HostStreamedStep:
             H_new.backward(gd[:n])
             ev_bwd = torch.cuda.Event()
             ev_bwd.record(comp)
-            free_ev[i % self.nslots] = ev_bwd
+            free_ev[slot] = ev_bwd
             with torch.cuda.stream(self.s_out):
                 self.s_out.wait_event(ev_fwd)
                 out_H_new[lo:hi].copy_(H_new.detach(), non_blocking=True)
@@ -85,6 +90,7 @@ class HostStreamedStep:
             H_new.record_stream(self.s_out)
             Hin.grad.record_stream(self.s_out)
             keep.append((H_new, Hin))
+        self._next = (first + n_groups) % self.nslots
         layer.grad_accumulate = False
         layer.grads_ready_hook = hook
         sync.finish()

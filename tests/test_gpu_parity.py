@@ -424,6 +424,29 @@ def test_host_streamed_step_matches_direct_run():
     assert torch.equal(flat[:4 * D * 24].view(4 * D, 24), hc.phi.grad.cpu())
 
 
+def test_host_streamed_step_back_to_back_calls_with_different_data():
+    """Two calls queued without a synchronisation in between, each with its own inputs and outputs: the
+    second call's uploads must not overwrite staging buffers that the first call's kernels still read."""
+    import mhc
+    torch.manual_seed(6)
+    B, S, D = 1, 2048, 1024                     # one group per call, kernels long enough to still run
+    p = cases.perturb_params_(O.default_params(D, 0, 0.1), 13)
+    hc = to_module(mhc.HyperConnection(dim=D), p).to(DEV)
+    data = [(torch.randn(B, S, 4, D).bfloat16(), torch.randn(B, S, 4, D).bfloat16()) for _ in range(4)]
+    direct = []
+    for H, up in data:
+        r = _run_module(hc, H, up, lambda t: t)
+        direct.append((r["H_new"].cpu(), r["dH"].cpu()))
+    step = mhc.HostStreamedStep(hc, group=1, slots=2)
+    pinned = [(H.pin_memory(), up.pin_memory(), torch.empty_like(H).pin_memory(), torch.empty_like(H).pin_memory())
+              for H, up in data]
+    for Hh, gh, out_new, out_dH in pinned:      # four calls on two slots, no synchronisation in between
+        step(Hh, gh, out_new, out_dH)
+    torch.cuda.synchronize()
+    for (Hh, gh, out_new, out_dH), (want_new, want_dH) in zip(pinned, direct):
+        assert torch.equal(out_new, want_new) and torch.equal(out_dH, want_dH)
+
+
 def test_layer_stack_with_mlp_branches():
     """Reduced form of the 16-layer configuration: a stack of dynamic layers, each wrapping a
     2-layer SiLU MLP branch, fp32, against the oracle chained the same way."""
@@ -546,7 +569,7 @@ def test_sequence_sharded_wrapper_single_rank_equals_layer():
 
 
 @pytest.mark.parametrize("dtype,B,S,D", [(torch.float32, 2, 150, 96), (torch.bfloat16, 2, 300, 512), (torch.float32, 1, 70, 20),
-                                           (torch.bfloat16, 2, 70, 2560)])
+                                           (torch.bfloat16, 2, 70, 2560), (torch.bfloat16, 1, 3, 512), (torch.float32, 2, 1, 256)])
 def test_cross_layer_pooling_matches_separate_pooling(dtype, B, S, D):
     """add_residual(pool_for_next=True) hands the next layer the token sums of H_new: that layer
     launches no mean-pool kernel and gives the same results (the pooled state only differs in
