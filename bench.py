@@ -637,17 +637,40 @@ class Bench:
             self.sync.set_hooks(False)
 
 
-def timed_regions(bench, steps, repeats, barrier, world, dev):
+PROFILE_EVERY = 5   # the dominant kernel's launches carry CUDA events in every 5th step of a timed region
+
+
+def _profile_resume(kernel):
+    from mhc import _lib
+    _lib.load().mhc_profile_enable(2)   # resume, keeping the records of the earlier sampled steps
+
+
+def _profile_pause():
+    from mhc import _lib
+    _lib.load().mhc_profile_enable(0)
+
+
+def timed_regions(bench, steps, repeats, barrier, world, dev, profiled_kernel=None):
     """`repeats` regions of exactly `steps` steps, each bracketed by a barrier + synchronize and timed
-    with CUDA events on the launching stream; returns per-region milliseconds (max over ranks)."""
+    with CUDA events on the launching stream; returns per-region milliseconds (max over ranks).
+    profiled_kernel: its launches are bracketed by the library's own events in every PROFILE_EVERY-th step
+    (an event on either side of a kernel keeps it from overlapping its neighbours' tails under programmatic
+    dependent launch, about 30 us per step at config 4, so not in every step)."""
     import torch.distributed as dist
     out = []
     for _ in range(repeats):
         barrier()
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         ev0.record()
-        for _ in range(steps):
+        for i in range(steps):
+            if profiled_kernel is not None:
+                if i % PROFILE_EVERY == 0:
+                    _profile_resume(profiled_kernel)
+                elif i % PROFILE_EVERY == 1:
+                    _profile_pause()
             bench.step()
+        if profiled_kernel is not None:
+            _profile_pause()
         bench.drain()
         ev1.record()
         barrier()
@@ -757,9 +780,11 @@ def main():
     barrier()
     # ---- timed regions: K steps each, device-timed; only the dominant kernel's launches carry events ----
     _lib.profile_start(only=dom)
+    lib.mhc_profile_enable(0)          # switched on for every PROFILE_EVERY-th step inside the regions
     n0 = lib.mhc_launch_count()
     clocks.mark()
-    regions = timed_regions(bench, args.steps, max(1, args.repeats), barrier, world, dev)
+    regions = timed_regions(bench, args.steps, max(1, args.repeats), barrier, world, dev,
+                            profiled_kernel=None if use_graph else dom)
     launches = (lib.mhc_launch_count() - n0) // max(1, args.repeats)
     if use_graph:   # replayed launches are not seen by the library's counter: count the captured step's kernels
         launches = int(sum(c for c, _ in breakdown.values()) / 3) * args.steps
@@ -793,7 +818,8 @@ def main():
         "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": dom_bytes / (dom_avg_ms * 1e-3) / 1e9 / peak,
         "traffic": traffic * B if traffic else None, "algorithmic_bytes_per_launch": dom_bytes,
         "avg_launch_ms": dom_avg_ms, "launches_timed": dom_calls,
-        "timed_where": "breakdown pass (the timed regions replay CUDA graphs)" if use_graph else "inside the timed regions",
+        "timed_where": "breakdown pass (the timed regions replay CUDA graphs)" if use_graph
+                       else f"inside the timed regions, every {PROFILE_EVERY}th step",
         "whole_step": {"algorithmic_bytes": step_bytes, "achieved": step_bytes / (step_ms_for_bytes * 1e-3) / 1e9,
                        "frac": step_bytes / (step_ms_for_bytes * 1e-3) / 1e9 / peak,
                        "note": "per GPU; algorithmic = 46 D*e bytes per token and layer (every op's tensors read once, "

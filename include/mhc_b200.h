@@ -86,7 +86,8 @@ int64_t mhc_launch_count(void);
 
 /* Per-kernel timing.  While enabled, every kernel launch of this library is bracketed by two CUDA
  * events on the stream it is launched on.  enable(1) drops earlier records and starts; enable(0)
- * stops.  After the device is synchronised, record i gives the kernel's name and its duration. */
+ * stops (pauses); enable(2) resumes and keeps the records, so that a caller can time a sample of its
+ * steps.  After the device is synchronised, record i gives the kernel's name and its duration. */
 int mhc_profile_enable(int on);
 /* Restrict timing to the kernel with this name (NULL or "" = every kernel); the events of a timed
  * kernel sit between it and its neighbours on the stream, so timing one kernel perturbs least. */

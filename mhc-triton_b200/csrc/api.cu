@@ -78,7 +78,7 @@ static void prof_clear() {
 }  // namespace mhc
 
 extern "C" int mhc_profile_enable(int on) {
-  if (on) mhc::prof_clear();
+  if (on == 1) mhc::prof_clear();   // 2 = resume, keeping the records
   mhc::g_prof_on.store(on ? 1 : 0);
   return MHC_OK;
 }
