@@ -778,7 +778,7 @@ def main():
     dom = max((n for n in breakdown if n in OP_UNITS), key=lambda n: breakdown[n][1])
     hc_ms_per_step = sum(t for _, t in breakdown.values()) / 3          # all hyper-connection kernels of one step
     barrier()
-    # ---- timed regions: K steps each, device-timed; only the dominant kernel's launches carry events ----
+    # ---- timed regions: K steps each, device-timed; the dominant kernel carries events in every 5th step ----
     _lib.profile_start(only=dom)
     lib.mhc_profile_enable(0)          # switched on for every PROFILE_EVERY-th step inside the regions
     n0 = lib.mhc_launch_count()
