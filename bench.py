@@ -19,7 +19,8 @@ batch on every GPU (`--scaling weak` makes that the headline instead).
 
 Rank 0 prints one JSON line: tokens/s over all ranks (device-timed, max over ranks; median of five
 timed regions of K steps each), the roofline of the dominant kernel (CUDA events around its
-launches inside the timed region when the step runs eagerly, else from the breakdown pass), the
+launches in every 5th step of the timed regions when the step runs eagerly, else from the breakdown
+pass), the
 same metric end to end from pinned host buffers with the measured PCIe ceiling beside it, the CPU
 implementation timed on the host cores, and a parity check of the batch-sharded and the
 sequence-sharded multi-GPU paths against the CPU oracle (untimed, after the timed regions; a failed
