@@ -610,26 +610,30 @@ def test_cross_layer_pooling_matches_separate_pooling(dtype, B, S, D):
     assert mhc.ops.pooled_sums_of(H1b) is None
 
 
-def test_step_replayed_from_cuda_graph_equals_eager():
+@pytest.mark.parametrize("n_layers,D", [(1, 128), (2, 512)])
+def test_step_replayed_from_cuda_graph_equals_eager(n_layers, D):
     """Forward + backward captured in a CUDA graph (kernels chained by programmatic dependent
     launch, no host synchronisation anywhere in the step) replays to the eager results, also
-    after the static input buffers are refilled."""
+    after the static input buffers are refilled.  Two layers: the first add-residual also pools
+    for the second (the kernel with the shared-memory ring of loads and a raised shared-memory limit)."""
     import mhc
     torch.manual_seed(13)
-    B, S, D = 2, 160, 128
-    p = cases.perturb_params_(O.default_params(D, 0, 0.1), 17)
-    hc = to_module(mhc.HyperConnection(dim=D), p).to(DEV)
-    sync = mhc.GradSync([hc])
+    B, S = 2, 160
+    hcs = [to_module(mhc.HyperConnection(dim=D, layer_idx=i), cases.perturb_params_(O.default_params(D, i, 0.1), 17 + i)).to(DEV)
+           for i in range(n_layers)]
+    sync = mhc.GradSync(hcs)
     H = torch.randn(B, S, 4, D, device=DEV).bfloat16().requires_grad_(True)
     g = torch.randn(B, S, 4, D, device=DEV).bfloat16()
     out = {}
 
     def step():
         H.grad = None
-        bi, add = hc(H)
-        H_new = add(torch.tanh(bi))
-        H_new.backward(g)
-        out["H_new"], out["dH"] = H_new, H.grad
+        h = H
+        for i, hc in enumerate(hcs):
+            bi, add = hc(h)
+            h = add(torch.tanh(bi), pool_for_next=i + 1 < n_layers)
+        h.backward(g)
+        out["H_new"], out["dH"] = h, H.grad
 
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
